@@ -1,0 +1,35 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def _have_gpu() -> bool:
+    import ctypes
+    try:
+        cu = ctypes.CDLL("libcuda.so.1")
+    except OSError:
+        return False
+    n = ctypes.c_int(0)
+    if cu.cuInit(0) != 0:
+        return False
+    if cu.cuDeviceGetCount(ctypes.byref(n)) != 0:
+        return False
+    return n.value > 0
+
+
+def pytest_collection_modifyitems(config, items):
+    if _have_gpu():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for it in items:
+        if "gpu" in it.keywords:
+            it.add_marker(skip)
