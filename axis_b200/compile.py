@@ -1,0 +1,596 @@
+"""Lowering of a Llama-class training step to one fused execution plan.
+
+Host-side mirror of the reference's `axis.compile` (axis/compile.py:27-664):
+same constructor arguments, same public attributes (`eng, pnames, shapes,
+owner, owned, rank, world, zero, attn_impl, lr, dtype, B, T, N, V, lora_r`) and
+same methods (`step / capture / replay_step / set_lr / grads / get_weights /
+state_dict / load_state_dict`).  What differs is the plan it emits:
+
+* parameters, gradients and AdamW moments live in flat arenas (per-tensor
+  buffers are windows into them), so clipping + AdamW is two launches over the
+  arena instead of two per tensor;
+* q/k/v stay in the [B,T,H,DH] layout the projections produce — rotary is
+  applied in place and the attention kernels read that layout directly, so no
+  head permutes exist;
+* residual adds ride in GEMM epilogues and in the RMSNorm backward; gradient
+  joins use accumulate-in-epilogue GEMMs; RMSNorm backward produces dx and dw
+  in one pass; cross-entropy writes dlogits over the logits; the embedding
+  scatter-add is ordered (no atomics);
+* data parallel: gradients are reduced to their owner rank in buckets on a
+  side stream while backward continues (axis/compile.py:490-496 all-reduces
+  per tensor after backward); ZeRO-1 keeps the reference's per-tensor greedy
+  owner map (axis/compile.py:128-139) bit for bit.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import numpy as np
+
+from axis_b200.engine import (
+    ADAMW_FLAT, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, EMBED_BWD_DET,
+    EMBED_I32, FORK, GEMM_EX, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
+    ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, Engine, f32_to_bf16_bits, op)
+
+LIN_ORDER = ("attn.q_proj", "attn.k_proj", "attn.v_proj", "attn.o_proj",
+             "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
+RB_BLOCKS = 148 * 2          # blocks of the fused RMSNorm backward (scratch rows)
+
+
+def _numel(shape) -> int:
+    return int(np.prod(shape))
+
+
+def _pad(n: int, q: int = CHUNK) -> int:
+    return (n + q - 1) // q * q
+
+
+def greedy_owner(pnames: Sequence[str], shapes: Dict[str, tuple], world: int, sharded: bool):
+    """Per-tensor owner map, identical to axis/compile.py:132-137: visit tensors
+    by decreasing size (stable), give each to the first least-loaded rank."""
+    load = [0] * world
+    owner = {}
+    for nm in sorted(pnames, key=lambda n: -_numel(shapes[n])):
+        r = int(np.argmin(load)) if sharded else 0
+        owner[nm] = r
+        load[r] += _numel(shapes[nm])
+    return owner, load
+
+
+class CompiledTransformer:
+    def __init__(self, lib_path: str, cfg: dict, weights: Dict[str, np.ndarray],
+                 batch: int, seq: int, lr: float = 3e-4, wd: float = 0.1,
+                 eps: float = 1e-5, tf32: bool = True, recompute_attn: bool = True,
+                 dtype: str = "fp32", attn_tile: int = 256, attn_impl: str = "auto",
+                 lora_r: int = 0, lora_alpha: float = 16.0,
+                 lora_targets=("q_proj", "k_proj", "v_proj", "o_proj",
+                               "gate_proj", "up_proj", "down_proj"),
+                 grad_sync: bool = False, max_grad_norm: float = 0.0,
+                 zero_stage: int = 0, rank: int = 0, world: int = 1,
+                 bucket_layers: int = 4, adam_eps: float = 1e-8):
+        assert dtype in ("fp32", "bf16")
+        assert attn_impl in ("auto", "flash", "tiled")
+        self.cfg = cfg
+        self.B, self.T = batch, seq
+        self.lr, self.wd = lr, wd
+        self.max_grad_norm = max_grad_norm
+        self.dtype = dtype
+        hf = dtype == "bf16"
+        DT = 1 if hf else 0
+        DTW = 2 if hf else 0
+        isz = 2 if hf else 4
+        V, D = cfg["vocab_size"], cfg["dim"]
+        L, H = cfg["n_layers"], cfg["n_heads"]
+        KV = cfg.get("n_kv_heads") or H
+        DH = D // H
+        MLP = cfg["mlp_hidden"]
+        tied = cfg.get("tie_embeddings", True)
+        theta = cfg.get("rope_theta", 10000.0)
+        B, T = batch, seq
+        N = B * T
+        scale = 1.0 / float(np.sqrt(DH))
+        self.N, self.V = N, V
+        self._L = L
+        lora = lora_r > 0
+        sc_l = float(lora_alpha) / lora_r if lora else 0.0
+        self.lora_r = lora_r
+        lin_geom = {"attn.q_proj": (D, H * DH), "attn.k_proj": (D, KV * DH),
+                    "attn.v_proj": (D, KV * DH), "attn.o_proj": (H * DH, D),
+                    "mlp.gate_proj": (D, MLP), "mlp.up_proj": (D, MLP),
+                    "mlp.down_proj": (MLP, D)}
+        lset = set(lora_targets) if lora else set()
+        if H % KV or DH % 2:
+            raise ValueError("n_heads must be a multiple of n_kv_heads and head_dim even")
+
+        # lib_path is the library path (None = the in-tree build); an object with the
+        # Engine interface is used as is (the CPU tests pass a plan interpreter)
+        eng = lib_path if hasattr(lib_path, "alloc") else Engine(lib_path)
+        eng.set_tf32(tf32)
+        self.eng = eng
+        A = eng.alloc
+        # the fused attention ops serve fp32 and bf16 alike; "tiled" is accepted for API
+        # compatibility and runs the same kernels
+        self.attn_impl = "flash" if (hf and attn_impl != "tiled") else "tiled"
+        self.attn_tile = max(1, min(attn_tile, T))
+
+        # slot 0 / 1: rotary tables (fp32) — slot 0 doubles as the "none" sentinel
+        half = DH // 2
+        freqs = 1.0 / (theta ** (np.arange(half, dtype=np.float32) / half))
+        ang = np.outer(np.arange(T, dtype=np.float32), freqs)
+        b_cos = eng.new_tensor(np.cos(ang).astype(np.float32))
+        b_sin = eng.new_tensor(np.sin(ang).astype(np.float32))
+        assert b_cos == 0
+
+        # ── parameter names / shapes (axis/compile.py:95-122) ──
+        base_names = ["embed.weight"]
+        for i in range(L):
+            p = f"blocks.{i}."
+            base_names += [p + "attn_norm.weight", p + "attn.q_proj.weight",
+                           p + "attn.k_proj.weight", p + "attn.v_proj.weight",
+                           p + "attn.o_proj.weight", p + "mlp_norm.weight",
+                           p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight",
+                           p + "mlp.down_proj.weight"]
+        base_names.append("norm.weight")
+        if not tied:
+            base_names.append("lm_head.weight")
+        if lora:
+            self.pnames, self.shapes = [], {}
+            for i in range(L):
+                for pref, (fin, fout) in lin_geom.items():
+                    if pref.split(".")[-1] in lset:
+                        self.pnames += [f"blocks.{i}.{pref}.lora_a", f"blocks.{i}.{pref}.lora_b"]
+                        self.shapes[f"blocks.{i}.{pref}.lora_a"] = (fin, lora_r)
+                        self.shapes[f"blocks.{i}.{pref}.lora_b"] = (lora_r, fout)
+        else:
+            self.pnames = base_names
+            self.shapes = {nm: tuple(weights[nm].shape) for nm in self.pnames}
+
+        # ── ownership (ZeRO-1) ──
+        zero = zero_stage >= 1 and world > 1
+        if zero:
+            assert hf, "ZeRO sharding requires dtype='bf16'"
+            assert grad_sync, "ZeRO sharding requires grad_sync=True (multi-GPU)"
+        self.owner, _ = greedy_owner(self.pnames, self.shapes, world, zero)
+        self.rank, self.world, self.zero = rank, world, zero
+        self.owned = [nm for nm in self.pnames if not zero or self.owner[nm] == rank]
+        self.grad_sync = bool(grad_sync) and world > 1
+        # reduction owner: the same greedy map over `world` ranks in both modes, so that
+        # replicated DP and ZeRO-1 sum every gradient in the same order
+        cw = world if self.grad_sync else 1
+        self._cown, _ = greedy_owner(self.pnames, self.shapes, cw, cw > 1)
+
+        # ── arena layout: by reduction owner, then by bucket (order of completion in backward) ──
+        def bucket_of(nm: str) -> int:
+            if nm in ("norm.weight", "lm_head.weight"):
+                return 0
+            if nm == "embed.weight":
+                return 1 + (L - 1) // bucket_layers
+            layer = int(nm.split(".")[1])
+            return 1 + (L - 1 - layer) // bucket_layers
+        nb = 2 + (L - 1) // bucket_layers
+        self._nbuckets = nb
+        off = 0
+        self._off: Dict[str, int] = {}
+        self._seg = []                     # (start, length) per reduction owner, in elements
+        self._groups = [[None] * nb for _ in range(cw)]     # (start, length) of (owner, bucket)
+        for r in range(cw):
+            s0 = off
+            for b in range(nb):
+                g0 = off
+                for nm in self.pnames:
+                    if self._cown[nm] == r and bucket_of(nm) == b:
+                        self._off[nm] = off
+                        off += _pad(_numel(self.shapes[nm]))
+                self._groups[r][b] = (g0, off - g0)
+            self._seg.append((s0, off - s0))
+        P_total = off
+        self._P_total = P_total
+        my_seg = self._seg[rank] if zero else (0, P_total)
+        self._my_seg = my_seg
+
+        # arenas: grads (all), mirror (all, bf16 mode), master/m/v (own segment under ZeRO)
+        self.a_grad = eng.alloc_zero(P_total * 4)
+        self.a_master = eng.alloc_zero(max(my_seg[1], 1) * 4)
+        self.a_m = eng.alloc_zero(max(my_seg[1], 1) * 4)
+        self.a_v = eng.alloc_zero(max(my_seg[1], 1) * 4)
+        self.a_mirror = eng.alloc_zero(P_total * 2) if hf else -1
+        flags = np.zeros(max(P_total // CHUNK, 1), dtype=np.uint8)
+        for nm in self.pnames:
+            if len(self.shapes[nm]) >= 2:
+                o = self._off[nm] // CHUNK
+                flags[o:o + _pad(_numel(self.shapes[nm])) // CHUNK] = 1
+        self.b_wdflag = eng.alloc(max(flags.size, 4), 1)
+        eng.upload_raw(self.b_wdflag, flags)
+
+        self.master, self.gbuf, self._mb, self._vb = {}, {}, {}, {}
+        P: Dict[str, int] = {}               # compute view of every weight the plan reads
+        src = dict(weights)
+        if lora:
+            rng_l = np.random.default_rng(0)
+            for i in range(L):
+                for pref, (fin, fout) in lin_geom.items():
+                    if pref.split(".")[-1] in lset:
+                        ka, kb = f"blocks.{i}.{pref}.lora_a", f"blocks.{i}.{pref}.lora_b"
+                        if ka not in src:
+                            src[ka] = (rng_l.standard_normal((fin, lora_r)) / np.sqrt(lora_r)).astype(np.float32)
+                        if kb not in src:
+                            src[kb] = np.zeros((lora_r, fout), dtype=np.float32)
+            # frozen base: compute copies only (bf16 bits converted on the host, or fp32)
+            tot = sum(_pad(_numel(weights[nm].shape)) for nm in base_names)
+            self.a_base = eng.alloc_zero(tot * isz)
+            o = 0
+            for nm in base_names:
+                w = np.ascontiguousarray(weights[nm], dtype=np.float32)
+                P[nm] = eng.view(self.a_base, o * isz, w.size * isz)
+                eng.upload_raw(P[nm], f32_to_bf16_bits(w) if hf else w)
+                o += _pad(w.size)
+        for nm in self.pnames:
+            n_el = _numel(self.shapes[nm])
+            o = self._off[nm]
+            self.gbuf[nm] = eng.view(self.a_grad, o * 4, n_el * 4)
+            w = np.ascontiguousarray(src[nm], dtype=np.float32)
+            if tuple(w.shape) != tuple(self.shapes[nm]):
+                raise ValueError(f"{nm}: shape {w.shape} != {self.shapes[nm]}")
+            if hf:
+                P[nm] = eng.view(self.a_mirror, o * 2, n_el * 2)
+            if not zero or self._cown[nm] == rank:
+                lo = o - my_seg[0]
+                self.master[nm] = eng.view(self.a_master, lo * 4, n_el * 4)
+                self._mb[nm] = eng.view(self.a_m, lo * 4, n_el * 4)
+                self._vb[nm] = eng.view(self.a_v, lo * 4, n_el * 4)
+                eng.upload(self.master[nm], w.reshape(-1))
+                if not hf:
+                    P[nm] = self.master[nm]
+            if hf and zero and self._cown[nm] != rank:
+                eng.upload_raw(P[nm], f32_to_bf16_bits(w))
+        if hf and my_seg[1] > 0:
+            # one cast of the whole owned segment (padding is zero on both sides)
+            eng.run([op(CAST, a=self.a_master,
+                        c=eng.view(self.a_mirror, my_seg[0] * 2, my_seg[1] * 2), m=my_seg[1], tb=0)])
+        self.pb = P
+
+        # ── io + scalars ──
+        self.b_ids = A(N)            # int32 token ids
+        self.b_tgt = A(N)            # int32 targets (< 0 ignored)
+        self.b_loss = A(1)
+        self.b_denom = A(1)          # valid-target count
+        self.b_lr = eng.new_tensor(np.array([lr], dtype=np.float32))
+        self.b_t = eng.new_tensor(np.zeros(1, dtype=np.float32))
+        self.b_gnorm = A(1)          # global gradient norm of the last step
+        self.b_sumsq = eng.alloc_zero(4 * max(cw, 1))     # per-owner sum of squares
+        self.b_sumsq_local = eng.alloc_zero(4)
+        npart = max(1, (max(s[1] for s in self._seg) + 8191) // 8192)
+        self.b_partials = A(npart)
+        self.b_ce_scratch = A(N + 8)
+        self.b_rb_scratch = A(RB_BLOCKS * D)
+
+        # ── saved activations ──
+        xs = [A(N * D, isz) for _ in range(L + 1)]
+        ys = [A(N * D, isz) for _ in range(L)]
+        q2s = [A(N * H * DH, isz) for _ in range(L)]
+        k2s = [A(N * KV * DH, isz) for _ in range(L)]
+        vs = [A(N * KV * DH, isz) for _ in range(L)]
+        at2s = [A(N * H * DH, isz) for _ in range(L)]
+        r1s = [A(N * D, isz) for _ in range(L)]
+        zs = [A(N * D, isz) for _ in range(L)]
+        gs = [A(N * MLP, isz) for _ in range(L)]
+        us = [A(N * MLP, isz) for _ in range(L)]
+        hs = [A(N * MLP, isz) for _ in range(L)]
+        lses = [A(B * H * T) for _ in range(L)]
+        # ── scratch ──
+        xf = A(N * D, isz)
+        logits = A(N * V, isz)               # dlogits overwrite the logits
+        dxf = A(N * D, isz)
+        dcur = A(N * D, isz); dr1 = A(N * D, isz); dz = A(N * D, isz); dy = A(N * D, isz)
+        dh_ = A(N * MLP, isz); dg_ = A(N * MLP, isz); du_ = A(N * MLP, isz)
+        dat2 = A(N * H * DH, isz); dq = A(N * H * DH, isz)
+        dk = A(N * KV * DH, isz); dv = A(N * KV * DH, isz)
+        bD = A(N * H)
+        if lora:
+            u_l = {(i, pref): A(N * lora_r, isz) for i in range(L) for pref in lin_geom
+                   if pref.split(".")[-1] in lset}
+            t1 = A(N * lora_r, isz)
+        G = self.gbuf
+
+        def lin_f(x, i, pref, y, res=-1):
+            """y = x@W (+ res) (+ s*(x@A)@B, with u = x@A saved)"""
+            fin, fout = lin_geom[pref]
+            key = f"blocks.{i}.{pref}"
+            if res >= 0:
+                o_ = [op(GEMM_EX, a=x, b=P[key + ".weight"], c=y, d=res, m=N, k=fin, n=fout, batch=1, dt=DT, beta=1.0)]
+            else:
+                o_ = [op(GEMM_SB, a=x, b=P[key + ".weight"], c=y, m=N, k=fin, n=fout, batch=1, dt=DT)]
+            if lora and pref.split(".")[-1] in lset:
+                u = u_l[(i, pref)]
+                o_ += [op(GEMM_SB, a=x, b=P[key + ".lora_a"], c=u, m=N, k=fin, n=lora_r, batch=1, dt=DT),
+                       op(GEMM_SB, a=u, b=P[key + ".lora_b"], c=y, m=N, k=lora_r, n=fout, batch=1, dt=DT,
+                          alpha=sc_l, beta=1.0)]
+            return o_
+
+        def lin_b(g, x, i, pref, dx, acc=False):
+            """dx (+)= g@W_eff^T ; weight grads: dW (full) or dA/dB (LoRA)"""
+            fin, fout = lin_geom[pref]
+            key = f"blocks.{i}.{pref}"
+            o_ = [op(GEMM_SB, a=g, b=P[key + ".weight"], c=dx, m=N, k=fout, n=fin, batch=1, tb=1, dt=DT,
+                     beta=1.0 if acc else 0.0)]
+            if not lora:
+                o_ += [op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)]
+            elif pref.split(".")[-1] in lset:
+                u = u_l[(i, pref)]
+                o_ += [op(GEMM_SB, a=g, b=P[key + ".lora_b"], c=t1, m=N, k=fout, n=lora_r, batch=1, tb=1, dt=DT),
+                       op(GEMM_SB, a=t1, b=P[key + ".lora_a"], c=dx, m=N, k=lora_r, n=fin, batch=1, tb=1, dt=DT,
+                          alpha=sc_l, beta=1.0),
+                       op(GEMM_SB, a=x, b=t1, c=G[key + ".lora_a"], m=fin, n=lora_r, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l),
+                       op(GEMM_SB, a=u, b=g, c=G[key + ".lora_b"], m=lora_r, n=fout, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l)]
+            return o_
+
+        def norm_b(x, wname, g, res, out):
+            """out = res + rmsnorm_bwd(x, w, g); dw -> G[wname] unless frozen"""
+            return [op(RMSNORM_BWD_ACC, a=x, b=P[wname], d=g, c=out, tb=(res if res >= 0 else 0),
+                       sa=(0 if lora else G[wname]), sb=self.b_rb_scratch, m=N, n=D, dt=DT, alpha=eps)]
+
+        # ── forward ──
+        plan = [op(EMBED_I32, a=P["embed.weight"], b=self.b_ids, c=xs[0], m=N, n=D, dt=DT)]
+        for i in range(L):
+            p = f"blocks.{i}."
+            plan += [op(RMSNORM, a=xs[i], b=P[p + "attn_norm.weight"], c=ys[i], m=N, n=D, dt=DT, alpha=eps)]
+            plan += lin_f(ys[i], i, "attn.q_proj", q2s[i])
+            plan += lin_f(ys[i], i, "attn.k_proj", k2s[i])
+            plan += lin_f(ys[i], i, "attn.v_proj", vs[i])
+            plan += [
+                op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT),
+                op(ROPE_BTHD, a=k2s[i], b=b_cos, d=b_sin, c=k2s[i], batch=B, m=T, k=KV, n=DH, dt=DT),
+                op(ATTN_FWD, a=q2s[i], b=k2s[i], d=vs[i], c=at2s[i], sa=lses[i],
+                   m=T, n=DH, k=KV, batch=B, tb=H, dt=DT, alpha=scale),
+            ]
+            plan += lin_f(at2s[i], i, "attn.o_proj", r1s[i], res=xs[i])
+            plan += [op(RMSNORM, a=r1s[i], b=P[p + "mlp_norm.weight"], c=zs[i], m=N, n=D, dt=DT, alpha=eps)]
+            plan += lin_f(zs[i], i, "mlp.gate_proj", gs[i])
+            plan += lin_f(zs[i], i, "mlp.up_proj", us[i])
+            plan += [op(SILU_MUL, a=gs[i], b=us[i], c=hs[i], n=N * MLP, dt=DT)]
+            plan += lin_f(hs[i], i, "mlp.down_proj", xs[i + 1], res=r1s[i])
+
+        # ── head + loss ──
+        lm_w = P["embed.weight"] if tied else P["lm_head.weight"]
+        plan += [
+            op(RMSNORM, a=xs[L], b=P["norm.weight"], c=xf, m=N, n=D, dt=DT, alpha=eps),
+            op(GEMM_SB, a=xf, b=lm_w, c=logits, m=N, k=D, n=V, batch=1, tb=(1 if tied else 0), dt=DT),
+            op(CE_FUSED, a=logits, b=self.b_tgt, c=logits, d=self.b_loss, sa=self.b_denom,
+               sb=self.b_ce_scratch, m=N, n=V, dt=DT),
+        ]
+        dlogits = logits
+        self._b_logits = logits
+
+        # ── backward ──
+        bucket_done: List[int] = []          # plan index after which bucket b is complete
+        if tied:
+            plan += [op(GEMM_SB, a=dlogits, b=lm_w, c=dxf, m=N, k=V, n=D, batch=1, tb=0, dt=DT)]
+            if not lora:
+                plan += [op(GEMM_SB, a=dlogits, b=xf, c=G["embed.weight"], m=V, n=D, k=N, batch=1, tb=2, dt=DTW)]
+        else:
+            plan += [op(GEMM_SB, a=dlogits, b=lm_w, c=dxf, m=N, k=V, n=D, batch=1, tb=1, dt=DT)]
+            if not lora:
+                plan += [op(GEMM_SB, a=xf, b=dlogits, c=G["lm_head.weight"], m=D, n=V, k=N, batch=1, tb=2, dt=DTW)]
+        plan += norm_b(xs[L], "norm.weight", dxf, -1, dcur)
+        marks = {0: len(plan)}
+        for i in reversed(range(L)):
+            p = f"blocks.{i}."
+            plan += lin_b(dcur, hs[i], i, "mlp.down_proj", dh_)
+            plan += [op(SILU_BWD, a=gs[i], b=us[i], d=dh_, c=dg_, tb=du_, n=N * MLP, dt=DT)]
+            plan += lin_b(dg_, zs[i], i, "mlp.gate_proj", dz)
+            plan += lin_b(du_, zs[i], i, "mlp.up_proj", dz, acc=True)
+            plan += norm_b(r1s[i], p + "mlp_norm.weight", dz, dcur, dr1)
+            plan += lin_b(dr1, at2s[i], i, "attn.o_proj", dat2)
+            plan += [
+                op(ATTN_BWD, a=q2s[i], b=k2s[i], d=vs[i], c=dat2, sa=lses[i], sb=at2s[i],
+                   tb=dq, sc=dk, oa=dv, ob=H, oc=bD, m=T, n=DH, k=KV, batch=B, dt=DT, alpha=scale),
+                op(ROPE_BTHD, a=dq, b=b_cos, d=b_sin, c=dq, batch=B, m=T, k=H, n=DH, tb=1, dt=DT),
+                op(ROPE_BTHD, a=dk, b=b_cos, d=b_sin, c=dk, batch=B, m=T, k=KV, n=DH, tb=1, dt=DT),
+            ]
+            plan += lin_b(dq, ys[i], i, "attn.q_proj", dy)
+            plan += lin_b(dk, ys[i], i, "attn.k_proj", dy, acc=True)
+            plan += lin_b(dv, ys[i], i, "attn.v_proj", dy, acc=True)
+            plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
+            if (L - 1 - i) % bucket_layers == bucket_layers - 1 and i > 0:
+                marks[1 + (L - 1 - i) // bucket_layers] = len(plan)
+        if not lora:
+            if not tied:
+                plan += [op(SCALE, a=G["embed.weight"], c=G["embed.weight"], n=V * D, alpha=0.0)]
+            plan += [op(EMBED_BWD_DET, a=dcur, b=self.b_ids, c=G["embed.weight"], m=N, n=D, dt=DT)]
+        marks[nb - 1] = len(plan)
+        self.plan_fb = plan
+
+        # ── gradient reduction: bucketed, on the side stream, overlapped with backward ──
+        def comm_ops(b):
+            red = [op(REDUCE, a=self.a_grad, m=ln // CHUNK, oa=st // CHUNK, tb=r)
+                   for r in range(cw) for (st, ln) in [self._groups[r][b]] if ln > 0]
+            if not red:
+                return []
+            out = [op(FORK), op(STREAM, tb=1), op(GROUP, tb=0)] + red + [op(GROUP, tb=1)]
+            if not zero:     # replicated: everyone gets the reduced gradients back
+                out += [op(GROUP, tb=0)] + [op(BROADCAST, a=self.a_grad, m=o[5], oa=o[14], tb=o[9]) for o in red] \
+                    + [op(GROUP, tb=1)]
+            return out + [op(STREAM, tb=0)]
+        self.plan_ar = []
+        if self.grad_sync:
+            merged, last = [], 0
+            for b in range(nb):
+                cut = marks.get(b, last)
+                merged += plan[last:cut] + comm_ops(b)
+                last = cut
+            merged += plan[last:] + [op(JOIN)]
+            self._plan_fb_sync = merged
+            self.plan_ar = [o for b in range(nb) for o in comm_ops(b)] + [op(JOIN)]
+        else:
+            self._plan_fb_sync = plan
+
+        # ── clip + AdamW over the arena ──
+        def opt_ops(max_norm):
+            ops_ = []
+            if zero:
+                s0, sl = my_seg
+                ops_ += [op(GNORM_FLAT, a=self.a_grad, c=self.b_partials, d=self.b_sumsq_local, ob=0,
+                            m=sl // CHUNK, oa=s0 // CHUNK, tb=self.b_t),
+                         op(ALLGATHER_F32, a=self.b_sumsq_local, c=self.b_sumsq, n=1)]
+            else:
+                for r in range(cw):
+                    s0, sl = self._seg[r]
+                    ops_ += [op(GNORM_FLAT, a=self.a_grad, c=self.b_partials, d=self.b_sumsq, ob=r,
+                                m=sl // CHUNK, oa=s0 // CHUNK, tb=(self.b_t if r == 0 else 0))]
+            s0, sl = my_seg
+            ops_ += [op(ADAMW_FLAT, a=self.a_master, b=self.a_grad, c=self.a_m, d=self.a_v,
+                        m=sl // CHUNK, k=s0 // CHUNK, sa=(self.a_mirror if hf else 0), sb=self.b_lr,
+                        tb=self.b_t, sc=self.b_wdflag, oa=self.b_sumsq, ob=cw, oc=self.b_gnorm,
+                        alpha=float(max_norm or 0.0), beta=self.wd, gamma=adam_eps)]
+            if zero:
+                ops_ += [op(GROUP, tb=0)] + \
+                    [op(BROADCAST, a=self.a_mirror, m=self._seg[r][1] // CHUNK, oa=self._seg[r][0] // CHUNK,
+                        tb=r, dt=1) for r in range(cw) if self._seg[r][1] > 0] + [op(GROUP, tb=1)]
+            return ops_
+        self._opt_ops = opt_ops
+        self.plan_step = self._plan_fb_sync + opt_ops(max_grad_norm)
+        self._plan_noclip = None
+        self._captured = False
+
+    # ── API (axis/compile.py:547-615) ──
+    def set_lr(self, lr: float) -> None:
+        """Learning rate for subsequent steps; lives in a device buffer, so it
+        also takes effect under CUDA-graph replay."""
+        self.lr = float(lr)
+        self.eng.upload(self.b_lr, np.array([lr], dtype=np.float32))
+
+    def _feed(self, tokens: np.ndarray, targets: np.ndarray) -> None:
+        if tokens.size != self.N or targets.size != self.N:
+            raise ValueError(f"expected {self.B}x{self.T} tokens and targets")
+        self.eng.upload_tokens(self.b_ids, np.where(np.asarray(tokens) < 0, self.V, tokens), self.V)
+        self.eng.upload_tokens(self.b_tgt, np.maximum(np.asarray(targets), -1), self.V)
+
+    def step(self, tokens: np.ndarray, targets: np.ndarray, t: int = None) -> float:
+        self._feed(tokens, targets)
+        if t is None:
+            self.eng.run(self.plan_step, sync=False)
+        else:
+            # parity path: bias correction for step t, no clipping
+            if self._plan_noclip is None:
+                self._plan_noclip = self._plan_fb_sync + self._opt_ops(0.0)
+            self.eng.upload(self.b_t, np.array([t - 1], dtype=np.float32))
+            self.eng.run(self._plan_noclip, sync=False)
+        return float(self.eng.download(self.b_loss, (1,))[0])
+
+    def capture(self, t: int = None) -> None:
+        if t is None:
+            self.eng.capture(self.plan_step)
+        else:
+            if self._plan_noclip is None:
+                self._plan_noclip = self._plan_fb_sync + self._opt_ops(0.0)
+            self.eng.upload(self.b_t, np.array([t - 1], dtype=np.float32))
+            self.eng.capture(self._plan_noclip)
+        self._captured = True
+
+    def replay_step(self, tokens: np.ndarray, targets: np.ndarray) -> float:
+        self._feed(tokens, targets)
+        self.eng.replay(1, sync=False)
+        return float(self.eng.download(self.b_loss, (1,))[0])
+
+    def forward_backward(self, tokens: np.ndarray, targets: np.ndarray) -> float:
+        """Forward + backward only (no reduction, no update); for gradient checks."""
+        self._feed(tokens, targets)
+        self.eng.run(self.plan_fb, sync=False)
+        return float(self.eng.download(self.b_loss, (1,))[0])
+
+    def grad_norm(self) -> float:
+        """Global gradient norm seen by the last optimizer step (before clipping)."""
+        return float(self.eng.download(self.b_gnorm, (1,))[0])
+
+    def valid_count(self) -> int:
+        """Number of non-ignored targets in the last batch (exact integer)."""
+        return int(self.eng.download(self.b_denom, (1,))[0])
+
+    def grads(self) -> Dict[str, np.ndarray]:
+        return {nm: self.eng.download(self.gbuf[nm], self.shapes[nm]) for nm in self.pnames}
+
+    def get_weights(self) -> Dict[str, np.ndarray]:
+        """Current fp32 master weights; under ZeRO only this rank's owned shard."""
+        return {nm: self.eng.download(self.master[nm], self.shapes[nm]) for nm in self.owned}
+
+    def state_dict(self) -> Dict[str, np.ndarray]:
+        st = {}
+        for nm in self.owned:
+            sh = self.shapes[nm]
+            st[f"w/{nm}"] = self.eng.download(self.master[nm], sh)
+            st[f"m/{nm}"] = self.eng.download(self._mb[nm], sh)
+            st[f"v/{nm}"] = self.eng.download(self._vb[nm], sh)
+        st["_t"] = self.eng.download(self.b_t, (1,))
+        st["_lr"] = np.array([self.lr], dtype=np.float32)
+        return st
+
+    def load_state_dict(self, st: Dict[str, np.ndarray]) -> None:
+        for nm in self.owned:
+            self.eng.upload(self.master[nm], np.asarray(st[f"w/{nm}"]).reshape(-1))
+            self.eng.upload(self._mb[nm], np.asarray(st[f"m/{nm}"]).reshape(-1))
+            self.eng.upload(self._vb[nm], np.asarray(st[f"v/{nm}"]).reshape(-1))
+        if self.dtype == "bf16" and self._my_seg[1] > 0:
+            s0, sl = self._my_seg
+            self.eng.run([op(CAST, a=self.a_master, c=self.eng.view(self.a_mirror, s0 * 2, sl * 2), m=sl, tb=0)])
+        self.eng.upload(self.b_t, np.asarray(st["_t"], dtype=np.float32).reshape(-1))
+        self.set_lr(float(np.asarray(st["_lr"]).reshape(-1)[0]))
+
+
+def compile_model(model, batch: int, seq: int, lib_path: str = None,
+                  lr: float = 3e-4, wd: float = 0.1, tf32: bool = True,
+                  recompute_attn: bool = True, dtype: str = "fp32",
+                  attn_tile: int = 256, attn_impl: str = "auto",
+                  grad_sync: bool = False, max_grad_norm: float = 0.0,
+                  zero_stage: int = 0, rank: int = 0, world: int = 1) -> CompiledTransformer:
+    """Compile a Transformer into a native training step (axis/compile.py:618-664).
+
+    `model` is anything shaped like the reference's `axis.nn.Transformer`:
+    `named_parameters()` yielding (name, obj-with-.data), `blocks` (with
+    `.attn.n_heads / .attn.n_kv_heads`), `tie_embeddings`.  LoRA-wrapped models
+    are detected from parameter names (`...lora_a` / `...lora_b`,
+    `...base.weight`), the rank from the adapter shape and alpha from the
+    wrapper's `scaling` attribute; base weights are then frozen.
+    """
+    weights = {n.replace(".base.weight", ".weight"): np.asarray(p.data)
+               for n, p in model.named_parameters()}
+    lora_r, lora_alpha = 0, 16.0
+    a_keys = [k for k in weights if k.endswith(".lora_a")]
+    if a_keys:
+        lora_r = int(weights[a_keys[0]].shape[1])
+        lora_alpha = float(_find_lora_scaling(model)) * lora_r
+    targets = tuple(sorted({k.split(".")[-2] for k in a_keys})) if lora_r else ()
+    blk = model.blocks[0]
+    cfg = dict(vocab_size=weights["embed.weight"].shape[0],
+               dim=weights["embed.weight"].shape[1],
+               n_layers=len(model.blocks),
+               n_heads=blk.attn.n_heads,
+               n_kv_heads=blk.attn.n_kv_heads,
+               mlp_hidden=weights["blocks.0.mlp.gate_proj.weight"].shape[1],
+               tie_embeddings=model.tie_embeddings)
+    return CompiledTransformer(lib_path, cfg, weights, batch, seq, lr=lr, wd=wd, tf32=tf32,
+                               recompute_attn=recompute_attn, dtype=dtype, attn_tile=attn_tile,
+                               attn_impl=attn_impl, lora_r=lora_r, lora_alpha=lora_alpha,
+                               lora_targets=targets or ("q_proj", "k_proj", "v_proj", "o_proj"),
+                               grad_sync=grad_sync, max_grad_norm=max_grad_norm,
+                               zero_stage=zero_stage, rank=rank, world=world)
+
+
+def _find_lora_scaling(model) -> float:
+    """alpha / rank of the first adapter module found (attribute `scaling`)."""
+    stack, seen = [model], set()
+    while stack:
+        m = stack.pop()
+        if id(m) in seen:
+            continue
+        seen.add(id(m))
+        if hasattr(m, "lora_a") and hasattr(m, "scaling"):
+            return float(m.scaling)
+        for child in getattr(m, "_modules", {}).values():
+            if hasattr(child, "_modules") or hasattr(child, "lora_a"):
+                stack.append(child)
+            else:
+                try:
+                    stack.extend(list(child))
+                except TypeError:
+                    pass
+    return 1.0

@@ -1,0 +1,738 @@
+// libaxeng.so — runtime and C ABI: buffer table, plan executor, CUDA-graph
+// capture, NCCL data-parallel ops.  Kernels live in the other translation
+// units of this directory; this file validates each op against the buffer
+// table before anything is launched (an op that refers to a missing buffer or
+// reaches past its end is refused with a code instead of faulting the GPU).
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include <cuda_runtime.h>
+#include <nccl.h>
+
+#include "../../include/axeng.h"
+#include "kernels.h"
+
+#define API extern "C" __attribute__((visibility("default")))
+#define MAX_BUFS 65536
+#define STAGE_SLOTS 4
+
+struct Buf { void* p; long long bytes; bool owned; };
+
+struct Engine {
+    bool inited = false;
+    cudaStream_t stream = nullptr, comm_stream = nullptr;
+    cudaStream_t cur = nullptr;                 // stream the next op goes to
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    std::vector<cudaEvent_t> fork_events;       // one per FORK/JOIN inside a plan
+    size_t fork_used = 0;
+    Buf bufs[MAX_BUFS];
+    cudaGraphExec_t graph = nullptr;
+    long long graph_launches = 0;
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    int tf32 = 0, fallback = 0;
+    int* d_status = nullptr;                    // device status word
+    void* l2_flush = nullptr;                   // 256 MiB scratch written between timed repetitions
+    long long bytes = 0, launches = 0;
+    int profile = 0;
+    float prof_ms[ENG_KIND_COUNT];
+    int prof_calls[ENG_KIND_COUNT];
+    int* stage[STAGE_SLOTS] = {nullptr};        // pinned token staging ring
+    long long stage_cap[STAGE_SLOTS] = {0};
+    cudaEvent_t stage_ev[STAGE_SLOTS] = {nullptr};
+    int stage_next = 0;
+    char err[512] = {0};
+    int last_op_rc = 0;
+};
+static Engine G;
+
+static void set_err(const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt);
+    vsnprintf(G.err, sizeof(G.err), fmt, ap);
+    va_end(ap);
+}
+
+static void release_all() {
+    if (G.stream) cudaStreamSynchronize(G.stream);
+    if (G.comm_stream) cudaStreamSynchronize(G.comm_stream);
+    if (G.graph) { cudaGraphExecDestroy(G.graph); G.graph = nullptr; }
+    for (int i = 0; i < MAX_BUFS; i++) {
+        if (G.bufs[i].p && G.bufs[i].owned) cudaFree(G.bufs[i].p);
+        G.bufs[i].p = nullptr; G.bufs[i].bytes = 0; G.bufs[i].owned = false;
+    }
+    for (auto e : G.fork_events) cudaEventDestroy(e);
+    G.fork_events.clear(); G.fork_used = 0;
+    for (int i = 0; i < STAGE_SLOTS; i++) {
+        if (G.stage[i]) cudaFreeHost(G.stage[i]);
+        if (G.stage_ev[i]) cudaEventDestroy(G.stage_ev[i]);
+        G.stage[i] = nullptr; G.stage_cap[i] = 0; G.stage_ev[i] = nullptr;
+    }
+    if (G.d_status) { cudaFree(G.d_status); G.d_status = nullptr; }
+    if (G.l2_flush) { cudaFree(G.l2_flush); G.l2_flush = nullptr; }
+    if (G.comm) { ncclCommDestroy(G.comm); G.comm = nullptr; }
+    if (G.stream) { cudaStreamDestroy(G.stream); G.stream = nullptr; }
+    if (G.comm_stream) { cudaStreamDestroy(G.comm_stream); G.comm_stream = nullptr; }
+    G.bytes = 0; G.launches = 0; G.graph_launches = 0; G.inited = false;
+}
+
+API int eng_init(void) {
+    if (G.inited) release_all();
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev < 1) { set_err("no CUDA device"); return 1; }
+    if (cudaStreamCreateWithFlags(&G.stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
+    if (cudaStreamCreateWithFlags(&G.comm_stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
+    G.cur = G.stream;
+    if (cudaMalloc(&G.d_status, 64)) { set_err("status alloc failed"); return 3; }
+    cudaMemset(G.d_status, 0, 64);
+    if (ax_gemm_tc_init()) { set_err("tensor-core GEMM init failed: %s", cudaGetErrorString(cudaGetLastError())); return 4; }
+    if (ax_attn_tc_init()) { set_err("tensor-core attention init failed: %s", cudaGetErrorString(cudaGetLastError())); return 4; }
+    memset(G.prof_ms, 0, sizeof(G.prof_ms));
+    memset(G.prof_calls, 0, sizeof(G.prof_calls));
+    G.inited = true; G.rank = 0; G.world = 1; G.fallback = 0;
+    const char* fb = getenv("AXENG_FALLBACK");
+    if (fb) G.fallback = atoi(fb);
+    G.err[0] = 0;
+    return 0;
+}
+
+API int eng_shutdown(void) { release_all(); return 0; }
+API const char* eng_last_error(void) { return G.err; }
+API int eng_has_flash(void) { return 1; }
+API int eng_set_tf32(int on) { G.tf32 = on; return 0; }
+API int eng_set_fallback(int mask) { G.fallback = mask; return 0; }
+API long long eng_bytes_allocated(void) { return G.bytes; }
+API int eng_sync(void) {
+    int rc = (int)cudaStreamSynchronize(G.stream);
+    if (!rc) rc = (int)cudaStreamSynchronize(G.comm_stream);
+    return rc;
+}
+API long long eng_launch_count(int reset) {
+    long long v = G.launches;
+    if (reset) G.launches = 0;
+    return v;
+}
+
+static int alloc_common(int idx, long long nbytes, bool zero) {
+    if (!G.inited) { set_err("engine not initialised"); return 1; }
+    if (idx < 0 || idx >= MAX_BUFS) { set_err("buffer index %d out of range", idx); return 1; }
+    if (nbytes < 0) { set_err("negative size"); return 1; }
+    if (G.bufs[idx].p && G.bufs[idx].owned) { cudaFree(G.bufs[idx].p); G.bytes -= G.bufs[idx].bytes; }
+    void* p = nullptr;
+    const long long want = nbytes > 0 ? nbytes : 4;
+    if (cudaMalloc(&p, (size_t)want) != cudaSuccess) {
+        cudaGetLastError();
+        set_err("cudaMalloc(%lld bytes) failed", want);
+        return 2;
+    }
+    if (zero) cudaMemsetAsync(p, 0, (size_t)want, G.stream);
+    G.bufs[idx].p = p; G.bufs[idx].bytes = want; G.bufs[idx].owned = true;
+    G.bytes += want;
+    return 0;
+}
+API int eng_alloc(int idx, long long nelems, int elsize) { return alloc_common(idx, nelems * elsize, false); }
+API int eng_alloc_zero(int idx, long long nbytes) { return alloc_common(idx, nbytes, true); }
+API int eng_alloc_view(int idx, int parent, long long byte_offset, long long nbytes) {
+    if (idx < 0 || idx >= MAX_BUFS || parent < 0 || parent >= MAX_BUFS || !G.bufs[parent].p) { set_err("bad view"); return 1; }
+    if (byte_offset < 0 || nbytes < 0 || byte_offset + nbytes > G.bufs[parent].bytes) { set_err("view exceeds parent"); return 1; }
+    if (G.bufs[idx].p && G.bufs[idx].owned) { cudaFree(G.bufs[idx].p); G.bytes -= G.bufs[idx].bytes; }
+    G.bufs[idx].p = (char*)G.bufs[parent].p + byte_offset;
+    G.bufs[idx].bytes = nbytes; G.bufs[idx].owned = false;
+    return 0;
+}
+
+static bool have(int idx, long long bytes_needed) {
+    return idx >= 0 && idx < MAX_BUFS && G.bufs[idx].p && G.bufs[idx].bytes >= bytes_needed;
+}
+
+API int eng_upload(int idx, const float* host, long long nfloats) {
+    if (!have(idx, nfloats * 4)) { set_err("upload: buffer %d missing or smaller than %lld floats", idx, nfloats); return 110; }
+    return (int)cudaMemcpyAsync(G.bufs[idx].p, host, sizeof(float) * nfloats, cudaMemcpyHostToDevice, G.stream);
+}
+API int eng_download(int idx, float* host, long long nfloats) {
+    if (!have(idx, nfloats * 4)) { set_err("download: buffer %d missing or smaller than %lld floats", idx, nfloats); return 110; }
+    if (cudaMemcpyAsync(host, G.bufs[idx].p, sizeof(float) * nfloats, cudaMemcpyDeviceToHost, G.stream)) return 1;
+    return (int)cudaStreamSynchronize(G.stream);
+}
+API int eng_upload_raw(int idx, long long off, const void* host, long long nbytes) {
+    if (off < 0 || !have(idx, off + nbytes)) { set_err("upload_raw: out of range"); return 110; }
+    return (int)cudaMemcpyAsync((char*)G.bufs[idx].p + off, host, nbytes, cudaMemcpyHostToDevice, G.stream);
+}
+API int eng_download_raw(int idx, long long off, void* host, long long nbytes) {
+    if (off < 0 || !have(idx, off + nbytes)) { set_err("download_raw: out of range"); return 110; }
+    if (cudaMemcpyAsync(host, (char*)G.bufs[idx].p + off, nbytes, cudaMemcpyDeviceToHost, G.stream)) return 1;
+    return (int)cudaStreamSynchronize(G.stream);
+}
+// int64 host tokens -> int32 device ids through a pinned ring, so that the
+// copy is truly asynchronous and the caller's array can be reused at once.
+API int eng_upload_tokens(int idx, const long long* host, long long n, long long limit) {
+    if (!have(idx, n * 4)) { set_err("upload_tokens: buffer %d too small", idx); return 110; }
+    const int s = G.stage_next;
+    G.stage_next = (s + 1) % STAGE_SLOTS;
+    if (G.stage_cap[s] < n) {
+        if (G.stage[s]) { cudaEventSynchronize(G.stage_ev[s]); cudaFreeHost(G.stage[s]); }
+        if (cudaMallocHost(&G.stage[s], (size_t)n * 4)) { G.stage[s] = nullptr; G.stage_cap[s] = 0; set_err("pinned alloc failed"); return 2; }
+        G.stage_cap[s] = n;
+        if (!G.stage_ev[s]) cudaEventCreateWithFlags(&G.stage_ev[s], cudaEventDisableTiming);
+    } else {
+        cudaEventSynchronize(G.stage_ev[s]);
+    }
+    int* dst = G.stage[s];
+    for (long long i = 0; i < n; i++) {
+        const long long v = host[i];
+        if (v >= limit || v < -1) { set_err("token %lld at %lld outside [-1, %lld)", v, i, limit); return 3; }
+        dst[i] = (int)v;
+    }
+    int rc = (int)cudaMemcpyAsync(G.bufs[idx].p, dst, (size_t)n * 4, cudaMemcpyHostToDevice, G.stream);
+    cudaEventRecord(G.stage_ev[s], G.stream);
+    return rc;
+}
+API int eng_device_status(int clear) {
+    int v[16];
+    cudaStreamSynchronize(G.stream);
+    if (cudaMemcpy(v, G.d_status, 64, cudaMemcpyDeviceToHost)) return -1;
+    if (clear) cudaMemset(G.d_status, 0, 64);
+    return v[0];
+}
+
+// ── NCCL ────────────────────────────────────────────────────────────────────
+API int eng_nccl_id(void* out128) {
+    static_assert(sizeof(ncclUniqueId) == 128, "unique id is 128 bytes");
+    return (int)ncclGetUniqueId((ncclUniqueId*)out128);
+}
+API int eng_nccl_init_timeout(int rank, int world, const void* id128, int timeout_ms) {
+    if (!G.inited) { set_err("engine not initialised"); return 1; }
+    if (world < 1 || rank < 0 || rank >= world) { set_err("bad rank/world %d/%d", rank, world); return 8; }
+    if (G.comm) { ncclCommDestroy(G.comm); G.comm = nullptr; }
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    cfg.blocking = 0;
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    ncclResult_t r = ncclCommInitRankConfig(&G.comm, world, id, rank, &cfg);
+    if (r != ncclSuccess && r != ncclInProgress) { set_err("ncclCommInitRankConfig: %s", ncclGetErrorString(r)); G.comm = nullptr; return (int)r; }
+    const auto t0 = std::chrono::steady_clock::now();
+    ncclResult_t st = ncclInProgress;
+    while (true) {
+        if (ncclCommGetAsyncError(G.comm, &st) != ncclSuccess) { st = ncclInternalError; break; }
+        if (st != ncclInProgress) break;
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (timeout_ms > 0 && ms > timeout_ms) {
+            ncclCommAbort(G.comm); G.comm = nullptr;
+            set_err("nccl init timed out after %d ms (rank %d of %d)", timeout_ms, rank, world);
+            return 7;
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    }
+    if (st != ncclSuccess) { set_err("nccl init: %s", ncclGetErrorString(st)); ncclCommAbort(G.comm); G.comm = nullptr; return (int)st; }
+    G.rank = rank; G.world = world;
+    return 0;
+}
+API int eng_nccl_init(int rank, int world, const void* id128) {
+    return eng_nccl_init_timeout(rank, world, id128, 0);
+}
+// non-blocking communicator: wait until an enqueue call has really been issued
+static int nccl_wait(ncclResult_t r) {
+    if (r == ncclSuccess) return 0;
+    if (r != ncclInProgress) { set_err("nccl: %s", ncclGetErrorString(r)); return (int)r; }
+    ncclResult_t st = ncclInProgress;
+    const auto t0 = std::chrono::steady_clock::now();
+    while (st == ncclInProgress) {
+        if (ncclCommGetAsyncError(G.comm, &st) != ncclSuccess) return 9;
+        if (std::chrono::duration_cast<std::chrono::seconds>(std::chrono::steady_clock::now() - t0).count() > 120) {
+            set_err("nccl enqueue did not complete in 120 s");
+            return 7;
+        }
+    }
+    if (st != ncclSuccess) { set_err("nccl: %s", ncclGetErrorString(st)); return (int)st; }
+    return 0;
+}
+
+// ── op execution ────────────────────────────────────────────────────────────
+#define BUFP(i) (G.bufs[i].p)
+#define NEED(idx, nbytes)                                                              \
+    do {                                                                               \
+        if (!have((idx), (long long)(nbytes))) {                                       \
+            set_err("op kind %d: buffer %d missing or smaller than %lld bytes (has %lld)", op->kind, (idx), \
+                    (long long)(nbytes), ((idx) >= 0 && (idx) < MAX_BUFS) ? G.bufs[idx].bytes : -1LL);       \
+            return ((idx) < 0 || (idx) >= MAX_BUFS || !G.bufs[idx].p) ? 110 : 111;     \
+        }                                                                              \
+    } while (0)
+
+static inline long long esz(int dt) { return dt == 1 ? 2 : 4; }
+
+static int do_gemm(const EngOp* op, bool ex) {
+    const int dt = op->dt;
+    const bool in_bf = dt >= 1, out_bf = dt == 1;
+    const long long ei = in_bf ? 2 : 4, eo = out_bf ? 2 : 4;
+    const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
+    const float beta = op->beta;
+    const int m = op->m, n = op->n, k = op->k;
+    const int batch = op->batch > 0 ? op->batch : 1;
+    if (m < 0 || n < 0 || k < 0 || op->tb < 0 || op->tb > 2) { set_err("gemm: bad shape"); return 112; }
+    const long long a_el = (long long)m * k, b_el = (long long)k * n, c_el = (long long)m * n;
+    NEED(op->a, (op->oa + (long long)(batch - 1) * op->sa + a_el) * ei);
+    NEED(op->b, (op->ob + (long long)(batch - 1) * op->sb + b_el) * ei);
+    NEED(op->c, (op->oc + (long long)(batch - 1) * op->sc + c_el) * eo);
+    const char* A = (const char*)BUFP(op->a) + (long long)op->oa * ei;
+    const char* B = (const char*)BUFP(op->b) + (long long)op->ob * ei;
+    char* C = (char*)BUFP(op->c) + (long long)op->oc * eo;
+    const char* D = C;
+    if (ex && op->d >= 0) {
+        NEED(op->d, (op->oc + (long long)(batch - 1) * op->sc + c_el) * eo);
+        D = (const char*)BUFP(op->d) + (long long)op->oc * eo;
+    }
+    if (in_bf && batch == 1 && !(G.fallback & 1)) {
+        const int rc = ax_gemm_tc(out_bf, op->tb, A, B, C, beta != 0.f ? D : nullptr, m, n, k, alpha, beta, G.d_status, G.cur);
+        if (rc == 0) { G.launches++; return 0; }
+        if (rc > 0) { set_err("tensor-core gemm failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+    }
+    G.launches++;
+    return ax_gemm_simt(in_bf, out_bf, op->tb, A, B, C, beta != 0.f ? D : nullptr, m, n, k, batch,
+                        op->sa, op->sb, op->sc, alpha, beta, G.cur);
+}
+
+static AttnShape shape_bhtd(int B, int H, int KV, int T, int DH, float scale) {
+    AttnShape s;
+    s.B = B; s.H = H; s.KV = KV; s.T = T; s.DH = DH; s.scale = scale;
+    s.qb = (long long)H * T * DH; s.qh = (long long)T * DH; s.qt = DH;
+    s.kb = (long long)KV * T * DH; s.kh = (long long)T * DH; s.kt = DH;
+    s.db = (long long)T * H; s.dh_ = 1; s.dtk = H;      // D laid out [B,T,H] (reference ROWDOT order)
+    return s;
+}
+static AttnShape shape_bthd(int B, int H, int KV, int T, int DH, float scale) {
+    AttnShape s;
+    s.B = B; s.H = H; s.KV = KV; s.T = T; s.DH = DH; s.scale = scale;
+    s.qb = (long long)T * H * DH; s.qh = DH; s.qt = (long long)H * DH;
+    s.kb = (long long)T * KV * DH; s.kh = DH; s.kt = (long long)KV * DH;
+    s.db = (long long)T * H; s.dh_ = 1; s.dtk = H;
+    return s;
+}
+
+static int exec_op(const EngOp* op) {
+    cudaStream_t st = G.cur;
+    const int dt = op->dt;
+    const long long es = esz(dt);
+    switch (op->kind) {
+        case ENG_GEMM: case ENG_GEMM_SB: return do_gemm(op, false);
+        case ENG_GEMM_EX: return do_gemm(op, true);
+        case ENG_ADD: case ENG_MUL: case ENG_SILU_MUL: {
+            const long long n = op->n;
+            NEED(op->a, n * es); NEED(op->b, n * es); NEED(op->c, n * es);
+            G.launches++;
+            return ax_binary(op->kind == ENG_ADD ? 0 : (op->kind == ENG_MUL ? 1 : 2), dt, BUFP(op->a), BUFP(op->b), BUFP(op->c), n, st);
+        }
+        case ENG_RMSNORM: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * es); NEED(op->b, op->n * es); NEED(op->c, el * es);
+            G.launches++;
+            return ax_rmsnorm(dt, BUFP(op->a), BUFP(op->b), BUFP(op->c), op->m, op->n, op->alpha, st);
+        }
+        case ENG_ADAMW: {
+            const long long n = op->n;
+            NEED(op->a, n * 4); NEED(op->b, n * 4); NEED(op->c, n * 4); NEED(op->d, n * 4);
+            const float* tb = nullptr; void* pbf = nullptr; const float* lrb = nullptr; const float* gsb = nullptr;
+            if (op->tb >= 0) { NEED(op->tb, 4); tb = (const float*)BUFP(op->tb); }
+            if (op->sa > 0) { NEED(op->sa, n * 2); pbf = BUFP(op->sa); }
+            if (op->sb > 0) { NEED(op->sb, 4); lrb = (const float*)BUFP(op->sb); }
+            if (op->oa > 0) { NEED(op->oa, 4); gsb = (const float*)BUFP(op->oa); }
+            G.launches++;
+            return ax_adamw((float*)BUFP(op->a), (const float*)BUFP(op->b), (float*)BUFP(op->c), (float*)BUFP(op->d),
+                            tb, pbf, lrb, gsb, op->alpha, op->beta, op->gamma, n, st);
+        }
+        case ENG_SCALE: {
+            const long long n = op->n;
+            NEED(op->c, n * es);
+            if (op->alpha != 0.f) NEED(op->a, n * es);
+            G.launches++;
+            return ax_scale(dt, op->a >= 0 ? BUFP(op->a) : nullptr, BUFP(op->c), op->alpha, n, st);
+        }
+        case ENG_COPY: {
+            const long long n = op->n;
+            NEED(op->a, n * es); NEED(op->c, n * es);
+            G.launches++;
+            return ax_copy(dt, BUFP(op->a), BUFP(op->c), n, st);
+        }
+        case ENG_PERM_0213: {
+            const long long el = (long long)op->m * op->n * op->k * op->batch;
+            NEED(op->a, el * es); NEED(op->c, el * es);
+            G.launches++;
+            return ax_perm0213(dt, BUFP(op->a), BUFP(op->c), op->m, op->n, op->k, op->batch, st);
+        }
+        case ENG_ROPE: {
+            const long long rows = (long long)op->batch * op->m;
+            NEED(op->a, rows * op->n * es); NEED(op->c, rows * op->n * es);
+            NEED(op->b, (long long)op->m * (op->n / 2) * 4); NEED(op->d, (long long)op->m * (op->n / 2) * 4);
+            G.launches++;
+            return ax_rope(dt, BUFP(op->a), (const float*)BUFP(op->b), (const float*)BUFP(op->d), BUFP(op->c), op->m, op->n, rows, 1, op->tb != 0, st);
+        }
+        case ENG_ROPE_BTHD: {
+            // a=x b=cos d=sin c=out; batch=B m=T k=heads n=DH; tb=1 inverse
+            const long long rows = (long long)op->batch * op->m * op->k;
+            NEED(op->a, rows * op->n * es); NEED(op->c, rows * op->n * es);
+            NEED(op->b, (long long)op->m * (op->n / 2) * 4); NEED(op->d, (long long)op->m * (op->n / 2) * 4);
+            G.launches++;
+            return ax_rope(dt, BUFP(op->a), (const float*)BUFP(op->b), (const float*)BUFP(op->d), BUFP(op->c), op->m, op->n, rows, op->k, op->tb != 0, st);
+        }
+        case ENG_SOFTMAX_CAUSAL: {
+            const long long rows = (long long)op->batch * op->m;
+            const int width = op->n > 0 ? op->n : op->m;
+            NEED(op->a, rows * width * es); NEED(op->c, rows * width * es);
+            G.launches++;
+            return ax_softmax_causal(dt, BUFP(op->a), BUFP(op->c), op->m, width, op->k, rows, st);
+        }
+        case ENG_SOFTMAX_BWD: {
+            const long long rows = (long long)op->batch * op->m;
+            const int width = op->n > 0 ? op->n : op->m;
+            NEED(op->a, rows * width * es); NEED(op->b, rows * width * es); NEED(op->c, rows * width * es);
+            G.launches++;
+            return ax_softmax_bwd(dt, BUFP(op->a), BUFP(op->b), BUFP(op->c), width, rows, st);
+        }
+        case ENG_REPEAT_KV: case ENG_REPEAT_KV_BWD: {
+            // batch=B, tb=KV, n=H, m=T, k=dh
+            const long long big = (long long)op->batch * op->n * op->m * op->k, small = (long long)op->batch * op->tb * op->m * op->k;
+            if (op->tb <= 0 || op->n % op->tb) { set_err("repeat_kv: H %% KV != 0"); return 112; }
+            G.launches++;
+            if (op->kind == ENG_REPEAT_KV) {
+                NEED(op->a, small * es); NEED(op->c, big * es);
+                return ax_repeat_kv(dt, BUFP(op->a), BUFP(op->c), op->batch, op->tb, op->n, op->m, op->k, st);
+            }
+            NEED(op->a, big * es); NEED(op->c, small * es);
+            return ax_repeat_kv_bwd(dt, BUFP(op->a), BUFP(op->c), op->batch, op->tb, op->n, op->m, op->k, st);
+        }
+        case ENG_RMSNORM_BWD: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * es); NEED(op->b, op->n * es); NEED(op->d, el * es); NEED(op->c, el * es); NEED(op->tb, el * es);
+            G.launches++;
+            return ax_rmsnorm_bwd(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), BUFP(op->tb), op->m, op->n, op->alpha, st);
+        }
+        case ENG_COLSUM: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->c, (long long)op->n * 4);
+            G.launches++;
+            return ax_colsum(dt, BUFP(op->a), (float*)BUFP(op->c), op->m, op->n, st);
+        }
+        case ENG_RMSNORM_BWD_ACC: {
+            // a=x b=w d=g c=dx; tb=residual (<=0 none); sa=dw fp32 (<=0 none); sb=scratch; m=N n=D; alpha=eps
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * es); NEED(op->b, op->n * es); NEED(op->d, el * es); NEED(op->c, el * es);
+            const void* res = nullptr; float* dw = nullptr; float* scr = nullptr;
+            if (op->tb > 0) { NEED(op->tb, el * es); res = BUFP(op->tb); }
+            if (op->sa > 0) {
+                NEED(op->sa, (long long)op->n * 4); dw = (float*)BUFP(op->sa);
+                NEED(op->sb, ax_rmsnorm_bwd_acc_scratch(op->n)); scr = (float*)BUFP(op->sb);
+            }
+            G.launches += dw ? 2 : 1;
+            return ax_rmsnorm_bwd_acc(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), res, BUFP(op->c), dw, scr, op->m, op->n, op->alpha, st);
+        }
+        case ENG_SILU_BWD: {
+            const long long n = op->n;
+            NEED(op->a, n * es); NEED(op->b, n * es); NEED(op->d, n * es); NEED(op->c, n * es); NEED(op->tb, n * es);
+            G.launches++;
+            return ax_silu_bwd(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), BUFP(op->tb), n, st);
+        }
+        case ENG_EMBED: case ENG_EMBED_I32: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->b, (long long)op->m * 4); NEED(op->c, el * es); NEED(op->a, (long long)op->n * es);
+            G.launches++;
+            return ax_embed(dt, BUFP(op->a), BUFP(op->b), op->kind == ENG_EMBED_I32, BUFP(op->c), op->m, op->n, st);
+        }
+        case ENG_EMBED_BWD: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->b, (long long)op->m * 4); NEED(op->c, (long long)op->n * 4);
+            G.launches++;
+            return ax_embed_bwd_atomic(dt >= 1, BUFP(op->a), (const float*)BUFP(op->b), (float*)BUFP(op->c), op->m, op->n, st);
+        }
+        case ENG_EMBED_BWD_DET: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->b, (long long)op->m * 4); NEED(op->c, (long long)op->n * 4);
+            G.launches++;
+            return ax_embed_bwd_det(dt, BUFP(op->a), (const int*)BUFP(op->b), (float*)BUFP(op->c), op->m, op->n, st);
+        }
+        case ENG_COUNTVALID:
+            NEED(op->a, (long long)op->m * 4); NEED(op->c, 4);
+            G.launches++;
+            return ax_countvalid((const float*)BUFP(op->a), (float*)BUFP(op->c), op->m, st);
+        case ENG_CE: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * es); NEED(op->b, (long long)op->m * 4); NEED(op->c, el * es); NEED(op->d, 4);
+            const float* den = nullptr;
+            if (op->sa > 0) { NEED(op->sa, 4); den = (const float*)BUFP(op->sa); }
+            G.launches++;
+            return ax_ce(dt, BUFP(op->a), (const float*)BUFP(op->b), BUFP(op->c), (float*)BUFP(op->d), den, op->m, op->n, st);
+        }
+        case ENG_CE_FUSED: {
+            // a=logits b=targets(int32) c=dlogits d=loss; sa=denom; sb=scratch (N+8 floats); m=N n=V
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * es); NEED(op->b, (long long)op->m * 4); NEED(op->c, el * es); NEED(op->d, 4);
+            NEED(op->sa, 4); NEED(op->sb, ((long long)op->m + 8) * 4);
+            G.launches += 2;
+            return ax_ce_fused(dt, BUFP(op->a), (const int*)BUFP(op->b), BUFP(op->c), (float*)BUFP(op->d),
+                               (float*)BUFP(op->sa), (float*)BUFP(op->sb), op->m, op->n, st);
+        }
+        case ENG_TICK:
+            NEED(op->a, 4);
+            G.launches++;
+            return ax_tick((float*)BUFP(op->a), st);
+        case ENG_CAST: {
+            const long long n = (long long)op->m * (op->n > 0 ? op->n : 1);
+            NEED(op->a, n * (op->tb == 0 ? 4 : 2)); NEED(op->c, n * (op->tb == 0 ? 2 : 4));
+            G.launches++;
+            return ax_cast(op->tb != 0, BUFP(op->a), BUFP(op->c), n, st);
+        }
+        case ENG_ROWDOT: {
+            const long long el = (long long)op->m * op->n;
+            NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->b, el * (dt >= 1 ? 2 : 4)); NEED(op->c, (long long)op->m * 4);
+            G.launches++;
+            return ax_rowdot(dt, BUFP(op->a), BUFP(op->b), (float*)BUFP(op->c), op->m, op->n, st);
+        }
+        case ENG_FLASH: {
+            // a=q b=k d=v c=o [B,H|KV,T,DH]; m=T n=DH k=KV batch=B tb=H; sa=lse (0 none); alpha=scale
+            if (dt != 1 || op->n % 16 || op->n > 128) { set_err("flash: needs bf16, head_dim %% 16 == 0, <= 128"); return 101; }
+            const int T = op->m, DH = op->n, KV = op->k, B = op->batch, H = op->tb;
+            if (KV <= 0 || H % KV) { set_err("flash: H %% KV != 0"); return 101; }
+            NEED(op->a, (long long)B * H * T * DH * 2); NEED(op->c, (long long)B * H * T * DH * 2);
+            NEED(op->b, (long long)B * KV * T * DH * 2); NEED(op->d, (long long)B * KV * T * DH * 2);
+            float* lse = nullptr;
+            if (op->sa > 0) { NEED(op->sa, (long long)B * H * T * 4); lse = (float*)BUFP(op->sa); }
+            AttnShape s = shape_bhtd(B, H, KV, T, DH, op->alpha);
+            G.launches++;
+            if (!(G.fallback & 2)) {
+                const int rc = ax_attn_fwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), lse, s, G.d_status, st);
+                if (rc == 0) return 0;
+                if (rc > 0) return rc;
+            }
+            return ax_attn_fwd_simt(1, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), lse, s, st);
+        }
+        case ENG_FLASH_BWD: {
+            // a=q b=k d=v c=dO; sa=lse sb=D[B,T,H] tb=dq sc=dk oa=dv (fp32) ob=H; m=T n=DH k=KV batch=B
+            if (dt != 1 || op->n % 16 || op->n > 128) { set_err("flash_bwd: needs bf16, head_dim %% 16 == 0, <= 128"); return 102; }
+            const int T = op->m, DH = op->n, KV = op->k, B = op->batch, H = op->ob;
+            if (KV <= 0 || H <= 0 || H % KV) { set_err("flash_bwd: H %% KV != 0"); return 102; }
+            const long long qe = (long long)B * H * T * DH, ke = (long long)B * KV * T * DH;
+            NEED(op->a, qe * 2); NEED(op->c, qe * 2); NEED(op->b, ke * 2); NEED(op->d, ke * 2);
+            NEED(op->sa, (long long)B * H * T * 4); NEED(op->sb, (long long)B * H * T * 4);
+            NEED(op->tb, qe * 4); NEED(op->sc, ke * 4); NEED(op->oa, ke * 4);
+            AttnShape s = shape_bhtd(B, H, KV, T, DH, op->alpha);
+            G.launches += 2;
+            // the reference accumulates into pre-zeroed fp32 buffers; writing the full
+            // sums gives the same result without atomics
+            return ax_attn_bwd_simt(1, 0, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (const float*)BUFP(op->sa),
+                                    (const float*)BUFP(op->sb), BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, st);
+        }
+        case ENG_ATTN_FWD: {
+            // a=q [B,T,H,DH] b=k d=v [B,T,KV,DH] c=o; sa=lse [B,H,T]; m=T n=DH k=KV batch=B tb=H; alpha=scale
+            const int T = op->m, DH = op->n, KV = op->k, B = op->batch, H = op->tb;
+            if (KV <= 0 || H <= 0 || H % KV) { set_err("attn: H %% KV != 0"); return 101; }
+            NEED(op->a, (long long)B * H * T * DH * es); NEED(op->c, (long long)B * H * T * DH * es);
+            NEED(op->b, (long long)B * KV * T * DH * es); NEED(op->d, (long long)B * KV * T * DH * es);
+            NEED(op->sa, (long long)B * H * T * 4);
+            AttnShape s = shape_bthd(B, H, KV, T, DH, op->alpha);
+            G.launches++;
+            if (dt == 1 && !(G.fallback & 2)) {
+                const int rc = ax_attn_fwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (float*)BUFP(op->sa), s, G.d_status, st);
+                if (rc == 0) return 0;
+                if (rc > 0) return rc;
+            }
+            return ax_attn_fwd_simt(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (float*)BUFP(op->sa), s, st);
+        }
+        case ENG_ATTN_BWD: {
+            // a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=D scratch [B,T,H] fp32
+            const int T = op->m, DH = op->n, KV = op->k, B = op->batch, H = op->ob;
+            if (KV <= 0 || H <= 0 || H % KV) { set_err("attn_bwd: H %% KV != 0"); return 102; }
+            const long long qe = (long long)B * H * T * DH, ke = (long long)B * KV * T * DH;
+            NEED(op->a, qe * es); NEED(op->c, qe * es); NEED(op->sb, qe * es); NEED(op->b, ke * es); NEED(op->d, ke * es);
+            NEED(op->sa, (long long)B * H * T * 4); NEED(op->oc, (long long)B * H * T * 4);
+            NEED(op->tb, qe * es); NEED(op->sc, ke * es); NEED(op->oa, ke * es);
+            AttnShape s = shape_bthd(B, H, KV, T, DH, op->alpha);
+            if (dt == 1 && !(G.fallback & 2)) {
+                const int rc = ax_attn_bwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->sb), BUFP(op->c), (const float*)BUFP(op->sa),
+                                              (float*)BUFP(op->oc), BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, G.d_status, st);
+                if (rc == 0) { G.launches += 2; return 0; }
+                if (rc > 0) return rc;
+            }
+            G.launches += 3;
+            int rc = ax_rowdot(dt, BUFP(op->c), BUFP(op->sb), (float*)BUFP(op->oc), (long long)B * T * H, DH, st);
+            if (rc) return rc;
+            return ax_attn_bwd_simt(dt, dt == 1 ? 1 : 0, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (const float*)BUFP(op->sa),
+                                    (const float*)BUFP(op->oc), BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, st);
+        }
+        case ENG_L2ACC:
+            NEED(op->a, (long long)op->n * 4); NEED(op->c, 4);
+            G.launches++;
+            return ax_l2acc((const float*)BUFP(op->a), (float*)BUFP(op->c), op->n, st);
+        case ENG_CLIPSCALE:
+            NEED(op->a, 4); NEED(op->c, 4);
+            G.launches++;
+            return ax_clipscale((const float*)BUFP(op->a), (float*)BUFP(op->c), op->alpha, st);
+        case ENG_GNORM_FLAT: {
+            // a=grad arena, c=partials scratch, m=chunks (AX_ADAMW_CHUNK elements each), oa=chunk offset in a,
+            // d=scalar out buffer with index ob, tb=step counter to tick (<=0 none)
+            const long long n = (long long)op->m * AX_ADAMW_CHUNK, off = (long long)op->oa * AX_ADAMW_CHUNK;
+            const long long np = (n + AX_GNORM_CHUNK - 1) / AX_GNORM_CHUNK;
+            NEED(op->a, (off + n) * 4); NEED(op->c, (np > 0 ? np : 1) * 4); NEED(op->d, ((long long)op->ob + 1) * 4);
+            float* tick = nullptr;
+            if (op->tb > 0) { NEED(op->tb, 4); tick = (float*)BUFP(op->tb); }
+            G.launches += 2;
+            return ax_gnorm_flat((const float*)BUFP(op->a) + off, (float*)BUFP(op->c), n, tick, (float*)BUFP(op->d) + op->ob, st);
+        }
+        case ENG_ADAMW_FLAT: {
+            // a=master b=grad c=m d=v (a,c,d segment-local; b, mirror and flags offset by k chunks);
+            // sa=bf16 mirror (<=0 none) sb=lr tb=t sc=decay flags oa=partials ob=#partials oc=norm out (<=0 none)
+            const long long n = (long long)op->m * AX_ADAMW_CHUNK, off = (long long)op->k * AX_ADAMW_CHUNK;
+            NEED(op->a, n * 4); NEED(op->c, n * 4); NEED(op->d, n * 4); NEED(op->b, (off + n) * 4);
+            NEED(op->sb, 4); NEED(op->tb, 4); NEED(op->sc, (long long)op->k + op->m);
+            void* pbf = nullptr; float* gout = nullptr; const float* parts = nullptr;
+            if (op->sa > 0) { NEED(op->sa, (off + n) * 2); pbf = (char*)BUFP(op->sa) + off * 2; }
+            if (op->ob > 0) { NEED(op->oa, (long long)op->ob * 4); parts = (const float*)BUFP(op->oa); }
+            if (op->oc > 0) { NEED(op->oc, 4); gout = (float*)BUFP(op->oc); }
+            G.launches++;
+            return ax_adamw_flat((float*)BUFP(op->a), (const float*)BUFP(op->b) + off, (float*)BUFP(op->c), (float*)BUFP(op->d),
+                                 pbf, (const unsigned char*)BUFP(op->sc) + op->k, (const float*)BUFP(op->tb), (const float*)BUFP(op->sb),
+                                 parts, op->ob > 0 ? op->ob : 0, gout, op->alpha, op->beta, op->gamma, n, st);
+        }
+        // ── collectives ──
+        case ENG_ALLREDUCE: case ENG_REDUCE: case ENG_BROADCAST: {
+            // n = element count, or (m chunks of AX_ADAMW_CHUNK elements at chunk offset oa) when m > 0
+            if (!G.comm) { set_err("collective before nccl_init"); return 104; }
+            const bool half = op->kind == ENG_BROADCAST && dt == 1;
+            const long long e = half ? 2 : 4;
+            const long long cnt = op->m > 0 ? (long long)op->m * AX_ADAMW_CHUNK : op->n;
+            const long long off = op->m > 0 ? (long long)op->oa * AX_ADAMW_CHUNK : 0;
+            NEED(op->a, (off + cnt) * e);
+            char* p = (char*)BUFP(op->a) + off * e;
+            G.launches++;
+            if (op->kind == ENG_ALLREDUCE) return nccl_wait(ncclAllReduce(p, p, cnt, ncclFloat, ncclAvg, G.comm, st));
+            if (op->tb < 0 || op->tb >= G.world) { set_err("collective root %d outside world %d", op->tb, G.world); return 112; }
+            if (op->kind == ENG_REDUCE) return nccl_wait(ncclReduce(p, p, cnt, ncclFloat, ncclAvg, op->tb, G.comm, st));
+            return nccl_wait(ncclBroadcast(p, p, cnt, half ? ncclBfloat16 : ncclFloat, op->tb, G.comm, st));
+        }
+        case ENG_ALLGATHER_F32: {
+            if (!G.comm) { set_err("collective before nccl_init"); return 104; }
+            NEED(op->a, (long long)(op->oa + op->n) * 4); NEED(op->c, (long long)op->n * G.world * 4);
+            G.launches++;
+            return nccl_wait(ncclAllGather((const float*)BUFP(op->a) + op->oa, BUFP(op->c), op->n, ncclFloat, G.comm, st));
+        }
+        case ENG_GROUP:
+            if (!G.comm) { set_err("group before nccl_init"); return 104; }
+            return op->tb ? nccl_wait(ncclGroupEnd()) : nccl_wait(ncclGroupStart());
+        case ENG_FORK: case ENG_JOIN: {
+            // FORK: the comm stream waits for everything queued on the main stream so far.
+            // JOIN: the main stream waits for everything queued on the comm stream so far.
+            if (G.fork_used >= G.fork_events.size()) {
+                cudaEvent_t e;
+                if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming)) return 113;
+                G.fork_events.push_back(e);
+            }
+            cudaEvent_t e = G.fork_events[G.fork_used++];
+            cudaStream_t from = op->kind == ENG_FORK ? G.stream : G.comm_stream;
+            cudaStream_t to = op->kind == ENG_FORK ? G.comm_stream : G.stream;
+            if (cudaEventRecord(e, from)) return 113;
+            if (cudaStreamWaitEvent(to, e, 0)) return 113;
+            return 0;
+        }
+        case ENG_STREAM:
+            G.cur = op->tb ? G.comm_stream : G.stream;
+            return 0;
+        default:
+            set_err("unknown op kind %d", op->kind);
+            return 100;
+    }
+}
+
+static int run_ops(const EngOp* ops, int n_ops) {
+    G.fork_used = 0;
+    G.cur = G.stream;
+    for (int i = 0; i < n_ops; i++) {
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        const bool prof = G.profile && ops[i].kind >= 0 && ops[i].kind < ENG_KIND_COUNT &&
+                          ops[i].kind != ENG_GROUP && ops[i].kind != ENG_STREAM && ops[i].kind != ENG_FORK && ops[i].kind != ENG_JOIN;
+        if (prof) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, G.cur); }
+        int rc = exec_op(&ops[i]);
+        if (!rc) {
+            cudaError_t ce = cudaPeekAtLastError();
+            if (ce != cudaSuccess) { set_err("op %d (kind %d): %s", i, ops[i].kind, cudaGetErrorString(ce)); cudaGetLastError(); rc = 130; }
+        }
+        if (prof) {
+            cudaEventRecord(e1, G.cur); cudaEventSynchronize(e1);
+            float ms = 0.f; cudaEventElapsedTime(&ms, e0, e1);
+            G.prof_ms[ops[i].kind] += ms; G.prof_calls[ops[i].kind]++;
+            cudaEventDestroy(e0); cudaEventDestroy(e1);
+        }
+        if (rc) { G.last_op_rc = rc; G.cur = G.stream; return 1000 + i; }
+    }
+    G.cur = G.stream;
+    return 0;
+}
+
+API int eng_run_plan(const EngOp* ops, int n_ops, int sync) {
+    if (!G.inited) { set_err("engine not initialised"); return 1; }
+    int rc = run_ops(ops, n_ops);
+    if (rc) return rc;
+    return sync ? eng_sync() : 0;
+}
+
+API int eng_capture_plan(const EngOp* ops, int n_ops) {
+    if (!G.inited) { set_err("engine not initialised"); return 1; }
+    if (G.graph) { cudaGraphExecDestroy(G.graph); G.graph = nullptr; }
+    eng_sync();
+    const int prof = G.profile; G.profile = 0;
+    if (cudaStreamBeginCapture(G.stream, cudaStreamCaptureModeThreadLocal)) { G.profile = prof; set_err("begin capture failed"); return 1; }
+    const long long before = G.launches;
+    int rc = run_ops(ops, n_ops);
+    G.profile = prof;
+    cudaGraph_t graph = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(G.stream, &graph);
+    G.graph_launches = G.launches - before;
+    G.launches = before;
+    if (rc) { if (graph) cudaGraphDestroy(graph); cudaGetLastError(); return rc; }
+    if (ce != cudaSuccess) { set_err("end capture: %s", cudaGetErrorString(ce)); cudaGetLastError(); return 2; }
+    ce = cudaGraphInstantiate(&G.graph, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) { set_err("instantiate: %s", cudaGetErrorString(ce)); cudaGetLastError(); G.graph = nullptr; return 3; }
+    return 0;
+}
+
+API int eng_replay(int times, int sync) {
+    if (!G.graph) { set_err("no captured plan"); return 1; }
+    for (int i = 0; i < times; i++) {
+        if (cudaGraphLaunch(G.graph, G.stream)) { set_err("graph launch failed: %s", cudaGetErrorString(cudaGetLastError())); return 2; }
+        G.launches += G.graph_launches;
+    }
+    return sync ? eng_sync() : 0;
+}
+
+API int eng_time_plan(const EngOp* ops, int n_ops, int reps, int flush_l2, float* ms_out) {
+    if (!G.inited) return 1;
+    if (reps < 1) reps = 1;
+    const size_t FL = 256u << 20;
+    if (flush_l2 && !G.l2_flush && cudaMalloc(&G.l2_flush, FL)) { G.l2_flush = nullptr; cudaGetLastError(); set_err("flush buffer alloc failed"); return 2; }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    double total = 0.0;
+    int rc = 0;
+    for (int r = 0; r < reps && !rc; r++) {
+        if (flush_l2) cudaMemsetAsync(G.l2_flush, r & 0xff, FL, G.stream);
+        cudaEventRecord(e0, G.stream);
+        rc = run_ops(ops, n_ops);
+        cudaEventRecord(e1, G.stream);
+        if (cudaEventSynchronize(e1)) rc = rc ? rc : 130;
+        float ms = 0.f; cudaEventElapsedTime(&ms, e0, e1);
+        total += ms;
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (ms_out) *ms_out = (float)(total / reps);
+    return rc;
+}
+
+API int eng_profile(int on) {
+    G.profile = on;
+    if (on) { memset(G.prof_ms, 0, sizeof(G.prof_ms)); memset(G.prof_calls, 0, sizeof(G.prof_calls)); }
+    return 0;
+}
+API int eng_profile_read(float* ms, int* calls, int n) {
+    for (int i = 0; i < n && i < ENG_KIND_COUNT; i++) { ms[i] = G.prof_ms[i]; calls[i] = G.prof_calls[i]; }
+    return 0;
+}

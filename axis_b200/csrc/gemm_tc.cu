@@ -1,0 +1,300 @@
+// bf16 GEMM on the 5th-generation tensor cores: TMA-fed shared-memory stages,
+// tcgen05.mma with fp32 accumulators in TMEM, double-buffered accumulators so
+// that the epilogue of one tile overlaps the main loop of the next.
+//
+//   C[m,n] = alpha * op(A) op(B) + beta * D          (fp32 accumulate)
+//   tb = 0: A [m,k] (K-major),  B [k,n] (N-major)      forward  y = x W
+//   tb = 1: A [m,k] (K-major),  B [n,k] (K-major)      dX = g W^T, logits = x E^T
+//   tb = 2: A [k,m] (M-major),  B [k,n] (N-major)      dW = x^T g   (fp32 out)
+//
+// One persistent CTA per SM, 192 threads: warp 0 lane 0 issues TMA loads,
+// warp 1 lane 0 issues the MMAs, warps 2..5 read TMEM and write C.  Tile
+// 128 x BN x 64 with BN = 128 or 256.  All barrier waits are bounded.
+#include <cuda_bf16.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "tc_common.cuh"
+
+#define BM 128
+#define BK 64
+#define GEMM_THREADS 192
+#define STAT_GEMM 0x100
+
+// ── host helpers shared with the attention kernels ──────────────────────────
+static PFN_tmapEncodeTiled g_encode = nullptr;
+PFN_tmapEncodeTiled tc_encode_fn() {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return nullptr;
+        g_encode = (PFN_tmapEncodeTiled)fn;
+    }
+    return g_encode;
+}
+int tc_make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box, bool swizzle128) {
+    PFN_tmapEncodeTiled enc = tc_encode_fn();
+    if (!enc) return 1;
+    cuuint64_t gd[5]; cuuint64_t gs[4]; cuuint32_t bx[5]; cuuint32_t es[5];
+    for (int i = 0; i < rank; i++) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+    for (int i = 0; i + 1 < rank; i++) gs[i] = strides_bytes[i];
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gd, gs, bx, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+template <int BN> struct GemmCfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;                 // two accumulators
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <typename TO> __device__ __forceinline__ void epi_store(TO* crow, const TO* drow, const uint32_t* acc, int col0,
+                                                                  int ncols_valid, float alpha, float beta, bool vec_ok);
+template <> __device__ __forceinline__ void epi_store<bf16>(bf16* crow, const bf16* drow, const uint32_t* acc, int col0,
+                                                            int nvalid, float alpha, float beta, bool vec_ok) {
+    if (vec_ok && nvalid >= 32) {
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            float f[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) f[q] = alpha * __uint_as_float(acc[v * 8 + q]);
+            if (drow) {
+                float d[8];
+                Vec<bf16>::ld(drow + col0 + v * 8, d);
+#pragma unroll
+                for (int q = 0; q < 8; q++) f[q] += beta * d[q];
+            }
+            Vec<bf16>::st(crow + col0 + v * 8, f);
+        }
+    } else {
+        for (int q = 0; q < 32 && q < nvalid; q++) {
+            float f = alpha * __uint_as_float(acc[q]);
+            if (drow) f += beta * __bfloat162float(drow[col0 + q]);
+            crow[col0 + q] = __float2bfloat16(f);
+        }
+    }
+}
+template <> __device__ __forceinline__ void epi_store<float>(float* crow, const float* drow, const uint32_t* acc, int col0,
+                                                             int nvalid, float alpha, float beta, bool vec_ok) {
+    if (vec_ok && nvalid >= 32) {
+#pragma unroll
+        for (int v = 0; v < 8; v++) {
+            float f[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) f[q] = alpha * __uint_as_float(acc[v * 4 + q]);
+            if (drow) {
+                float d[4];
+                Vec<float>::ld(drow + col0 + v * 4, d);
+#pragma unroll
+                for (int q = 0; q < 4; q++) f[q] += beta * d[q];
+            }
+            Vec<float>::st(crow + col0 + v * 4, f);
+        }
+    } else {
+        for (int q = 0; q < 32 && q < nvalid; q++) {
+            float f = alpha * __uint_as_float(acc[q]);
+            if (drow) f += beta * drow[col0 + q];
+            crow[col0 + q] = f;
+        }
+    }
+}
+
+// A_MN / B_MN: 1 when that operand is MN-major in global memory (see header).
+template <int BN, int A_MN, int B_MN, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+          TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem base word, abort flag
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t smem_base = smem_u32(smem);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kblocks = (k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 128); }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ── TMA producer ──
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            for (int kb = 0; kb < kblocks; kb++, it++) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (it >= (uint32_t)STAGES && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
+                if (*abort_flag) { ok = false; break; }
+                const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+                mbar_expect_tx(bar_full + 8 * s, Cfg::STAGE_BYTES);
+                if (A_MN) {     // A [k, m]: boxes of 64 (m) x 64 (k)
+#pragma unroll
+                    for (int b = 0; b < BM / 64; b++) tma_load_2d(sa + b * 8192, &tmA, bar_full + 8 * s, tm * BM + b * 64, kb * BK);
+                } else {        // A [m, k]: one box 64 (k) x 128 (m)
+                    tma_load_2d(sa, &tmA, bar_full + 8 * s, kb * BK, tm * BM);
+                }
+                if (B_MN) {     // B [k, n]: boxes of 64 (n) x 64 (k)
+#pragma unroll
+                    for (int b = 0; b < BN / 64; b++) tma_load_2d(sb + b * 8192, &tmB, bar_full + 8 * s, tn * BN + b * 64, kb * BK);
+                } else {        // B [n, k]: one box 64 (k) x BN (n)
+                    tma_load_2d(sb, &tmB, bar_full + 8 * s, kb * BK, tn * BN);
+                }
+            }
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(status, STAT_GEMM | 1); }
+        // before leaving, wait (bounded) for every load this thread issued
+        const uint32_t issued = it;
+        for (uint32_t j = (issued > (uint32_t)STAGES ? issued - STAGES : 0); j < issued; j++)
+            mbar_wait(bar_full + 8 * (j % STAGES), (j / STAGES) & 1);
+    } else if (warp == 1 && lane == 0) {
+        // ── MMA issuer ──
+        constexpr uint32_t idesc = tc_idesc_bf16(BM, BN, A_MN, B_MN);
+        uint32_t it = 0, tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+            const int acc = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            if (tcount >= 2 && !mbar_wait(bar_tempty + 8 * acc, aph ^ 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (int kb = 0; kb < kblocks; kb++, it++) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(bar_full + 8 * s, ph) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES, sb = sa + Cfg::A_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; kk++) {
+                    // K-major: 16 k-elements = 32 bytes inside the 128-byte row; MN-major: 16 k-rows = 2048 bytes
+                    const uint64_t ad = A_MN ? tc_smem_desc(sa + kk * 2048, 8192, 1024) : tc_smem_desc(sa + kk * 32, 16, 1024);
+                    const uint64_t bd = B_MN ? tc_smem_desc(sb + kk * 2048, 8192, 1024) : tc_smem_desc(sb + kk * 32, 16, 1024);
+                    tc_mma_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+                }
+                tc_commit(bar_empty + 8 * s);          // frees the stage when these MMAs finish
+            }
+            if (ok) tc_commit(bar_tfull + 8 * acc);    // accumulator complete
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(status, STAT_GEMM | 2); }
+    } else if (warp >= 2) {
+        // ── epilogue: TMEM -> registers -> global ──
+        const int quad = warp & 3;                     // TMEM lane quadrant this warp may read
+        uint32_t tcount = 0;
+        bool ok = true;
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (n % (16 / (int)sizeof(TO))) == 0 &&
+                            (!D || (reinterpret_cast<uintptr_t>(D) & 15) == 0);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const int acc = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            if (!mbar_wait(bar_tfull + 8 * acc, aph) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+            const int row = tm * BM + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+            TO* crow = C + (long long)row * n;
+            const TO* drow = (D && beta != 0.f) ? D + (long long)row * n : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                tmem_ld_wait();
+                const int col0 = tn * BN + c;
+                if (row < m && col0 < n) epi_store<TO>(crow, drow, r, col0, n - col0, alpha, beta, vec_ok);
+            }
+            tc_fence_before();
+            mbar_arrive(bar_tempty + 8 * acc);
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_GEMM | 3); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
+}
+
+template <int BN, int A_MN, int B_MN, typename TO>
+static int gemm_set_attr() {
+    return (int)cudaFuncSetAttribute(k_gemm_tc<BN, A_MN, B_MN, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM);
+}
+int ax_gemm_tc_init(void) {
+    if (!tc_encode_fn()) return 1;
+    int rc = 0;
+    rc |= gemm_set_attr<128, 0, 1, bf16>(); rc |= gemm_set_attr<256, 0, 1, bf16>();
+    rc |= gemm_set_attr<128, 0, 0, bf16>(); rc |= gemm_set_attr<256, 0, 0, bf16>();
+    rc |= gemm_set_attr<128, 1, 1, bf16>(); rc |= gemm_set_attr<256, 1, 1, bf16>();
+    rc |= gemm_set_attr<128, 0, 1, float>(); rc |= gemm_set_attr<256, 0, 1, float>();
+    rc |= gemm_set_attr<128, 0, 0, float>(); rc |= gemm_set_attr<256, 0, 0, float>();
+    rc |= gemm_set_attr<128, 1, 1, float>(); rc |= gemm_set_attr<256, 1, 1, float>();
+    return rc;
+}
+
+template <int BN, int A_MN, int B_MN, typename TO>
+static int gemm_launch(const void* A, const void* B, void* C, const void* D, int m, int n, int k,
+                       float alpha, float beta, int* status, cudaStream_t st) {
+    CUtensorMap tmA, tmB;
+    {
+        // A: K-major [m,k] -> dims {k, m}, box {64, 128};  M-major [k,m] -> dims {m, k}, box {64, 64}
+        uint64_t dims[2], strides[1]; uint32_t box[2];
+        if (A_MN) { dims[0] = m; dims[1] = k; strides[0] = (uint64_t)m * 2; box[0] = 64; box[1] = BK; }
+        else { dims[0] = k; dims[1] = m; strides[0] = (uint64_t)k * 2; box[0] = BK; box[1] = BM; }
+        if (tc_make_tmap_bf16(&tmA, A, 2, dims, strides, box, true)) return 2;
+        // B: N-major [k,n] -> dims {n, k}, box {64, 64};  K-major [n,k] -> dims {k, n}, box {64, BN}
+        if (B_MN) { dims[0] = n; dims[1] = k; strides[0] = (uint64_t)n * 2; box[0] = 64; box[1] = BK; }
+        else { dims[0] = k; dims[1] = n; strides[0] = (uint64_t)k * 2; box[0] = BK; box[1] = BN; }
+        if (tc_make_tmap_bf16(&tmB, B, 2, dims, strides, box, true)) return 2;
+    }
+    const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const int grid = tiles < AX_SMS ? tiles : AX_SMS;
+    k_gemm_tc<BN, A_MN, B_MN, TO><<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM, st>>>(tmA, tmB, (TO*)C, (const TO*)D, m, n, k, alpha, beta, status);
+    return 0;
+}
+
+int ax_gemm_tc(int out_bf16, int tb, const void* A, const void* B, void* C, const void* D,
+               int m, int n, int k, float alpha, float beta, int* status, cudaStream_t st) {
+    // shapes the TMA path serves: 16-byte aligned bases and row pitches, and at
+    // least one full box in every dimension
+    if (!aligned16(A) || !aligned16(B)) return -1;
+    if (m < BM || n < 128 || k < BK) return -1;
+    if (tb == 0) { if (k % 8 || n % 8) return -1; }
+    else if (tb == 1) { if (k % 8) return -1; }
+    else { if (m % 8 || n % 8) return -1; }
+    // BN = 256 when it does not leave SMs idle compared with 128
+    const long long t256 = (long long)((m + BM - 1) / BM) * ((n + 255) / 256);
+    const long long t128 = (long long)((m + BM - 1) / BM) * ((n + 127) / 128);
+    auto waves = [](long long t) { return (t + AX_SMS - 1) / AX_SMS; };
+    // a 256-wide tile costs two 128-wide ones; prefer it on ties (fewer smem reads per flop)
+    const bool use256 = n >= 256 && waves(t256) * 2 <= waves(t128);
+#define GL(BN_, AM, BMj)                                                                                       \
+    (out_bf16 ? gemm_launch<BN_, AM, BMj, bf16>(A, B, C, D, m, n, k, alpha, beta, status, st)                \
+              : gemm_launch<BN_, AM, BMj, float>(A, B, C, D, m, n, k, alpha, beta, status, st))
+    if (tb == 0) return use256 ? GL(256, 0, 1) : GL(128, 0, 1);
+    if (tb == 1) return use256 ? GL(256, 0, 0) : GL(128, 0, 0);
+    return use256 ? GL(256, 1, 1) : GL(128, 1, 1);
+#undef GL
+}

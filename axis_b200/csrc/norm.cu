@@ -1,0 +1,221 @@
+// RMSNorm forward/backward.  HBM-bound: each row is read once from DRAM (the
+// second sweep of a row hits L1/L2) and written once; reductions are warp
+// shuffles + one shared-memory hop; fp32 math on fp32 or bf16 storage.
+#include "common.cuh"
+#include "kernels.h"
+
+// y = x * rsqrt(mean(x^2) + eps) * w          (one block per row, grid-strided)
+template <typename T, bool VEC>
+__global__ void k_rmsnorm(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ o,
+                          int rows, int dim, float eps) {
+    __shared__ float sh[40];
+    constexpr int N = Vec<T>::N;
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* xr = x + (long long)r * dim;
+        T* orow = o + (long long)r * dim;
+        float acc = 0.f;
+        if (VEC) {
+            for (int j = threadIdx.x * N; j < dim; j += blockDim.x * N) {
+                float f[N];
+                Vec<T>::ld(xr + j, f);
+#pragma unroll
+                for (int q = 0; q < N; q++) acc += f[q] * f[q];
+            }
+        } else {
+            for (int j = threadIdx.x; j < dim; j += blockDim.x) { float v = ldf(xr, j); acc += v * v; }
+        }
+        const float inv = rsqrtf(block_sum(acc, sh) / dim + eps);
+        if (VEC) {
+            for (int j = threadIdx.x * N; j < dim; j += blockDim.x * N) {
+                float f[N], g[N];
+                Vec<T>::ld(xr + j, f);
+                Vec<T>::ld(w + j, g);
+#pragma unroll
+                for (int q = 0; q < N; q++) f[q] = f[q] * inv * g[q];
+                Vec<T>::st(orow + j, f);
+            }
+        } else {
+            for (int j = threadIdx.x; j < dim; j += blockDim.x) stf(orow, j, ldf(xr, j) * inv * ldf(w, j));
+        }
+    }
+}
+static int norm_threads(int dim, int per) {
+    int t = (dim / per + 31) / 32 * 32;
+    if (t < 32) t = 32;
+    if (t > 512) t = 512;
+    return t;
+}
+int ax_rmsnorm(int dt, const void* x, const void* w, void* o, int rows, int dim, float eps, cudaStream_t st) {
+    if (rows <= 0 || dim <= 0) return 0;
+    const int per = dt == 1 ? 8 : 4;
+    const bool vec = dim % per == 0 && aligned16(x) && aligned16(w) && aligned16(o);
+    const int thr = norm_threads(dim, vec ? per : 1);
+    const int grid = rows < AX_SMS * 32 ? rows : AX_SMS * 32;
+    if (dt == 1) {
+        if (vec) k_rmsnorm<bf16, true><<<grid, thr, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)o, rows, dim, eps);
+        else k_rmsnorm<bf16, false><<<grid, thr, 0, st>>>((const bf16*)x, (const bf16*)w, (bf16*)o, rows, dim, eps);
+    } else {
+        if (vec) k_rmsnorm<float, true><<<grid, thr, 0, st>>>((const float*)x, (const float*)w, (float*)o, rows, dim, eps);
+        else k_rmsnorm<float, false><<<grid, thr, 0, st>>>((const float*)x, (const float*)w, (float*)o, rows, dim, eps);
+    }
+    return 0;
+}
+
+// Two-kernel form of the reference ABI: dx plus tmp = g*x*inv (N x D), whose
+// column sum (COLSUM) is dw.
+template <typename T>
+__global__ void k_rmsnorm_bwd(const T* x, const T* w, const T* g, T* dx, T* tmp, int rows, int dim, float eps) {
+    __shared__ float sh[40];
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const long long base = (long long)r * dim;
+        float ss = 0.f, gwx = 0.f;
+        for (int j = threadIdx.x; j < dim; j += blockDim.x) {
+            const float xv = ldf(x, base + j), gv = ldf(g, base + j);
+            ss += xv * xv;
+            gwx += gv * ldf(w, j) * xv;
+        }
+        ss = block_sum(ss, sh);
+        gwx = block_sum(gwx, sh);
+        const float inv = rsqrtf(ss / dim + eps);
+        const float coef = inv * inv * inv * (gwx / dim);
+        for (int j = threadIdx.x; j < dim; j += blockDim.x) {
+            const float xv = ldf(x, base + j), gv = ldf(g, base + j);
+            stf(dx, base + j, gv * ldf(w, j) * inv - xv * coef);
+            stf(tmp, base + j, gv * xv * inv);
+        }
+    }
+}
+int ax_rmsnorm_bwd(int dt, const void* x, const void* w, const void* g, void* dx, void* tmp, int rows, int dim,
+                   float eps, cudaStream_t st) {
+    if (rows <= 0 || dim <= 0) return 0;
+    const int thr = norm_threads(dim, 1);
+    const int grid = rows < AX_SMS * 32 ? rows : AX_SMS * 32;
+    if (dt == 1) k_rmsnorm_bwd<bf16><<<grid, thr, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (bf16*)dx, (bf16*)tmp, rows, dim, eps);
+    else k_rmsnorm_bwd<float><<<grid, thr, 0, st>>>((const float*)x, (const float*)w, (const float*)g, (float*)dx, (float*)tmp, rows, dim, eps);
+    return 0;
+}
+
+// Column sum: block (32 columns x 8 row lanes), rows strided over lanes, then
+// a fixed-order shared-memory combine.  c[j] = sum_r a[r, j].
+template <typename T>
+__global__ void k_colsum(const T* __restrict__ a, float* __restrict__ c, int rows, int n) {
+    __shared__ float sh[8][33];
+    const int col = blockIdx.x * 32 + threadIdx.x;
+    float acc = 0.f;
+    if (col < n)
+        for (int r = threadIdx.y; r < rows; r += 8) acc += ldf(a, (long long)r * n + col);
+    sh[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < n) {
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) t += sh[q][threadIdx.x];
+        c[col] = t;
+    }
+}
+int ax_colsum(int dt, const void* a, float* c, int rows, int n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    dim3 blk(32, 8);
+    if (dt >= 1) k_colsum<bf16><<<(n + 31) / 32, blk, 0, st>>>((const bf16*)a, c, rows, n);
+    else k_colsum<float><<<(n + 31) / 32, blk, 0, st>>>((const float*)a, c, rows, n);
+    return 0;
+}
+
+// ── fused backward: dx (+ residual) and dw in one pass over x and g ────────
+// Grid of NB blocks; block b owns rows b, b+NB, ...  Each thread owns fixed
+// columns, so the per-block dw partial accumulates in shared memory without
+// synchronisation.  A second kernel adds the NB partials per column in block
+// order — no atomics, run-to-run identical.
+#define RB_BLOCKS (AX_SMS * 2)
+template <typename T, bool VEC>
+__global__ void k_rmsnorm_bwd_acc(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ g,
+                                  const T* res, T* dx, float* __restrict__ partial,
+                                  int rows, int dim, float eps) {
+    extern __shared__ float sdw[];            // dim floats
+    __shared__ float sh[40];
+    constexpr int N = Vec<T>::N;
+    for (int j = threadIdx.x; j < dim; j += blockDim.x) sdw[j] = 0.f;
+    __syncthreads();
+    // inside the row loop each thread only touches the columns it owns
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const long long base = (long long)r * dim;
+        float ss = 0.f, gwx = 0.f;
+        if (VEC) {
+            for (int j = threadIdx.x * N; j < dim; j += blockDim.x * N) {
+                float xv[N], gv[N], wv[N];
+                Vec<T>::ld(x + base + j, xv);
+                Vec<T>::ld(g + base + j, gv);
+                Vec<T>::ld(w + j, wv);
+#pragma unroll
+                for (int q = 0; q < N; q++) { ss += xv[q] * xv[q]; gwx += gv[q] * wv[q] * xv[q]; }
+            }
+        } else {
+            for (int j = threadIdx.x; j < dim; j += blockDim.x) {
+                const float xv = ldf(x, base + j), gv = ldf(g, base + j);
+                ss += xv * xv; gwx += gv * ldf(w, j) * xv;
+            }
+        }
+        ss = block_sum(ss, sh);
+        gwx = block_sum(gwx, sh);
+        const float inv = rsqrtf(ss / dim + eps);
+        const float coef = inv * inv * inv * (gwx / dim);
+        if (VEC) {
+            for (int j = threadIdx.x * N; j < dim; j += blockDim.x * N) {
+                float xv[N], gv[N], wv[N], o[N];
+                Vec<T>::ld(x + base + j, xv);
+                Vec<T>::ld(g + base + j, gv);
+                Vec<T>::ld(w + j, wv);
+                if (res) Vec<T>::ld(res + base + j, o);
+#pragma unroll
+                for (int q = 0; q < N; q++) {
+                    const float d = gv[q] * wv[q] * inv - xv[q] * coef;
+                    o[q] = res ? o[q] + d : d;
+                    sdw[j + q] += gv[q] * xv[q] * inv;
+                }
+                Vec<T>::st(dx + base + j, o);
+            }
+        } else {
+            for (int j = threadIdx.x; j < dim; j += blockDim.x) {
+                const float xv = ldf(x, base + j), gv = ldf(g, base + j);
+                const float d = gv * ldf(w, j) * inv - xv * coef;
+                stf(dx, base + j, res ? ldf(res, base + j) + d : d);
+                sdw[j] += gv * xv * inv;
+            }
+        }
+    }
+    __syncthreads();
+    if (partial)
+        for (int j = threadIdx.x; j < dim; j += blockDim.x) partial[(long long)blockIdx.x * dim + j] = sdw[j];
+}
+__global__ void k_colsum_partials(const float* __restrict__ partial, float* __restrict__ dw, int nb, int dim) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= dim) return;
+    float acc = 0.f;
+    for (int b = 0; b < nb; b++) acc += partial[(long long)b * dim + j];
+    dw[j] = acc;
+}
+long long ax_rmsnorm_bwd_acc_scratch(int dim) { return (long long)RB_BLOCKS * dim * sizeof(float); }
+int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, const void* res, void* dx,
+                       float* dw, float* scratch, int rows, int dim, float eps, cudaStream_t st) {
+    if (rows <= 0 || dim <= 0) return 0;
+    if ((size_t)dim * 4 > 200 * 1024) return 120;
+    const int per = dt == 1 ? 8 : 4;
+    const bool vec = dim % per == 0 && aligned16(x) && aligned16(w) && aligned16(g) && aligned16(dx) &&
+                     (!res || aligned16(res));
+    const int thr = norm_threads(dim, vec ? per : 1);
+    const int nb = rows < RB_BLOCKS ? rows : RB_BLOCKS;
+    const size_t smem = (size_t)dim * 4;
+    float* part = dw ? scratch : nullptr;
+#define RB_LAUNCH(TT, VV)                                                                              \
+    do {                                                                                               \
+        if (smem > 48 * 1024)                                                                          \
+            cudaFuncSetAttribute(k_rmsnorm_bwd_acc<TT, VV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        k_rmsnorm_bwd_acc<TT, VV><<<nb, thr, smem, st>>>((const TT*)x, (const TT*)w, (const TT*)g,      \
+                                                         (const TT*)res, (TT*)dx, part, rows, dim, eps); \
+    } while (0)
+    if (dt == 1) { if (vec) RB_LAUNCH(bf16, true); else RB_LAUNCH(bf16, false); }
+    else { if (vec) RB_LAUNCH(float, true); else RB_LAUNCH(float, false); }
+#undef RB_LAUNCH
+    if (dw) k_colsum_partials<<<(dim + 127) / 128, 128, 0, st>>>(scratch, dw, nb, dim);
+    return 0;
+}

@@ -1,0 +1,81 @@
+"""Weight containers shaped like the reference's `axis.nn.Transformer`, enough
+for `compile_model` (which only reads names, arrays and a few attributes).
+They hold parameters; all arithmetic happens in the engine."""
+from __future__ import annotations
+
+from types import SimpleNamespace
+from typing import Dict, Iterator, Sequence, Tuple
+
+import numpy as np
+
+
+class Param:
+    def __init__(self, data: np.ndarray):
+        self.data = np.ascontiguousarray(data, dtype=np.float32)
+
+
+class Transformer:
+    """Parameter set of a Llama-class decoder (names as in axis/nn.py:331-364).
+    2-D tensors ~ N(0, std) drawn in `named_parameters()` order from
+    `default_rng(seed)`; norm weights are ones."""
+
+    def __init__(self, vocab_size: int, dim: int, n_layers: int, n_heads: int,
+                 n_kv_heads: int = None, mlp_hidden: int = None, tie_embeddings: bool = True,
+                 seed: int = 42, std: float = 0.02):
+        n_kv_heads = n_kv_heads or n_heads
+        mlp_hidden = mlp_hidden or int(dim * 8 / 3)
+        dh = dim // n_heads
+        self.tie_embeddings = tie_embeddings
+        self.blocks = [SimpleNamespace(attn=SimpleNamespace(n_heads=n_heads, n_kv_heads=n_kv_heads))
+                       for _ in range(n_layers)]
+        rng = np.random.default_rng(seed)
+        self._params: Dict[str, Param] = {}
+        self.lora_scaling = None
+
+        def mat(name, shape):
+            self._params[name] = Param((rng.standard_normal(shape) * std).astype(np.float32))
+
+        def ones(name, n):
+            self._params[name] = Param(np.ones(n, dtype=np.float32))
+        mat("embed.weight", (vocab_size, dim))
+        for i in range(n_layers):
+            p = f"blocks.{i}."
+            ones(p + "attn_norm.weight", dim)
+            mat(p + "attn.q_proj.weight", (dim, n_heads * dh))
+            mat(p + "attn.k_proj.weight", (dim, n_kv_heads * dh))
+            mat(p + "attn.v_proj.weight", (dim, n_kv_heads * dh))
+            mat(p + "attn.o_proj.weight", (n_heads * dh, dim))
+            ones(p + "mlp_norm.weight", dim)
+            mat(p + "mlp.gate_proj.weight", (dim, mlp_hidden))
+            mat(p + "mlp.up_proj.weight", (dim, mlp_hidden))
+            mat(p + "mlp.down_proj.weight", (mlp_hidden, dim))
+        ones("norm.weight", dim)
+        if not tie_embeddings:
+            mat("lm_head.weight", (dim, vocab_size))
+
+    def named_parameters(self) -> Iterator[Tuple[str, Param]]:
+        return iter(self._params.items())
+
+    def apply_lora(self, rank: int, alpha: float,
+                   targets: Sequence[str] = ("q_proj", "k_proj", "v_proj", "o_proj",
+                                             "gate_proj", "up_proj", "down_proj"),
+                   seed: int = 7, std: float = 0.02) -> "Transformer":
+        """Add adapters A ~ N(0, std) [in, r], B = 0 [r, out] on the named
+        projections (W_eff = W + alpha/r * A B, axis/lora.py:29-54); the base
+        weights become frozen when the model is compiled."""
+        rng = np.random.default_rng(seed)
+        new: Dict[str, Param] = {}
+        for name, p in self._params.items():
+            parts = name.split(".")
+            if len(parts) == 5 and parts[3] in targets and parts[4] == "weight":
+                stem = ".".join(parts[:4])
+                fin, fout = p.data.shape
+                new[stem + ".base.weight"] = p
+                new[stem + ".lora_a"] = Param((rng.standard_normal((fin, rank)) * std).astype(np.float32))
+                new[stem + ".lora_b"] = Param(np.zeros((rank, fout), dtype=np.float32))
+            else:
+                new[name] = p
+        self._params = new
+        self.lora_a = True               # marks the container as adapter-carrying
+        self.scaling = float(alpha) / rank
+        return self

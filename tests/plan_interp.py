@@ -1,0 +1,278 @@
+"""Test-only plan interpreter: executes the engine's op tuples with numpy.
+
+It stands in for `axis_b200.engine.Engine` in the CPU tests so that the host
+lowering (buffer plan, op plan, arena layout, bucketed reduction schedule,
+ownership) can be checked against the oracle without a GPU.  It is test
+infrastructure: nothing in the package imports it, and the GPU tests never use
+it.  bf16 storage is emulated with round-to-nearest-even on uint16 bit
+patterns; collectives run over a `torch.distributed` gloo group when given.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from axis_b200 import engine as E
+from oracle import step_numpy as O
+
+
+class InterpEngine:
+    has_flash = True
+
+    def __init__(self, dist=None):
+        self.bufs = []          # numpy uint8 arrays (views share memory)
+        self.dist = dist        # torch.distributed module with an initialised gloo group, or None
+        self.rank = dist.get_rank() if dist else 0
+        self.world = dist.get_world_size() if dist else 1
+        self.launches = 0
+        self.captured = None
+        self.trace = []
+
+    # ── buffers ──
+    def alloc(self, nelems, itemsize=4):
+        self.bufs.append(np.full(int(nelems) * itemsize, 0xFF, dtype=np.uint8))   # garbage, not zeros
+        return len(self.bufs) - 1
+
+    def alloc_zero(self, nbytes):
+        self.bufs.append(np.zeros(int(nbytes), dtype=np.uint8))
+        return len(self.bufs) - 1
+
+    def view(self, parent, byte_offset, nbytes):
+        assert byte_offset + nbytes <= self.bufs[parent].size
+        self.bufs.append(self.bufs[parent][byte_offset:byte_offset + nbytes])
+        return len(self.bufs) - 1
+
+    def new_tensor(self, arr):
+        i = self.alloc(arr.size)
+        self.upload(i, arr)
+        return i
+
+    def _f32(self, i, n=None, off=0):
+        v = self.bufs[i].view(np.float32)
+        return v[off:] if n is None else v[off:off + n]
+
+    def _get(self, i, n, dt, off=0):
+        """Read n elements as float32 from storage type dt (0 fp32, 1 bf16)."""
+        if dt == 1:
+            return E.bf16_bits_to_f32(self.bufs[i].view(np.uint16)[off:off + n])
+        return self.bufs[i].view(np.float32)[off:off + n].copy()
+
+    def _put(self, i, arr, dt, off=0):
+        a = np.asarray(arr, dtype=np.float32).reshape(-1)
+        if dt == 1:
+            self.bufs[i].view(np.uint16)[off:off + a.size] = E.f32_to_bf16_bits(a)
+        else:
+            self.bufs[i].view(np.float32)[off:off + a.size] = a
+
+    def upload(self, i, arr):
+        a = np.ascontiguousarray(arr, dtype=np.float32).reshape(-1)
+        self.bufs[i].view(np.float32)[:a.size] = a
+
+    def download(self, i, shape):
+        n = int(np.prod(shape))
+        return self.bufs[i].view(np.float32)[:n].reshape(shape).copy()
+
+    def upload_raw(self, i, arr, byte_offset=0):
+        b = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+        self.bufs[i][byte_offset:byte_offset + b.size] = b
+
+    def download_raw(self, i, shape, dtype, byte_offset=0):
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        return self.bufs[i][byte_offset:byte_offset + n].view(dtype).reshape(shape).copy()
+
+    def upload_tokens(self, i, tokens, limit):
+        t = np.asarray(tokens, dtype=np.int64).reshape(-1)
+        if (t >= limit).any() or (t < -1).any():
+            raise RuntimeError("upload_tokens failed rc=3")
+        self.bufs[i].view(np.int32)[:t.size] = t.astype(np.int32)
+
+    def set_tf32(self, on): pass
+    def sync(self): pass
+    def nccl_id(self): return bytes(128)
+    def nccl_init(self, *a, **k): pass
+    def launch_count(self, reset=False): return self.launches
+
+    # ── plans ──
+    def run(self, plan, sync=True):
+        for i, o in enumerate(plan):
+            try:
+                self._exec(o)
+            except Exception as e:      # pragma: no cover - debugging aid
+                raise RuntimeError(f"op {i} kind {E.KIND_NAMES[o[0]]} failed: {e}") from e
+
+    def capture(self, plan):
+        self.captured = list(plan)
+
+    def replay(self, times=1, sync=True):
+        if self.captured is None:
+            raise RuntimeError("replay failed rc=1")
+        for _ in range(times):
+            self.run(self.captured)
+
+    # ── ops ──
+    def _gemm(self, o, ex):
+        (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc, alpha, beta, _) = o
+        in_dt = 1 if dt >= 1 else 0
+        out_dt = 1 if dt == 1 else 0
+        alpha = 1.0 if alpha == 0.0 else alpha
+        batch = max(batch, 1)
+        for z in range(batch):
+            A = self._get(a, m * k, in_dt, oa + z * sa)
+            B = self._get(b, k * n, in_dt, ob + z * sb)
+            if tb == 0:
+                r = A.reshape(m, k) @ B.reshape(k, n)
+            elif tb == 1:
+                r = A.reshape(m, k) @ B.reshape(n, k).T
+            else:
+                r = A.reshape(k, m).T @ B.reshape(k, n)
+            r = np.float32(alpha) * r
+            if beta != 0.0:
+                src = d if (ex and d >= 0) else c
+                r = r + np.float32(beta) * self._get(src, m * n, out_dt, oc + z * sc).reshape(m, n)
+            self._put(c, r, out_dt, oc + z * sc)
+
+    def _exec(self, o):
+        (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc, alpha, beta, gamma) = o
+        self.trace.append(kind)
+        if kind not in (E.GROUP, E.FORK, E.JOIN, E.STREAM):
+            self.launches += 1
+        if kind in (E.GEMM, E.GEMM_SB):
+            return self._gemm(o, False)
+        if kind == E.GEMM_EX:
+            return self._gemm(o, True)
+        if kind == E.EMBED_I32:
+            ids = self.bufs[b].view(np.int32)[:m]
+            tab = self._get(a, self.bufs[a].size // (2 if dt == 1 else 4), dt).reshape(-1, n)
+            return self._put(c, tab[ids], dt)
+        if kind == E.RMSNORM:
+            x = self._get(a, m * n, dt).reshape(m, n)
+            y, _ = O.rmsnorm_fwd(x, self._get(b, n, dt), alpha)
+            return self._put(c, y, dt)
+        if kind == E.ROPE_BTHD:
+            B_, T, H, DH = batch, m, k, n
+            cos = self._f32(b, T * (DH // 2)).reshape(T, DH // 2)
+            sin = self._f32(d, T * (DH // 2)).reshape(T, DH // 2)
+            x = self._get(a, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)
+            y = O.rope_bwd(x, cos, sin) if tb else O.rope_fwd(x, cos, sin)
+            return self._put(c, y.transpose(0, 2, 1, 3), dt)
+        if kind == E.ATTN_FWD:
+            B_, T, DH, KV, H = batch, m, n, k, tb
+            q = self._get(a, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)
+            kk = self._get(b, B_ * T * KV * DH, dt).reshape(B_, T, KV, DH).transpose(0, 2, 1, 3)
+            v = self._get(d, B_ * T * KV * DH, dt).reshape(B_, T, KV, DH).transpose(0, 2, 1, 3)
+            out, lse = O.attention_fwd(q, kk, v, alpha)
+            self._put(c, out.transpose(0, 2, 1, 3), dt)
+            return self._put(sa, lse, 0)
+        if kind == E.ATTN_BWD:
+            B_, T, DH, KV, H = batch, m, n, k, ob
+            q = self._get(a, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)
+            kk = self._get(b, B_ * T * KV * DH, dt).reshape(B_, T, KV, DH).transpose(0, 2, 1, 3)
+            v = self._get(d, B_ * T * KV * DH, dt).reshape(B_, T, KV, DH).transpose(0, 2, 1, 3)
+            do = self._get(c, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)
+            dq, dk, dv = O.attention_bwd(q, kk, v, do, alpha)
+            self._put(tb, dq.transpose(0, 2, 1, 3), dt)
+            self._put(sc, dk.transpose(0, 2, 1, 3), dt)
+            return self._put(oa, dv.transpose(0, 2, 1, 3), dt)
+        if kind == E.SILU_MUL:
+            g, u = self._get(a, n, dt), self._get(b, n, dt)
+            return self._put(c, O.silu_mul_fwd(g, u)[0], dt)
+        if kind == E.SILU_BWD:
+            g, u, gr = self._get(a, n, dt), self._get(b, n, dt), self._get(d, n, dt)
+            sig = 1.0 / (1.0 + np.exp(-g))
+            dg, du = O.silu_mul_bwd(g, u, sig, gr)
+            self._put(c, dg, dt)
+            return self._put(tb, du, dt)
+        if kind == E.CE_FUSED:
+            lg = self._get(a, m * n, dt).reshape(m, n)
+            tg = self.bufs[b].view(np.int32)[:m].astype(np.int64)
+            tg = np.where(tg < 0, -1, tg)
+            cnt = O.count_valid(tg)
+            self._f32(sa)[0] = cnt
+            if cnt == 0:
+                self._put(c, np.zeros_like(lg), dt)
+                self._f32(d)[0] = np.nan
+                return
+            loss, dl, _ = O.cross_entropy_fwd_bwd(lg, tg, -1)
+            self._f32(d)[0] = loss
+            return self._put(c, dl, dt)
+        if kind == E.RMSNORM_BWD_ACC:
+            x = self._get(a, m * n, dt).reshape(m, n)
+            w = self._get(b, n, dt)
+            g = self._get(d, m * n, dt).reshape(m, n)
+            _, inv = O.rmsnorm_fwd(x, w, alpha)
+            dx, dw = O.rmsnorm_bwd(x, w, inv, g)
+            if tb > 0:
+                dx = dx + self._get(tb, m * n, dt).reshape(m, n)
+            self._put(c, dx, dt)
+            if sa > 0:
+                self._put(sa, dw, 0)
+            return
+        if kind == E.EMBED_BWD_DET:
+            ids = self.bufs[b].view(np.int32)[:m]
+            g = self._get(a, m * n, 1 if dt >= 1 else 0).reshape(m, n)
+            tab = self._f32(c).reshape(-1, n)
+            np.add.at(tab, ids, g)
+            return
+        if kind == E.SCALE:
+            if alpha == 0.0:
+                return self._put(c, np.zeros(n, np.float32), dt)
+            return self._put(c, self._get(a, n, dt) * np.float32(alpha), dt)
+        if kind == E.CAST:
+            cnt = m * max(n, 1)
+            if tb == 0:
+                return self._put(c, self._get(a, cnt, 0), 1)
+            return self._put(c, self._get(a, cnt, 1), 0)
+        if kind == E.GNORM_FLAT:
+            g = self._f32(a, m * E.CHUNK, oa * E.CHUNK)
+            if tb > 0:
+                self._f32(tb)[0] += 1.0
+            self._f32(d)[ob] = np.float32((g.astype(np.float64) ** 2).sum())
+            return
+        if kind == E.ADAMW_FLAT:
+            cnt, off = m * E.CHUNK, k * E.CHUNK
+            p = self._f32(a, cnt); mm = self._f32(c, cnt); vv = self._f32(d, cnt)
+            g = self._f32(b, cnt, off)
+            flags = np.repeat(self.bufs[sc][k:k + m], E.CHUNK).astype(bool)
+            tot = float(np.sqrt(np.float32(self._f32(oa, ob).astype(np.float64).sum())))
+            if oc > 0:
+                self._f32(oc)[0] = tot
+            gs = alpha / tot if (alpha > 0 and tot > alpha) else 1.0
+            t = float(self._f32(tb)[0]); lr = float(self._f32(sb)[0])
+            bc1, bc2 = 1 - 0.9 ** t, 1 - 0.95 ** t
+            gi = g * np.float32(gs)
+            mm[:] = 0.9 * mm + np.float32(0.1) * gi
+            vv[:] = 0.95 * vv + np.float32(0.05) * gi * gi
+            decay = np.where(flags, np.float32(1 - lr * beta), np.float32(1.0))
+            p[:] = p * decay - np.float32(lr * np.sqrt(bc2) / bc1) * mm / (np.sqrt(vv) + np.float32(gamma * np.sqrt(bc2)))
+            if sa > 0:
+                self._put(sa, p, 1, off)
+            return
+        if kind in (E.GROUP, E.FORK, E.JOIN, E.STREAM):
+            return
+        if kind in (E.REDUCE, E.BROADCAST, E.ALLREDUCE):
+            import torch
+            half = kind == E.BROADCAST and dt == 1
+            cnt = m * E.CHUNK if m > 0 else n
+            off = oa * E.CHUNK if m > 0 else 0
+            if half:        # gloo moves bytes; a broadcast does not care about the element type
+                view = self.bufs[a][off * 2:(off + cnt) * 2]
+            else:
+                view = self.bufs[a].view(np.float32)[off:off + cnt]
+            tns = torch.from_numpy(view)
+            if kind == E.BROADCAST:
+                self.dist.broadcast(tns, src=tb)
+            elif kind == E.REDUCE:
+                self.dist.reduce(tns, dst=tb, op=self.dist.ReduceOp.SUM)
+                if self.rank == tb:
+                    view /= np.float32(self.world)
+            else:
+                self.dist.all_reduce(tns, op=self.dist.ReduceOp.SUM)
+                view /= np.float32(self.world)
+            return
+        if kind == E.ALLGATHER_F32:
+            import torch
+            send = torch.from_numpy(self._f32(a, n, oa).copy())
+            outs = [torch.empty(n) for _ in range(self.world)]
+            self.dist.all_gather(outs, send)
+            self._f32(c)[:n * self.world] = torch.cat(outs).numpy()
+            return
+        raise NotImplementedError(E.KIND_NAMES[kind])
