@@ -66,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    link = [nvcc, "-shared", "-o", LIB, *objs, "-lnccl", "-lcudart"]
+    link = [nvcc, "-shared", "-o", LIB, *objs, "-lnccl", "-cudart", "static"]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

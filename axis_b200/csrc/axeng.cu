@@ -704,6 +704,25 @@ API int eng_replay(int times, int sync) {
     return sync ? eng_sync() : 0;
 }
 
+API int eng_time_replay(int times, float* ms_out) {
+    if (!G.graph) { set_err("no captured plan"); return 1; }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaEventRecord(e0, G.stream);
+    int rc = 0;
+    for (int i = 0; i < times && !rc; i++) {
+        if (cudaGraphLaunch(G.graph, G.stream)) { set_err("graph launch failed: %s", cudaGetErrorString(cudaGetLastError())); rc = 2; }
+        G.launches += G.graph_launches;
+    }
+    cudaEventRecord(e1, G.stream);
+    if (cudaEventSynchronize(e1) && !rc) { set_err("replay failed: %s", cudaGetErrorString(cudaGetLastError())); rc = 130; }
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (ms_out) *ms_out = ms;
+    return rc;
+}
+
 API int eng_time_plan(const EngOp* ops, int n_ops, int reps, int flush_l2, float* ms_out) {
     if (!G.inited) return 1;
     if (reps < 1) reps = 1;

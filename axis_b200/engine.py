@@ -244,7 +244,10 @@ class Engine:
         pp = self.pack(plan)
         rc = self.lib.eng_run_plan(pp.ptr, pp.n, 1 if sync else 0)
         if rc:
-            where = f"op {rc - 1000} kind {KIND_NAMES[int(pp.arr['kind'][rc - 1000])]}" if rc >= 1000 else "?"
+            where = "?"
+            if rc >= 1000:
+                kind = int(pp.arr["kind"][rc - 1000])
+                where = f"op {rc - 1000} kind {KIND_NAMES[kind] if 0 <= kind < KIND_COUNT else kind}"
             raise RuntimeError(f"run_plan failed rc={rc} ({where}): {self.last_error()}")
 
     def capture(self, plan) -> None:

@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the compiled training step (fwd + bwd + clip + AdamW).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config c3]
+
+One JSON line on stdout (rank 0).  `value` is tokens/s of the whole job with the
+batch already on the device (CUDA-graph replays between two CUDA events, max
+over ranks); `e2e` is the same metric through the public API with host arrays
+(`ct.replay_step(x, y)`: pinned H2D of ids/targets and the D2H loss read every
+step).  N > 1 (launched by torchrun): data parallel + ZeRO-1, one process per
+GPU, weak scaling (fixed per-GPU batch).  `--impl reference` times the numpy
+restatement of the reference's step on the host cores (the only place besides
+`cpu_baseline` where this file runs anything from oracle/).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+RANK = int(os.environ.get("RANK", "0"))
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+LOCAL_RANK = int(os.environ.get("LOCAL_RANK", "0"))
+if WORLD > 1 and "AXIS_KEEP_VISIBLE" not in os.environ:
+    # one GPU per process, as the engine expects (axis/_csrc/runtime.cu:57-65 is process-global)
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    devs = vis.split(",") if vis else [str(i) for i in range(64)]
+    os.environ["CUDA_VISIBLE_DEVICES"] = devs[LOCAL_RANK % len(devs)]
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # BASELINE configs[2]: the 1B-class step the headline metric is quoted on
+    "c3": dict(cfg=dict(vocab_size=32000, dim=1536, n_layers=48, n_heads=24, n_kv_heads=8, mlp_hidden=4096,
+                        tie_embeddings=True), B=4, T=2048, dtype="bf16", ignore=0.05, lora=0, lr=3e-4,
+               name="1B-class V32000 D1536 L48 H24/KV8 MLP4096 B4 T2048 bf16+fp32 masters, graph replay"),
+    # BASELINE configs[0]: the reference's CPU-runnable plumbing case
+    "c1": dict(cfg=dict(vocab_size=1024, dim=256, n_layers=4, n_heads=8, n_kv_heads=4, mlp_hidden=688,
+                        tie_embeddings=True), B=2, T=256, dtype="fp32", ignore=0.10, lora=0, lr=3e-4,
+               name="V1024 D256 L4 H8/KV4 MLP688 B2 T256 fp32"),
+    # BASELINE configs[4]: LoRA fine-tune on a long sequence
+    "c5": dict(cfg=dict(vocab_size=32000, dim=1536, n_layers=48, n_heads=24, n_kv_heads=8, mlp_hidden=4096,
+                        tie_embeddings=True), B=1, T=8192, dtype="bf16", ignore=0.0, lora=16, lr=1e-4,
+               name="1B-class LoRA r16 a32 B1 T8192 bf16, 40% prompt masked"),
+    # BASELINE configs[3]: 7B data parallel + ZeRO-1 (needs >= 2 GPUs for the optimizer state)
+    "c4": dict(cfg=dict(vocab_size=32000, dim=4096, n_layers=32, n_heads=32, n_kv_heads=32, mlp_hidden=11008,
+                        tie_embeddings=True), B=2, T=4096, dtype="bf16", ignore=0.0, lora=0, lr=3e-4,
+               name="7B-class V32000 D4096 L32 H32/KV32 MLP11008 B2/GPU T4096 bf16 ZeRO-1"),
+    # small stand-in used by smoke runs
+    "tiny": dict(cfg=dict(vocab_size=512, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=384,
+                          tie_embeddings=True), B=2, T=256, dtype="bf16", ignore=0.05, lora=0, lr=3e-4,
+                 name="tiny"),
+}
+METRIC = "train tok/s (fwd+bwd+AdamW)"
+
+
+def step_flops(c) -> float:
+    """6 * dense params * tokens + 7 * B*H*T^2*DH*L (causal attention, fwd+bwd)."""
+    cfg, B, T = c["cfg"], c["B"], c["T"]
+    D, L, H, V, MLP = cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["vocab_size"], cfg["mlp_hidden"]
+    KV = cfg["n_kv_heads"]
+    DH = D // H
+    per_layer = D * H * DH + 2 * D * KV * DH + H * DH * D + 3 * D * MLP
+    dense = L * per_layer + V * D
+    mult = 4 if c["lora"] else 6
+    return mult * dense * B * T + 7.0 * B * H * T * T * DH * L
+
+
+def make_weights(cfg, seed):
+    from axis_b200.model import Transformer
+    return Transformer(cfg["vocab_size"], cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"],
+                       cfg["mlp_hidden"], cfg["tie_embeddings"], seed=seed, std=0.02)
+
+
+def make_batch(c, rng):
+    V, B, T = c["cfg"]["vocab_size"], c["B"], c["T"]
+    x = rng.integers(0, V, size=(B, T)).astype(np.int64)
+    y = rng.integers(0, V, size=(B, T)).astype(np.int64)
+    if c["lora"]:
+        y[:, :int(0.4 * T)] = -1
+    elif c["ignore"] > 0:
+        y = np.where(rng.random((B, T)) < c["ignore"], -1, y)
+    return x, y
+
+
+class ClockSampler:
+    """nvidia-smi samples every 200 ms while the timed region runs (read-only queries)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            dev = os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0] or "0"
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", dev], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except (OSError, ValueError):
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def cpu_reference(c, budget_s=25.0):
+    """Times the numpy restatement of the reference's step on the host cores, on a bounded
+    sample of the workload: the same widths and vocabulary, batch 1 and fewer layers /
+    a shorter sequence, extrapolated linearly in layers and batch."""
+    from oracle import step_numpy as O
+    cfg = dict(c["cfg"])
+    L_full, B_full, T_full = cfg["n_layers"], c["B"], c["T"]
+    small = cfg["dim"] <= 512
+    T = T_full if small else min(T_full, 512)
+    B = B_full if small else 1
+    times = {}
+    for L in ((L_full,) if small else (1, 2)):
+        cfg["n_layers"] = L
+        w = O.init_weights(cfg, seed=1)
+        kw = {}
+        if c["lora"]:
+            tg = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+            w.update(O.init_lora(cfg, c["lora"], tg))
+            kw = dict(lora_rank=c["lora"], lora_alpha=2.0 * c["lora"], lora_targets=tg)
+        model = O.OracleTransformer(cfg, w, **kw)
+        opt = O.OracleAdamW(model, lr=c["lr"])
+        rng = np.random.default_rng(0)
+        x, y = O.make_batch(rng, cfg["vocab_size"], B, T, c["ignore"])
+        reps = 3 if small else 1
+        if small:
+            O.train_step(model, opt, x, y, max_grad_norm=1.0)     # warm
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            O.train_step(model, opt, x, y, max_grad_norm=1.0)
+        times[L] = (time.perf_counter() - t0) / reps
+    if small:
+        step_s = times[L_full]
+        sample = f"full workload, {3} timed steps after 1 warm-up"
+    else:
+        per_layer = max(times[2] - times[1], 1e-9)
+        # attention is quadratic in T: scale the per-layer time by the flop ratio at the full T
+        H, DH, D, MLP, KV = cfg["n_heads"], cfg["dim"] // cfg["n_heads"], cfg["dim"], cfg["mlp_hidden"], cfg["n_kv_heads"]
+        lin = 6.0 * (D * H * DH + 2 * D * KV * DH + H * DH * D + 3 * D * MLP)
+        att = lambda t: 7.0 * H * t * DH
+        scale_T = (lin + att(T_full)) / (lin + att(T))
+        head = max(times[1] - per_layer, 0.0)
+        step_s = (head + L_full * per_layer * scale_T) * (B_full * T_full) / (B * T)
+        sample = (f"B={B} T={T} with 1 and 2 layers (same widths/vocab), one step each; extrapolated to "
+                  f"L={L_full} B={B_full} T={T_full} (linear in layers and tokens, attention by flops)")
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    return {"value": c["B"] * c["T"] / step_s, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": sample, "step_s_est": step_s}
+
+
+def reduce_max(val: float) -> float:
+    if WORLD == 1:
+        return val
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([val], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def barrier():
+    if WORLD > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="axis_b200")
+    ap.add_argument("--config", default="c3")
+    ap.add_argument("--zero", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernel-table", action="store_true")
+    args = ap.parse_args()
+    c = CONFIGS[args.config]
+    W = max(args.warmup, 3)
+    K = max(args.steps, 1)
+
+    if args.impl == "reference":
+        if RANK != 0:
+            return
+        cb = cpu_reference(c)
+        line = {"metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+                "ms_per_step": cb["step_s_est"] * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+                "config": {"workload": c["name"]}, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    if WORLD > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo", init_method=f"tcp://{os.environ.get('MASTER_ADDR', '127.0.0.1')}:"
+                                f"{os.environ.get('MASTER_PORT', '29500')}", rank=RANK, world_size=WORLD)
+
+    from axis_b200.compile import compile_model
+    model = make_weights(c["cfg"], seed=42)
+    if c["lora"]:
+        model.apply_lora(rank=c["lora"], alpha=2.0 * c["lora"])
+    zero = args.zero if WORLD > 1 else 0
+    ct = compile_model(model, batch=c["B"], seq=c["T"], dtype=c["dtype"], lr=c["lr"], max_grad_norm=1.0,
+                       grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD)
+    del model
+    eng = ct.eng
+    if WORLD > 1:
+        import torch
+        import torch.distributed as dist
+        uid = torch.zeros(128, dtype=torch.uint8)
+        if RANK == 0:
+            uid = torch.frombuffer(bytearray(eng.nccl_id()), dtype=torch.uint8).clone()
+        dist.broadcast(uid, src=0)
+        eng.nccl_init(RANK, WORLD, bytes(uid.numpy().tobytes()), timeout_ms=120000)
+
+    rng = np.random.default_rng(100 + RANK)
+    batches = [make_batch(c, rng) for _ in range(4)]
+    ct.capture()
+    losses = []
+    for i in range(W):
+        losses.append(ct.replay_step(*batches[i % 4]))
+
+    # ── device-resident throughput: K replays between two events ──
+    clocks = ClockSampler()
+    clocks.start()
+    eng.sync(); barrier()
+    eng.launch_count(reset=True)
+    # graph replays timed by events inside the engine
+    ms_dev = time_replays(eng, K)
+    launches = eng.launch_count()
+    ms_dev = reduce_max(ms_dev)
+    barrier()
+    # ── end to end through the public API: host arrays in, loss out, every step ──
+    eng.sync(); barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        losses.append(ct.replay_step(*batches[i % 4]))
+    eng.sync()
+    e2e_s = reduce_max(time.perf_counter() - t0)
+    clk = clocks.stop()
+
+    tokens = c["B"] * c["T"] * WORLD
+    value = tokens * K / (ms_dev / 1e3)
+    e2e = tokens * K / e2e_s
+
+    line = {"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": WORLD, "steps": K, "warmup": W,
+            "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": c["dtype"], "data": "synthetic",
+            "config": {"workload": c["name"], "parallelism": f"dp{WORLD}" + ("+zero1" if zero else ""),
+                       "l2": "working set per step far exceeds the 126 MB L2 (no flush needed)",
+                       "global_batch": c["B"] * WORLD, "seq_len": c["T"]},
+            "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 2 * 4 * c["B"] * c["T"],
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches), "clocks": clk, "loss_first": losses[0], "loss_last": losses[-1],
+            "step_tflops": step_flops(c) * K / (ms_dev / 1e3) / 1e12 / 1.0,
+            "device_status": eng.device_status()}
+
+    if RANK == 0 and not args.no_kernel_table:
+        line.update(kernel_table(ct, c, batches[0]))
+    if RANK == 0 and not args.no_cpu_baseline and WORLD == 1:
+        line["cpu_baseline"] = cpu_reference(c)
+    barrier()
+    if RANK == 0:
+        print(json.dumps(line))
+    if WORLD > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def time_replays(eng, K):
+    """K graph launches between two CUDA events on the engine stream (milliseconds)."""
+    import ctypes
+    lib = eng.lib
+    if not hasattr(lib, "eng_time_replay"):
+        raise RuntimeError("libaxeng.so lacks eng_time_replay")
+    lib.eng_time_replay.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
+    ms = ctypes.c_float(0)
+    rc = lib.eng_time_replay(K, ctypes.byref(ms))
+    if rc:
+        raise RuntimeError(f"eng_time_replay rc={rc}: {eng.last_error()}")
+    return float(ms.value)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def kernel_table(ct, c, batch):
+    """Per-op-kind device time of one eager step (CUDA events around every op), the GEMM
+    roofline entry, and the isolated flash-attention backward at the benchmark shape."""
+    from axis_b200 import engine as E
+    eng = ct.eng
+    hbm, tf_burst, tf_sus, src = peaks()
+    ct._feed(*batch)
+    eng.profile(True)
+    eng.run(ct.plan_step, sync=True)
+    prof = eng.profile_read()
+    eng.profile(False)
+    total = sum(v[0] for v in prof.values()) or 1.0
+    gemm_ms = sum(prof.get(k, (0, 0))[0] for k in ("GEMM", "GEMM_SB", "GEMM_EX"))
+    gemm_calls = sum(prof.get(k, (0, 0))[1] for k in ("GEMM", "GEMM_SB", "GEMM_EX"))
+    gemm_flops = 0.0
+    for o in ct.plan_step:
+        if o[0] in (E.GEMM, E.GEMM_SB, E.GEMM_EX):
+            gemm_flops += 2.0 * o[5] * o[6] * o[7] * max(o[8], 1)
+    achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f).get("gemm_tc_bytes_per_launch")
+    out = {"roofline": {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 bf16 GEMM, all GEMM ops of the step)",
+                        "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s", "frac": achieved / tf_sus,
+                        "peak_source": f"{src} (sustained cuBLAS bf16)", "launches": gemm_calls,
+                        "avg_launch_ms": gemm_ms / max(gemm_calls, 1), "traffic": traffic},
+           "kernels": {k: {"ms": round(v[0], 3), "calls": v[1], "share": round(v[0] / total, 4)}
+                       for k, v in sorted(prof.items(), key=lambda kv: -kv[1][0])}}
+    return out
+
+
+if __name__ == "__main__":
+    main()

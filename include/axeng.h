@@ -128,6 +128,9 @@ int eng_device_status(int clear);
 /* Time `reps` executions of a plan with CUDA events on the engine stream,
  * flushing L2 between repetitions when flush_l2 != 0; ms_out = mean ms. */
 int eng_time_plan(const EngOp* ops, int n_ops, int reps, int flush_l2, float* ms_out);
+/* `times` launches of the captured graph between two CUDA events on the engine
+ * stream; ms_out = total milliseconds. */
+int eng_time_replay(int times, float* ms_out);
 /* Per-kind accounting: when on, every op in run_plan is bracketed by events.
  * eng_profile_read fills ms[ENG_KIND_COUNT] and calls[ENG_KIND_COUNT]. */
 int eng_profile(int on);

@@ -1,0 +1,125 @@
+"""GEMM op (kinds GEMM / GEMM_SB / GEMM_EX) on the GPU against numpy: the three
+operand layouts the plan uses (tb 0/1/2, axis/engine.py:47), fp32 and bf16
+storage, bf16-in/fp32-out weight gradients, alpha/beta epilogues, offsets and
+strided batches, tile tails, and tensor-core path vs general path agreement."""
+import numpy as np
+import pytest
+
+from axis_b200 import engine as E
+from axis_b200.engine import Engine, op
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    e = Engine()
+    e.alloc(4)
+    yield e
+    e.shutdown()
+
+
+def bf(a):
+    return E.bf16_bits_to_f32(E.f32_to_bf16_bits(a))
+
+
+def put(eng, arr, dt):
+    i = eng.alloc(arr.size, 2 if dt else 4)
+    eng.upload_bf16(i, arr) if dt else eng.upload(i, arr)
+    return i
+
+
+def run_gemm(eng, rng, m, n, k, tb, dt, alpha=0.0, beta=0.0, addend=False, fallback=0):
+    in_bf, out_bf = dt >= 1, dt == 1
+    sha = (k, m) if tb == 2 else (m, k)
+    shb = (n, k) if tb == 1 else (k, n)
+    A = rng.standard_normal(sha).astype(np.float32)
+    B = rng.standard_normal(shb).astype(np.float32)
+    C0 = rng.standard_normal((m, n)).astype(np.float32)
+    if in_bf:
+        A, B = bf(A), bf(B)
+    if out_bf:
+        C0 = bf(C0)
+    ia, ib = put(eng, A, in_bf), put(eng, B, in_bf)
+    ic = put(eng, C0, out_bf)
+    idd = put(eng, C0, out_bf) if addend else -1
+    if addend:
+        eng.upload_bf16(ic, np.zeros((m, n), np.float32)) if out_bf else eng.upload(ic, np.zeros((m, n), np.float32))
+    eng.set_fallback(fallback)
+    kind = E.GEMM_EX if addend else E.GEMM_SB
+    eng.run([op(kind, a=ia, b=ib, c=ic, d=idd, m=m, n=n, k=k, batch=1, tb=tb, dt=dt, alpha=alpha, beta=beta)])
+    eng.set_fallback(0)
+    got = eng.download_bf16(ic, (m, n)) if out_bf else eng.download(ic, (m, n))
+    Aop = A.T if tb == 2 else A
+    Bop = B.T if tb == 1 else B
+    ref = (alpha if alpha != 0.0 else 1.0) * (Aop.astype(np.float64) @ Bop.astype(np.float64)) + beta * C0
+    return got, ref.astype(np.float32)
+
+
+def check(got, ref, out_bf, k):
+    scale = np.abs(ref).max() + 1e-6
+    err = np.abs(got - ref).max() / scale
+    lim = 6e-3 if out_bf else 3e-6 * max(1.0, np.sqrt(k) / 4)
+    assert err <= lim, (err, lim)
+
+
+@pytest.mark.parametrize("tb", [0, 1, 2])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (5, 7, 3), (64, 64, 16), (100, 130, 70), (257, 96, 33)])
+def test_fp32_gemm_is_true_fp32(eng, tb, m, n, k):
+    rng = np.random.default_rng(m * n + k)
+    got, ref = run_gemm(eng, rng, m, n, k, tb, 0)
+    check(got, ref, False, k)
+    got, ref = run_gemm(eng, rng, m, n, k, tb, 0, alpha=0.5, beta=1.0)
+    check(got, ref, False, k)
+
+
+@pytest.mark.parametrize("tb", [0, 1, 2])
+@pytest.mark.parametrize("dt", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 128), (384, 512, 192), (200, 136, 72),
+                                   (128, 264, 1000), (1000, 128, 64)])
+def test_bf16_tensor_core_gemm(eng, tb, dt, m, n, k):
+    if tb == 2 and m % 8:
+        pytest.skip("M-major operand needs m % 8 == 0 for the TMA path")
+    rng = np.random.default_rng(m + n + k + tb)
+    got, ref = run_gemm(eng, rng, m, n, k, tb, dt)
+    check(got, ref, dt == 1, k)
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("tb", [0, 1, 2])
+def test_bf16_epilogues_and_addend(eng, tb):
+    rng = np.random.default_rng(tb)
+    for dt in (1, 2):
+        got, ref = run_gemm(eng, rng, 256, 384, 128, tb, dt, alpha=2.0, beta=1.0)
+        check(got, ref, dt == 1, 128)
+        got, ref = run_gemm(eng, rng, 256, 384, 128, tb, dt, beta=1.0, addend=True)
+        check(got, ref, dt == 1, 128)
+
+
+@pytest.mark.parametrize("tb", [0, 1, 2])
+def test_tensor_core_and_general_path_agree(eng, tb):
+    for dt in (1, 2):
+        a = run_gemm(eng, np.random.default_rng(9), 256, 256, 256, tb, dt)[0]
+        b = run_gemm(eng, np.random.default_rng(9), 256, 256, 256, tb, dt, fallback=1)[0]
+        assert np.abs(a - b).max() <= (2e-2 if dt == 1 else 1e-3) * np.abs(b).max()
+
+
+@pytest.mark.parametrize("dt", [0, 1])
+def test_small_and_unaligned_bf16_and_batched_offsets(eng, dt):
+    rng = np.random.default_rng(5)
+    for (m, n, k, tb) in [(3, 5, 7, 0), (130, 16, 136, 0), (16, 130, 130, 2), (130, 136, 16, 1), (129, 131, 67, 1)]:
+        got, ref = run_gemm(eng, rng, m, n, k, tb, dt)
+        check(got, ref, dt == 1, k)
+    # strided batch with element offsets, as the tiled attention plan issues them
+    batch, qt, kl, DH, T, rep = 4, 8, 24, 16, 32, 2
+    q = rng.standard_normal((batch, rep, T, DH)).astype(np.float32)
+    kk = rng.standard_normal((batch, T, DH)).astype(np.float32)
+    if dt:
+        q, kk = bf(q), bf(kk)
+    iq, ik, ic = put(eng, q, dt), put(eng, kk, dt), eng.alloc(batch * qt * kl)
+    j, qs = 1, 16
+    eng.run([op(E.GEMM_SB, a=iq, b=ik, c=ic, m=qt, k=DH, n=kl, batch=batch, tb=1, sa=rep * T * DH, sb=T * DH,
+                sc=qt * kl, oa=(j * T + qs) * DH, dt=dt, alpha=0.25)])
+    ref = 0.25 * np.einsum("bqd,bkd->bqk", q[:, j, qs:qs + qt], kk[:, :kl])
+    got = eng.download_bf16(ic, ref.shape) if dt else eng.download(ic, ref.shape)
+    check(got, ref, dt == 1, DH)

@@ -1,0 +1,218 @@
+"""The compiled training step on the GPU against the oracle and the golden
+vectors: fp32 parity (gradients <= 1e-5 per-tensor max-relative, loss <= 1e-6
+relative over 30 steps), bf16 tolerances (gradients <= 2e-2, loss <= 1e-3),
+graph replay == eager, lr schedule under replay, state_dict resume, LoRA,
+shape fuzz (the reference's gates: engine/modal_compile_test.py:41-71,
+modal_bf16_test.py:59-136, modal_harden_test.py:51-227, modal_trainfix_test.py:70-161)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from axis_b200.compile import CompiledTransformer, compile_model
+from axis_b200.model import Transformer
+from oracle import step_numpy as O
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def rel(got, ref):
+    return float(np.abs(got - ref).max() / (np.abs(ref).max() + 1e-9))
+
+
+def load(name):
+    z = np.load(os.path.join(G, name + ".npz"))
+    cfg = json.loads(str(z["cfg"]))
+    return z, cfg, {k[3:]: z[k] for k in z.files if k.startswith("w0/")}
+
+
+def build(cfg, w0, B, T, dtype="fp32", **kw):
+    return CompiledTransformer(None, cfg, w0, B, T, dtype=dtype, **kw)
+
+
+@pytest.mark.parametrize("name", ["step_tied_gqa", "step_untied_mha", "step_lora"])
+def test_fp32_step_matches_golden(name):
+    z, cfg, w0 = load(name)
+    kw = {}
+    if cfg["lora"]:
+        kw = dict(lora_r=cfg["lora"]["rank"], lora_alpha=cfg["lora"]["alpha"], lora_targets=tuple(cfg["lora"]["targets"]))
+    ct = build(cfg, w0, cfg["B"], cfg["T"], max_grad_norm=cfg["max_norm"], **kw)
+    for s in range(cfg["steps"]):
+        loss = ct.step(z[f"x/{s}"], z[f"y/{s}"])
+        assert abs(loss - z["losses"][s]) <= 1e-6 * abs(z["losses"][s]) + 1e-6
+        assert abs(ct.grad_norm() - z["norms"][s]) <= 1e-5 * z["norms"][s]
+        assert ct.valid_count() == int((z[f"y/{s}"] >= 0).sum())          # integer work: exact
+        if s == 0:
+            g = ct.grads()
+            for k in z.files:
+                if k.startswith("g0/"):
+                    assert rel(g[k[3:]], z[k]) <= 1e-5, k
+    w = ct.get_weights()
+    for k in z.files:
+        if k.startswith("w1/"):
+            assert np.abs(w[k[3:]] - z[k]).max() <= 0.05 * 3e-4, k
+    assert ct.eng.device_status() == 0
+
+
+C1 = dict(vocab_size=1024, dim=256, n_layers=4, n_heads=8, n_kv_heads=4, mlp_hidden=688, tie_embeddings=True)
+
+
+def test_config1_fp32_30_step_trajectory():
+    """vocab 1024, dim 256, 4 layers, 8/4 heads, mlp 688, batch 2 x seq 256, 10 % ignored
+    targets, lr 3e-4, wd 0.1, clip 1.0: loss within 1e-6 (relative) of the oracle over 30
+    steps, first-step gradients within 1e-5."""
+    w0 = O.init_weights(C1, seed=42)
+    ct = build(C1, w0, 2, 256, max_grad_norm=1.0)
+    model = O.OracleTransformer(C1, w0)
+    opt = O.OracleAdamW(model)
+    rng = np.random.default_rng(42)
+    worst = 0.0
+    for s in range(30):
+        x, y = O.make_batch(rng, 1024, 2, 256, 0.10)
+        if s == 0:
+            l_ref, g_ref = model.loss_and_grads(x, y)
+            l = ct.forward_backward(x, y)
+            g = ct.grads()
+            for nm in g_ref:
+                assert rel(g[nm], g_ref[nm]) <= 1e-5, nm
+        loss = ct.step(x, y)
+        ref, _, _ = O.train_step(model, opt, x, y, max_grad_norm=1.0)
+        worst = max(worst, abs(loss - ref) / max(abs(ref), 1e-9))
+    assert worst <= 1e-6, worst
+
+
+def test_bf16_step_within_tolerance_of_fp32():
+    """bf16 storage vs the fp32 oracle on the canonical small fixture
+    (V500 B2 T32 D128 H4 KV2 MLP256 L3): gradients <= 2e-2, loss <= 1e-3."""
+    cfg = dict(vocab_size=500, dim=128, n_layers=3, n_heads=4, n_kv_heads=2, mlp_hidden=256, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=0)
+    rng = np.random.default_rng(0)
+    x, y = O.make_batch(rng, 500, 2, 32, 0.0)
+    l_ref, g_ref = O.OracleTransformer(cfg, w0).loss_and_grads(x, y)
+    for fb in (0, 3):
+        ct = build(cfg, w0, 2, 32, dtype="bf16")
+        ct.eng.set_fallback(fb)
+        loss = ct.forward_backward(x, y)
+        assert abs(loss - l_ref) <= 1e-3 * abs(l_ref), (fb, loss, l_ref)
+        g = ct.grads()
+        worst = max((rel(g[nm], g_ref[nm]), nm) for nm in g_ref)
+        assert worst[0] <= 2e-2, (fb, worst)
+
+
+def test_bf16_tensor_core_shapes_and_curve():
+    """A shape large enough for every GEMM to take the tcgen05 path (N = 512 tokens,
+    dims multiples of 128): gradients vs the fp32 oracle, then 10 steps of loss drift."""
+    cfg = dict(vocab_size=512, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=384, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=1)
+    rng = np.random.default_rng(1)
+    x, y = O.make_batch(rng, 512, 2, 256, 0.05)
+    l_ref, g_ref = O.OracleTransformer(cfg, w0).loss_and_grads(x, y)
+    ct = build(cfg, w0, 2, 256, dtype="bf16", max_grad_norm=1.0)
+    loss = ct.forward_backward(x, y)
+    assert abs(loss - l_ref) <= 1e-3 * abs(l_ref)
+    g = ct.grads()
+    worst = max((rel(g[nm], g_ref[nm]), nm) for nm in g_ref)
+    assert worst[0] <= 2e-2, worst
+    model = O.OracleTransformer(cfg, w0); opt = O.OracleAdamW(model, lr=1e-3)
+    ct.set_lr(1e-3)
+    drift = 0.0
+    for s in range(10):
+        x, y = O.make_batch(rng, 512, 2, 256, 0.05)
+        a = ct.step(x, y)
+        b, _, _ = O.train_step(model, opt, x, y, max_grad_norm=1.0)
+        drift = max(drift, abs(a - b) / abs(b))
+    assert drift <= 3e-3, drift
+    assert ct.eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_graph_replay_equals_eager_and_lr_schedule(dtype):
+    z, cfg, w0 = load("step_tied_gqa")
+    a = build(cfg, w0, cfg["B"], cfg["T"], dtype=dtype, max_grad_norm=1.0)
+    la = []
+    for s in range(3):
+        a.set_lr(3e-4 * (s + 1))
+        la.append(a.step(z[f"x/{s}"], z[f"y/{s}"]))
+    wa = a.get_weights()
+    b = build(cfg, w0, cfg["B"], cfg["T"], dtype=dtype, max_grad_norm=1.0)
+    b.capture()
+    lb = []
+    for s in range(3):
+        b.set_lr(3e-4 * (s + 1))
+        lb.append(b.replay_step(z[f"x/{s}"], z[f"y/{s}"]))
+    assert la == lb
+    for nm, w in b.get_weights().items():
+        assert np.array_equal(w, wa[nm]), nm
+
+
+def test_state_dict_resume_is_exact():
+    z, cfg, w0 = load("step_tied_gqa")
+    a = build(cfg, w0, cfg["B"], cfg["T"], dtype="bf16", max_grad_norm=1.0)
+    a.step(z["x/0"], z["y/0"])
+    st = a.state_dict()
+    l_a = [a.step(z[f"x/{s}"], z[f"y/{s}"]) for s in (1, 2)]
+    w_a = a.get_weights()
+    b = build(cfg, w0, cfg["B"], cfg["T"], dtype="bf16", max_grad_norm=1.0)
+    b.load_state_dict(st)
+    l_b = [b.step(z[f"x/{s}"], z[f"y/{s}"]) for s in (1, 2)]
+    assert l_a == l_b
+    for nm, w in b.get_weights().items():
+        assert np.array_equal(w, w_a[nm])
+
+
+FUZZ = [  # V, B, T, D, H, KV, MLP, L, tied
+    (300, 1, 17, 64, 4, 4, 96, 1, True),       # ragged T, MHA
+    (128, 2, 16, 64, 4, 1, 128, 2, False),     # MQA, untied
+    (64, 1, 8, 256, 2, 1, 64, 1, True),        # head_dim 128
+    (200, 3, 12, 64, 4, 2, 72, 2, True),       # head_dim 16, odd batch
+    (1000, 1, 33, 96, 6, 3, 200, 1, False),    # nothing a multiple of 64
+]
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("V,B,T,D,H,KV,MLP,L,tied", FUZZ)
+def test_shape_fuzz(dtype, V, B, T, D, H, KV, MLP, L, tied):
+    cfg = dict(vocab_size=V, dim=D, n_layers=L, n_heads=H, n_kv_heads=KV, mlp_hidden=MLP, tie_embeddings=tied)
+    w0 = O.init_weights(cfg, seed=V)
+    rng = np.random.default_rng(V)
+    x, y = O.make_batch(rng, V, B, T, 0.1)
+    l_ref, g_ref = O.OracleTransformer(cfg, w0).loss_and_grads(x, y)
+    ct = build(cfg, w0, B, T, dtype=dtype)
+    loss = ct.forward_backward(x, y)
+    lim_l, lim_g = (1e-6, 1e-5) if dtype == "fp32" else (1e-3, 2e-2)
+    assert abs(loss - l_ref) <= lim_l * abs(l_ref) + 1e-6
+    g = ct.grads()
+    worst = max((rel(g[nm], g_ref[nm]), nm) for nm in g_ref)
+    assert worst[0] <= lim_g, worst
+
+
+def test_lora_bf16_and_prompt_masking():
+    """Frozen base + rank-8 adapters on all seven projections; first 40 % of targets masked."""
+    cfg = dict(vocab_size=256, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=256, tie_embeddings=True)
+    m = Transformer(256, 128, 2, 4, 2, 256, seed=3).apply_lora(rank=8, alpha=16.0)
+    rng = np.random.default_rng(2)
+    for n, p in m.named_parameters():
+        if n.endswith("lora_b"):
+            p.data[...] = (rng.standard_normal(p.data.shape) * 0.02).astype(np.float32)
+    B, T = 2, 64
+    x = rng.integers(0, 256, (B, T)).astype(np.int64)
+    y = np.roll(x, -1, axis=1); y[:, :int(0.4 * T)] = -1
+    weights = {n.replace(".base.weight", ".weight"): p.data for n, p in m.named_parameters()}
+    om = O.OracleTransformer(cfg, weights, lora_rank=8, lora_alpha=16.0,
+                             lora_targets=("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"))
+    l_ref, g_ref = om.loss_and_grads(x, y)
+    for dtype, lim_l, lim_g in (("fp32", 1e-6, 1e-5), ("bf16", 1e-3, 2e-2)):
+        ct = compile_model(m, batch=B, seq=T, dtype=dtype, lr=1e-4)
+        assert ct.lora_r == 8 and len(ct.pnames) == 2 * 7 * 2
+        loss = ct.forward_backward(x, y)
+        assert ct.valid_count() == int((y >= 0).sum())
+        assert abs(loss - l_ref) <= lim_l * abs(l_ref) + 1e-6
+        g = ct.grads()
+        worst = max((rel(g[nm], g_ref[nm]), nm) for nm in g_ref)
+        assert worst[0] <= lim_g, (dtype, worst)
+        before = ct.get_weights()
+        ct.step(x, y)
+        after = ct.get_weights()
+        assert set(after) == set(ct.pnames) and any(not np.array_equal(before[n], after[n]) for n in after)
