@@ -34,6 +34,23 @@ def _nvcc() -> str:
     return "nvcc"
 
 
+def _nccl_paths():
+    """Include and library directory of the NCCL that PyTorch itself loads (the
+    `nvidia.nccl` wheel), so that a process importing both torch and this engine
+    ends up with one NCCL; the system NCCL is the fallback."""
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("nvidia.nccl")
+        if spec and spec.submodule_search_locations:
+            base = list(spec.submodule_search_locations)[0]
+            inc, lib = os.path.join(base, "include"), os.path.join(base, "lib")
+            if os.path.exists(os.path.join(inc, "nccl.h")) and os.path.exists(os.path.join(lib, "libnccl.so.2")):
+                return inc, lib
+    except (ImportError, ValueError):
+        pass
+    return None, None
+
+
 def _digest() -> str:
     h = hashlib.sha256()
     for root in (CSRC, os.path.join(HERE, "..", "include")):
@@ -52,10 +69,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and os.path.exists(LIB) and os.path.exists(stamp) and open(stamp).read() == dig:
         return LIB
     nvcc = _nvcc()
+    nccl_inc, nccl_lib = _nccl_paths()
+    inc_flags = ["-I", nccl_inc] if nccl_inc else []
 
     def compile_one(src):
         obj = os.path.join(LIBDIR, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-Xptxas", "-v" if verbose else "-warn-spills", "-c",
+        cmd = [nvcc, *NVCC_FLAGS, *inc_flags, "-Xptxas", "-v" if verbose else "-warn-spills", "-c",
                os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -66,7 +85,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    link = [nvcc, "-shared", "-o", LIB, *objs, "-lnccl", "-cudart", "static"]
+    if nccl_lib:
+        nccl_link = ["-L", nccl_lib, "-l:libnccl.so.2", "-Xlinker", f"-rpath={nccl_lib}"]
+    else:
+        nccl_link = ["-lnccl"]
+    link = [nvcc, "-shared", "-o", LIB, *objs, *nccl_link, "-cudart", "static"]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

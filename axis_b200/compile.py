@@ -285,7 +285,7 @@ class CompiledTransformer:
         dh_ = A(N * MLP, isz); dg_ = A(N * MLP, isz); du_ = A(N * MLP, isz)
         dat2 = A(N * H * DH, isz); dq = A(N * H * DH, isz)
         dk = A(N * KV * DH, isz); dv = A(N * KV * DH, isz)
-        bD = A(N * H)
+        bD = A(N * H + (N * H * DH if hf else 0))     # row dots, then the fp32 dQ accumulator of the bf16 path
         if lora:
             u_l = {(i, pref): A(N * lora_r, isz) for i in range(L) for pref in lin_geom
                    if pref.split(".")[-1] in lset}

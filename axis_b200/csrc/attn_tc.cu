@@ -1,7 +1,536 @@
-// tcgen05 flash attention (placeholder until the kernels land): reports
-// "not served" so that the dispatcher uses the general attention kernels.
+// Causal grouped-query flash attention on the 5th-generation tensor cores
+// (tcgen05 + TMEM), bf16, head_dim 64, on the [B,T,H,DH] layout that the
+// projections produce.  Q/K/V/dO tiles arrive by TMA (128-byte swizzle, no
+// multicast); scores and gradients live in TMEM; probabilities go back into
+// TMEM as packed bf16 and feed the next MMA as its A operand.
+//
+// Forward:  one CTA per (128 queries, head, batch).  S = Q K^T -> online
+//   softmax by 128 threads (one row each, lazy rescale) -> P (bf16, TMEM) ->
+//   O += P V.  Saves LSE (natural log) for the backward.
+// Backward: one CTA per (128 keys, kv head, batch).  K/V resident; loops over
+//   the group's query heads and the causal query tiles:
+//     S^T = K Q^T, dP^T = V dO^T            (TMEM, lanes = keys)
+//     P^T = exp2(S^T c - lse), dS^T = P^T (dP^T - D)
+//     dV += P^T dO, dK += dS^T Q            (A from TMEM; summed over the group)
+//     dQ  = dS K                            (A = dS^T staged in shared memory)
+//   dK/dV are written once (no atomics, GQA sum on chip); dQ tiles are added
+//   into an fp32 buffer with TMA reduce-add and converted afterwards.
+// Every mbarrier wait is bounded; on a timeout the kernel records a status
+// code, unwinds and frees its TMEM.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
 #include "kernels.h"
-int ax_attn_tc_init(void) { return 0; }
-int ax_attn_fwd_tc(const void*, const void*, const void*, void*, float*, const AttnShape&, int*, cudaStream_t) { return -1; }
-int ax_attn_bwd_tc(const void*, const void*, const void*, const void*, const void*, const float*, float*, void*, void*, void*,
-                   const AttnShape&, int*, cudaStream_t) { return -1; }
+#include "tc_common.cuh"
+
+#define AT 128                 // queries / keys per tile
+#define ADH 64                 // head dim served
+#define ATT_THREADS 160        // 4 softmax warps + 1 control warp
+#define STAT_FWD 0x200
+#define STAT_BWD 0x300
+#define LOG2E 1.4426950408889634f
+#define LN2 0.6931471805599453f
+
+__device__ __forceinline__ void named_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, uint32_t src, int x, int y, int z, int w) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// ════════════════════════════════ forward ═══════════════════════════════════
+struct FwdSmem {
+    static constexpr int Q = 0, K0 = 16384, V0 = K0 + 2 * 16384, BARS = V0 + 2 * 16384, TOTAL = BARS + 128 + 1024;
+};
+
+__global__ void __launch_bounds__(ATT_THREADS)
+k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse,
+              int T, int H, int KV, float scale, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sb = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BARS);
+    const uint32_t b_q = smem_u32(bars), b_kvf = b_q + 8, b_kve = b_kvf + 16, b_s = b_kve + 16, b_p = b_s + 8, b_o = b_p + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x;       // heavy tiles first
+    const int h = blockIdx.y, b = blockIdx.z, g = h / (H / KV);
+    const int nkt = qt + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_q, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(b_kvf + 8 * s, 1); mbar_init(b_kve + 8 * s, 1); }
+        mbar_init(b_s, 1); mbar_init(b_p, 128); mbar_init(b_o, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) { tmem_alloc(smem_u32(tmem_slot), 256); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_S = tmem, t_O = tmem + 128;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            bool ok = true;
+            constexpr uint32_t id_s = tc_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t id_pv = tc_idesc_bf16(128, 64, 0, 1);
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+            mbar_expect_tx(b_q, 16384);
+            tma_load_4d(sb + FwdSmem::Q, &tmQ, b_q, 0, h, qt * AT, b);
+            mbar_expect_tx(b_kvf, 32768);
+            tma_load_4d(sb + FwdSmem::K0, &tmK, b_kvf, 0, g, 0, b);
+            tma_load_4d(sb + FwdSmem::V0, &tmV, b_kvf, 0, g, 0, b);
+            if (!mbar_wait(b_q, 0)) ok = false;
+            for (int j = 0; j < nkt && ok; j++) {
+                const int s = j & 1;
+                if (!mbar_wait(b_kvf + 8 * s, (j >> 1) & 1) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sK = sb + FwdSmem::K0 + s * 16384, sV = sb + FwdSmem::V0 + s * 16384;
+#pragma unroll
+                for (int kk = 0; kk < ADH / 16; kk++)
+                    tc_mma_ss(t_S, tc_smem_desc(sb + FwdSmem::Q + kk * 32, 16, 1024), tc_smem_desc(sK + kk * 32, 16, 1024), id_s, kk != 0);
+                tc_commit(b_s);
+                if (j + 1 < nkt) {      // next K/V tile into the other stage, once PV(j-1) has released it
+                    const int s2 = s ^ 1;
+                    if (j >= 1 && !mbar_wait(b_kve + 8 * s2, ((j - 1) >> 1) & 1)) { ok = false; break; }
+                    mbar_expect_tx(b_kvf + 8 * s2, 32768);
+                    tma_load_4d(sb + FwdSmem::K0 + s2 * 16384, &tmK, b_kvf + 8 * s2, 0, g, (j + 1) * AT, b);
+                    tma_load_4d(sb + FwdSmem::V0 + s2 * 16384, &tmV, b_kvf + 8 * s2, 0, g, (j + 1) * AT, b);
+                }
+                if (!mbar_wait(b_p, j & 1) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < AT / 16; kk++)
+                    tc_mma_ts(t_O, t_S + kk * 8, tc_smem_desc(sV + kk * 2048, 16384, 1024), id_pv, (j | kk) != 0);
+                tc_commit(b_kve + 8 * s);
+                tc_commit(b_o);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_FWD | 1); }
+        }
+    } else {
+        const int r = threadIdx.x;                         // query row within the tile == TMEM lane
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = scale * LOG2E;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nkt && ok; j++) {
+            if (!mbar_wait(b_s, j & 1) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = j == qt;
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t v[32];
+                tmem_ld32(t_S + lane_base + ch * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 32; q++) {
+                    const float sv = __uint_as_float(v[q]) * c;
+                    if (!diag || ch * 32 + q <= r) mx = fmaxf(mx, sv);
+                }
+            }
+            if (j == 0) {
+                m_used = mx;
+            } else {
+                const bool need = mx > m_used + 8.f;
+                if (__any_sync(0xffffffffu, need)) {
+                    // rescale this warp's rows of O; PV(j-1) must have landed first
+                    if (!mbar_wait(b_o, (j - 1) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const float m_new = fmaxf(m_used, mx);
+                    const float f = fast_exp2(m_used - m_new);
+                    m_used = m_new;
+                    l *= f;
+#pragma unroll 1
+                    for (int ch = 0; ch < 2; ch++) {
+                        uint32_t v[32];
+                        tmem_ld32(t_O + lane_base + ch * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 32; q++) v[q] = __float_as_uint(__uint_as_float(v[q]) * f);
+                        tmem_st16(t_O + lane_base + ch * 32, v);
+                        tmem_st16(t_O + lane_base + ch * 32 + 16, v + 16);
+                    }
+                    tmem_st_wait();
+                }
+            }
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t v[32], w[16];
+                tmem_ld32(t_S + lane_base + ch * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 32; q += 2) {
+                    float p0 = fast_exp2(__uint_as_float(v[q]) * c - m_used);
+                    float p1 = fast_exp2(__uint_as_float(v[q + 1]) * c - m_used);
+                    if (diag) { if (ch * 32 + q > r) p0 = 0.f; if (ch * 32 + q + 1 > r) p1 = 0.f; }
+                    l += p0 + p1;
+                    w[q >> 1] = pack_bf16(p0, p1);
+                }
+                tmem_st16(t_S + lane_base + ch * 16, w);       // P overwrites S columns already consumed
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(b_p);
+        }
+        if (ok && mbar_wait(b_o, (nkt - 1) & 1)) {
+            tc_fence_after();
+            const int t = qt * AT + r;
+            const float il = 1.f / l;
+            bf16* orow = o + (((long long)b * T + t) * H + h) * ADH;
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ch++) {
+                uint32_t v[32];
+                tmem_ld32(t_O + lane_base + ch * 32, v);
+                tmem_ld_wait();
+                if (t < T) {
+#pragma unroll
+                    for (int q = 0; q < 32; q += 8) {
+                        uint4 pk;
+                        pk.x = pack_bf16(__uint_as_float(v[q]) * il, __uint_as_float(v[q + 1]) * il);
+                        pk.y = pack_bf16(__uint_as_float(v[q + 2]) * il, __uint_as_float(v[q + 3]) * il);
+                        pk.z = pack_bf16(__uint_as_float(v[q + 4]) * il, __uint_as_float(v[q + 5]) * il);
+                        pk.w = pack_bf16(__uint_as_float(v[q + 6]) * il, __uint_as_float(v[q + 7]) * il);
+                        *reinterpret_cast<uint4*>(orow + ch * 32 + q) = pk;
+                    }
+                }
+            }
+            if (t < T) lse[((long long)b * H + h) * T + t] = (m_used + log2f(l)) * LN2;
+        } else if (lane == 0) {
+            *abort_flag = 1;
+            atomicExch(status, STAT_FWD | 2);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 256); }
+}
+
+// ════════════════════════════════ backward ══════════════════════════════════
+// D[b,h,t] = sum_d dO*O on the [B,T,H,DH] layout, written as [B,H,T]; one warp per row.
+__global__ void k_attn_bwd_prep(const bf16* __restrict__ o, const bf16* __restrict__ dO, float* __restrict__ Dv,
+                                int B, int T, int H) {
+    const int lane = threadIdx.x & 31;
+    const long long rows = (long long)B * T * H;
+    const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += wstride) {
+        const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + row * ADH)[lane];
+        const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(dO + row * ADH)[lane];
+        const float2 fa = __bfloat1622float2(a), fg = __bfloat1622float2(g);
+        float acc = warp_sum(fa.x * fg.x + fa.y * fg.y);
+        if (!lane) {
+            const int hh = (int)(row % H);
+            const long long bt = row / H;
+            const int t = (int)(bt % T), bb = (int)(bt / T);
+            Dv[((long long)bb * H + hh) * T + t] = acc;
+        }
+    }
+}
+
+struct BwdSmem {
+    static constexpr int K = 0, V = 16384, Q0 = 32768, DO0 = Q0 + 2 * 16384, DS = DO0 + 2 * 16384, DQ = DS + 32768,
+                         LSE = DQ + 32768, DD = LSE + 2 * 512, BARS = DD + 2 * 512, TOTAL = BARS + 128 + 1024;
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+              const __grid_constant__ CUtensorMap tmdQ, const float* __restrict__ lse, const float* __restrict__ Dv,
+              bf16* __restrict__ dk, bf16* __restrict__ dv, int T, int H, int KV, float scale, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sb = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
+    // kv_full, q_full[2], q_empty[2], sdp_full, pds_full, dq_full
+    const uint32_t b_kv = smem_u32(bars), b_qf = b_kv + 8, b_qe = b_qf + 16, b_sdp = b_qe + 16, b_pds = b_sdp + 8, b_dq = b_pds + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* s_lse = reinterpret_cast<float*>(smem + BwdSmem::LSE);     // [2][128], pre-multiplied by log2(e)
+    float* s_D = reinterpret_cast<float*>(smem + BwdSmem::DD);        // [2][128]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x, g = blockIdx.y, b = blockIdx.z;         // key tile (0 = most work), kv head, batch
+    const int rep = H / KV, nqt = T / AT;
+    const int per_head = nqt - j;                                     // causal: query tiles j .. nqt-1
+    const int n_it = rep * per_head;
+
+    if (threadIdx.x == 0) {
+        mbar_init(b_kv, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 1); }
+        mbar_init(b_sdp, 1); mbar_init(b_pds, 128); mbar_init(b_dq, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_S = tmem, t_dP = tmem + 128, t_dV = tmem + 256, t_dK = tmem + 320, t_dQ = tmem + 384;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            bool ok = true;
+            constexpr uint32_t id_s = tc_idesc_bf16(128, 128, 0, 0);       // S^T = K Q^T, dP^T = V dO^T
+            constexpr uint32_t id_acc = tc_idesc_bf16(128, 64, 0, 1);      // dV/dK: A in TMEM, B N-major
+            constexpr uint32_t id_dq = tc_idesc_bf16(128, 64, 1, 1);       // dQ: A M-major (dS^T in smem), B N-major
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+            mbar_expect_tx(b_kv, 32768);
+            tma_load_4d(sb + BwdSmem::K, &tmK, b_kv, 0, g, j * AT, b);
+            tma_load_4d(sb + BwdSmem::V, &tmV, b_kv, 0, g, j * AT, b);
+            auto load_q = [&](int it) {
+                const int s = it & 1, hh = it / per_head, i = j + it % per_head, h = g * rep + hh;
+                mbar_expect_tx(b_qf + 8 * s, 32768);
+                tma_load_4d(sb + BwdSmem::Q0 + s * 16384, &tmQ, b_qf + 8 * s, 0, h, i * AT, b);
+                tma_load_4d(sb + BwdSmem::DO0 + s * 16384, &tmdO, b_qf + 8 * s, 0, h, i * AT, b);
+            };
+            load_q(0);
+            if (!mbar_wait(b_kv, 0)) ok = false;
+            for (int it = 0; it < n_it && ok; it++) {
+                const int s = it & 1;
+                if (it + 1 < n_it) {        // prefetch the next Q/dO pair once its stage is free
+                    if (it >= 1 && !mbar_wait(b_qe + 8 * (s ^ 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
+                    load_q(it + 1);
+                }
+                if (!mbar_wait(b_qf + 8 * s, (it >> 1) & 1) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sQ = sb + BwdSmem::Q0 + s * 16384, sdO = sb + BwdSmem::DO0 + s * 16384;
+#pragma unroll
+                for (int kk = 0; kk < ADH / 16; kk++)
+                    tc_mma_ss(t_S, tc_smem_desc(sb + BwdSmem::K + kk * 32, 16, 1024), tc_smem_desc(sQ + kk * 32, 16, 1024), id_s, kk != 0);
+#pragma unroll
+                for (int kk = 0; kk < ADH / 16; kk++)
+                    tc_mma_ss(t_dP, tc_smem_desc(sb + BwdSmem::V + kk * 32, 16, 1024), tc_smem_desc(sdO + kk * 32, 16, 1024), id_s, kk != 0);
+                tc_commit(b_sdp);
+                if (!mbar_wait(b_pds, it & 1) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < AT / 16; kk++)       // dV += P^T dO   (k = queries)
+                    tc_mma_ts(t_dV, t_S + kk * 8, tc_smem_desc(sdO + kk * 2048, 16384, 1024), id_acc, (it | kk) != 0);
+#pragma unroll
+                for (int kk = 0; kk < AT / 16; kk++)       // dK += dS^T Q
+                    tc_mma_ts(t_dK, t_dP + kk * 8, tc_smem_desc(sQ + kk * 2048, 16384, 1024), id_acc, (it | kk) != 0);
+#pragma unroll
+                for (int kk = 0; kk < AT / 16; kk++)       // dQ = dS K      (k = keys)
+                    tc_mma_ss(t_dQ, tc_smem_desc(sb + BwdSmem::DS + kk * 2048, 16384, 1024),
+                              tc_smem_desc(sb + BwdSmem::K + kk * 2048, 16384, 1024), id_dq, kk != 0);
+                tc_commit(b_qe + 8 * s);
+                tc_commit(b_dq);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_BWD | 1); }
+        }
+    } else {
+        const int r = threadIdx.x;                          // key row of S^T / query row of dQ == TMEM lane
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const float c = scale * LOG2E;
+        bool ok = true;
+        // lse / D of the first query tile
+        {
+            const int h = g * rep, i = j;
+            s_lse[r] = lse[((long long)b * H + h) * T + i * AT + r] * LOG2E;
+            s_D[r] = Dv[((long long)b * H + h) * T + i * AT + r];
+        }
+        for (int it = 0; it < n_it && ok; it++) {
+            const int hh = it / per_head, i = j + it % per_head, h = g * rep + hh;
+            const int cur = it & 1;
+            float n_lse = 0.f, n_D = 0.f;
+            if (it + 1 < n_it) {        // prefetch the next tile's row statistics into registers
+                const int h2 = g * rep + (it + 1) / per_head, i2 = j + (it + 1) % per_head;
+                n_lse = lse[((long long)b * H + h2) * T + i2 * AT + r] * LOG2E;
+                n_D = Dv[((long long)b * H + h2) * T + i2 * AT + r];
+            }
+            named_bar_sync(1, 128);                            // s_lse/s_D[cur] visible to all rows
+            if (!mbar_wait(b_sdp, it & 1) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+            const bool diag = i == j;
+            const float* L = s_lse + cur * 128;
+            const float* Dr = s_D + cur * 128;
+            uint8_t* ds_row = smem + BwdSmem::DS + r * 128;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t sv[32], dp[32], wp[16], wd[16];
+                tmem_ld32(t_S + lane_base + ch * 32, sv);
+                tmem_ld32(t_dP + lane_base + ch * 32, dp);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 32; q += 2) {
+                    const int c0 = ch * 32 + q;                 // query column within the tile
+                    float p0 = fast_exp2(__uint_as_float(sv[q]) * c - L[c0]);
+                    float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - L[c0 + 1]);
+                    if (diag) { if (c0 < r) p0 = 0.f; if (c0 + 1 < r) p1 = 0.f; }      // query < key: masked
+                    const float d0 = p0 * (__uint_as_float(dp[q]) - Dr[c0]);
+                    const float d1 = p1 * (__uint_as_float(dp[q + 1]) - Dr[c0 + 1]);
+                    wp[q >> 1] = pack_bf16(p0, p1);
+                    wd[q >> 1] = pack_bf16(d0, d1);
+                }
+                tmem_st16(t_S + lane_base + ch * 16, wp);        // P^T over consumed S^T columns
+                tmem_st16(t_dP + lane_base + ch * 16, wd);       // dS^T over consumed dP^T columns
+                // dS^T also to shared memory, M-major (queries contiguous), 128-byte swizzle:
+                // half = query/64, 16-byte chunk (query%64)/8 XOR (row & 7)
+                const int half = ch >> 1;
+#pragma unroll
+                for (int k4 = 0; k4 < 4; k4++) {
+                    const int chunk = (ch & 1) * 4 + k4;
+                    uint4 pk = make_uint4(wd[k4 * 4], wd[k4 * 4 + 1], wd[k4 * 4 + 2], wd[k4 * 4 + 3]);
+                    *reinterpret_cast<uint4*>(ds_row + half * 16384 + ((chunk ^ (r & 7)) << 4)) = pk;
+                }
+            }
+            tmem_st_wait();
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(b_pds);
+            if (it + 1 < n_it) { s_lse[(cur ^ 1) * 128 + r] = n_lse; s_D[(cur ^ 1) * 128 + r] = n_D; }
+            // ── drain dQ(it): TMEM -> swizzled fp32 staging -> TMA reduce-add into the fp32 dq buffer ──
+            if (!mbar_wait(b_dq, it & 1) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+            if (threadIdx.x == 0) bulk_wait_read0();             // staging free again (previous reduce has read it)
+            named_bar_sync(1, 128);
+            uint8_t* dq_row = smem + BwdSmem::DQ + r * 128;
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ch++) {
+                uint32_t v[32];
+                tmem_ld32(t_dQ + lane_base + ch * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int k4 = 0; k4 < 8; k4++) {
+                    float4 f = make_float4(__uint_as_float(v[k4 * 4]) * scale, __uint_as_float(v[k4 * 4 + 1]) * scale,
+                                           __uint_as_float(v[k4 * 4 + 2]) * scale, __uint_as_float(v[k4 * 4 + 3]) * scale);
+                    *reinterpret_cast<float4*>(dq_row + ch * 16384 + ((k4 ^ (r & 7)) << 4)) = f;
+                }
+            }
+            fence_async_smem();
+            named_bar_sync(1, 128);
+            if (threadIdx.x == 0) {
+                tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ, 0, h, i * AT, b);
+                tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ + 16384, 32, h, i * AT, b);
+                bulk_commit();
+            }
+            tc_fence_before();
+        }
+        if (threadIdx.x == 0) bulk_wait0();
+        if (ok) {
+            // dV, dK complete once the last commit (dq_full of the last iteration) has fired — already waited.
+            const int t = j * AT + r;
+            bf16* kr = dk + (((long long)b * T + t) * KV + g) * ADH;
+            bf16* vr = dv + (((long long)b * T + t) * KV + g) * ADH;
+#pragma unroll 1
+            for (int which = 0; which < 2; which++) {
+                const uint32_t ta = which ? t_dK : t_dV;
+                const float f = which ? scale : 1.f;
+                bf16* dst = which ? kr : vr;
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ch++) {
+                    uint32_t v[32];
+                    tmem_ld32(ta + lane_base + ch * 32, v);
+                    tmem_ld_wait();
+                    if (t < T) {
+#pragma unroll
+                        for (int q = 0; q < 32; q += 8) {
+                            uint4 pk;
+                            pk.x = pack_bf16(__uint_as_float(v[q]) * f, __uint_as_float(v[q + 1]) * f);
+                            pk.y = pack_bf16(__uint_as_float(v[q + 2]) * f, __uint_as_float(v[q + 3]) * f);
+                            pk.z = pack_bf16(__uint_as_float(v[q + 4]) * f, __uint_as_float(v[q + 5]) * f);
+                            pk.w = pack_bf16(__uint_as_float(v[q + 6]) * f, __uint_as_float(v[q + 7]) * f);
+                            *reinterpret_cast<uint4*>(dst + ch * 32 + q) = pk;
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            *abort_flag = 1;
+            atomicExch(status, STAT_BWD | 2);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// fp32 dq accumulator -> bf16 dq (same [B,T,H,DH] layout)
+__global__ void k_dq_convert(const float* __restrict__ src, bf16* __restrict__ dst, long long n8) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        float f[8];
+        Vec<float>::ld(src + i * 8, f);
+        Vec<float>::ld(src + i * 8 + 4, f + 4);
+        Vec<bf16>::st(dst + i * 8, f);
+    }
+}
+
+// ── host ────────────────────────────────────────────────────────────────────
+int ax_attn_tc_init(void) {
+    int rc = 0;
+    rc |= (int)cudaFuncSetAttribute(k_attn_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::TOTAL);
+    rc |= (int)cudaFuncSetAttribute(k_attn_bwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
+    return rc;
+}
+
+static bool served(const AttnShape& s) {
+    // [B,T,H,DH] layout, head_dim 64, whole tiles
+    return s.DH == ADH && s.T % AT == 0 && s.T >= AT && s.qh == ADH && s.kh == ADH &&
+           s.qt == (long long)s.H * ADH && s.kt == (long long)s.KV * ADH && s.H % s.KV == 0;
+}
+static int map_bthd(CUtensorMap* m, const void* base, int B, int T, int heads) {
+    uint64_t dims[4] = {ADH, (uint64_t)heads, (uint64_t)T, (uint64_t)B};
+    uint64_t strides[3] = {(uint64_t)ADH * 2, (uint64_t)heads * ADH * 2, (uint64_t)T * heads * ADH * 2};
+    uint32_t box[4] = {ADH, 1, AT, 1};
+    return tc_make_tmap_bf16(m, base, 4, dims, strides, box, true);
+}
+static int map_dq_f32(CUtensorMap* m, const void* base, int B, int T, int heads) {
+    PFN_tmapEncodeTiled enc = tc_encode_fn();
+    if (!enc) return 1;
+    cuuint64_t gd[4] = {ADH, (cuuint64_t)heads, (cuuint64_t)T, (cuuint64_t)B};
+    cuuint64_t gs[3] = {(cuuint64_t)ADH * 4, (cuuint64_t)heads * ADH * 4, (cuuint64_t)T * heads * ADH * 4};
+    cuuint32_t bx[4] = {32, 1, AT, 1};
+    cuuint32_t es[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
+                   const AttnShape& s, int* status, cudaStream_t st) {
+    if (!served(s) || !lse || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return -1;
+    CUtensorMap tq, tk, tv;
+    if (map_bthd(&tq, q, s.B, s.T, s.H) || map_bthd(&tk, k, s.B, s.T, s.KV) || map_bthd(&tv, v, s.B, s.T, s.KV)) return 2;
+    dim3 grid(s.T / AT, s.H, s.B);
+    k_attn_fwd_tc<<<grid, ATT_THREADS, FwdSmem::TOTAL, st>>>(tq, tk, tv, (bf16*)o, lse, s.T, s.H, s.KV, s.scale, status);
+    return 0;
+}
+
+int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                   const float* lse, float* Dscratch, float* g_dq_acc, void* dq, void* dk, void* dv,
+                   const AttnShape& s, int* status, cudaStream_t st) {
+    if (!served(s) || !g_dq_acc || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) ||
+        !aligned16(dq) || !aligned16(dk) || !aligned16(dv) || !aligned16(g_dq_acc)) return -1;
+    const size_t need = (size_t)s.B * s.T * s.H * ADH * 4;
+    CUtensorMap tq, tk, tv, tdo, tdq;
+    if (map_bthd(&tq, q, s.B, s.T, s.H) || map_bthd(&tk, k, s.B, s.T, s.KV) || map_bthd(&tv, v, s.B, s.T, s.KV) ||
+        map_bthd(&tdo, dO, s.B, s.T, s.H) || map_dq_f32(&tdq, g_dq_acc, s.B, s.T, s.H)) return 2;
+    cudaMemsetAsync(g_dq_acc, 0, need, st);
+    const long long rows = (long long)s.B * s.T * s.H;
+    k_attn_bwd_prep<<<ew_grid(rows * 32, 256), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, Dscratch, s.B, s.T, s.H);
+    dim3 grid(s.T / AT, s.KV, s.B);
+    k_attn_bwd_tc<<<grid, ATT_THREADS, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, lse, Dscratch, (bf16*)dk, (bf16*)dv,
+                                                              s.T, s.H, s.KV, s.scale, status);
+    const long long n8 = rows * ADH / 8;
+    k_dq_convert<<<ew_grid(n8, 256), 256, 0, st>>>(g_dq_acc, (bf16*)dq, n8);
+    return 0;
+}

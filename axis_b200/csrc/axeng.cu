@@ -548,9 +548,12 @@ static int exec_op(const EngOp* op) {
             NEED(op->tb, qe * es); NEED(op->sc, ke * es); NEED(op->oa, ke * es);
             AttnShape s = shape_bthd(B, H, KV, T, DH, op->alpha);
             if (dt == 1 && !(G.fallback & 2)) {
+                // the tensor-core path needs an fp32 dQ accumulator behind the D scratch in the same buffer
+                const long long dwords = (long long)B * H * T;
+                float* dq_acc = have(op->oc, (dwords + qe) * 4) ? (float*)BUFP(op->oc) + dwords : nullptr;
                 const int rc = ax_attn_bwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->sb), BUFP(op->c), (const float*)BUFP(op->sa),
-                                              (float*)BUFP(op->oc), BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, G.d_status, st);
-                if (rc == 0) { G.launches += 2; return 0; }
+                                              (float*)BUFP(op->oc), dq_acc, BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, G.d_status, st);
+                if (rc == 0) { G.launches += 4; return 0; }
                 if (rc > 0) return rc;
             }
             G.launches += 3;

@@ -77,7 +77,8 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
     ROPE_BTHD: a=x b=cos d=sin c=out on [batch=B, m=T, k=heads, n=DH]; tb=1 inverse
     ATTN_FWD:  a=q [B,T,H,DH] b=k d=v [B,T,KV,DH] c=o; sa=lse [B,H,T];
                m=T n=DH k=KV batch=B tb=H; alpha=scale
-    ATTN_BWD:  a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=D scratch;
+    ATTN_BWD:  a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=scratch (B*H*T
+               floats, plus B*T*H*DH floats to enable the tensor-core path);
                m=T n=DH k=KV batch=B; alpha=scale; outputs in storage dtype
     RMSNORM_BWD_ACC: a=x b=w d=g c=dx; tb=residual added to dx; sa=dw (fp32);
                sb=scratch; m=N n=D; alpha=eps

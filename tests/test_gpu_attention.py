@@ -48,7 +48,9 @@ def make(rng, B, H, KV, T, DH, dt):
     return q, k, v, do
 
 
-CASES = [(2, 4, 2, 32, 32), (1, 6, 2, 17, 16), (2, 2, 2, 64, 64), (1, 4, 1, 40, 128), (1, 3, 3, 130, 64)]
+CASES = [(2, 4, 2, 32, 32), (1, 6, 2, 17, 16), (2, 2, 2, 64, 64), (1, 4, 1, 40, 128), (1, 3, 3, 130, 64),
+         # head_dim 64 with whole 128-token tiles: the tcgen05 kernels when fallback == 0
+         (1, 4, 4, 128, 64), (2, 6, 2, 256, 64), (2, 3, 1, 384, 64), (1, 4, 2, 1024, 64)]
 
 
 @pytest.mark.parametrize("dt", [0, 1])
@@ -112,9 +114,14 @@ def test_reference_layout_flash_ops(eng):
     assert rel(eng.download(idv, k.shape), dv_ref) <= 2e-2
 
 
-def test_attention_backward_is_deterministic(eng):
+@pytest.mark.parametrize("fallback", [0, 2])
+def test_attention_backward_is_deterministic(eng, fallback):
+    """dK/dV are summed on chip in a fixed order in both paths.  dQ is bit-stable in the
+    general path; the tensor-core path adds its per-key-tile dQ pieces with an unordered
+    fp32 reduce-add (as the reference's atomics do), so dQ is only checked there for
+    closeness."""
     rng = np.random.default_rng(1)
-    B, H, KV, T, DH = 1, 6, 2, 128, 64
+    B, H, KV, T, DH = 1, 6, 2, 256, 64
     q, k, v, do = make(rng, B, H, KV, T, DH, 1)
     t = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1, 3))
     iq, ik, iv, ido = put(eng, t(q), 1), put(eng, t(k), 1), put(eng, t(v), 1), put(eng, t(do), 1)
@@ -123,9 +130,17 @@ def test_attention_backward_is_deterministic(eng):
     plan = [op(E.ATTN_FWD, a=iq, b=ik, d=iv, c=io, sa=ilse, m=T, n=DH, k=KV, batch=B, tb=H, dt=1, alpha=0.125),
             op(E.ATTN_BWD, a=iq, b=ik, d=iv, c=ido, sa=ilse, sb=io, tb=idq, sc=idk, oa=idv, ob=H, oc=iD,
                m=T, n=DH, k=KV, batch=B, dt=1, alpha=0.125)]
+    eng.set_fallback(fallback)
     eng.run(plan)
     first = [eng.download_raw(i, n, np.uint16) for i, n in ((idq, q.size), (idk, k.size), (idv, k.size))]
     for _ in range(3):
         eng.run(plan)
-        for f, (i, n) in zip(first, ((idq, q.size), (idk, k.size), (idv, k.size))):
-            assert np.array_equal(f, eng.download_raw(i, n, np.uint16))
+        for which, (f, (i, n)) in enumerate(zip(first, ((idq, q.size), (idk, k.size), (idv, k.size)))):
+            again = eng.download_raw(i, n, np.uint16)
+            if which == 0 and fallback == 0:
+                a, b2 = E.bf16_bits_to_f32(f), E.bf16_bits_to_f32(again)
+                assert np.abs(a - b2).max() <= 1e-2 * np.abs(a).max()
+            else:
+                assert np.array_equal(f, again)
+    eng.set_fallback(0)
+    assert eng.device_status() == 0
