@@ -1,6 +1,8 @@
 // RMSNorm forward/backward.  HBM-bound: each row is read once from DRAM (the
 // second sweep of a row hits L1/L2) and written once; reductions are warp
 // shuffles + one shared-memory hop; fp32 math on fp32 or bf16 storage.
+#include <cstdio>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -218,4 +220,45 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
 #undef RB_LAUNCH
     if (dw) k_colsum_partials<<<(dim + 127) / 128, 128, 0, st>>>(scratch, dw, nb, dim);
     return 0;
+}
+
+// ── allocation-free variant of the fused RMSNorm backward ──────────────────
+// The per-block dw partials normally live in a scratch buffer that the caller
+// allocates.  Some callers cannot allocate: code that runs while a stream is
+// being captured into a CUDA graph (cudaMalloc is illegal there), hosts that
+// hand this library a fixed memory budget carved up at start-up, and latency
+// sensitive loops where an allocator call (and its implicit synchronisation)
+// is not acceptable.  For them the partials live in this file-scope device
+// array instead: RB_BLOCKS x AX_NOALLOC_MAX_DIM floats (about 9.7 MB), held by
+// every GPU that loads the library until the process exits.
+#define AX_NOALLOC_MAX_DIM 8192
+#define AX_NOALLOC_MAX_DEVICES 64
+static __device__ __align__(256) float g_noalloc_partials[RB_BLOCKS * AX_NOALLOC_MAX_DIM];
+// Device address of the array per device ordinal.  In host code the symbol
+// g_noalloc_partials is only a handle, not a pointer a kernel can follow, so
+// the address is looked up once per device with that device current.
+static float* g_noalloc_addr[AX_NOALLOC_MAX_DEVICES];
+
+extern "C" __attribute__((visibility("default")))
+int eng_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* g, const void* res, void* dx, float* dw,
+                            int rows, int dim, int dt, float eps, void* stream) {
+    if (!x || !w || !g || !dx || rows < 0 || dim <= 0 || (dt != 0 && dt != 1)) return 202;
+    if (dim > AX_NOALLOC_MAX_DIM) {
+        fprintf(stderr, "eng_rmsnorm_bwd_noalloc: dim %d exceeds the built-in scratch (max %d)\n", dim, AX_NOALLOC_MAX_DIM);
+        return 201;
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= AX_NOALLOC_MAX_DEVICES) return 203;
+    if (!g_noalloc_addr[dev]) {
+        // first call on this device: resolve the array's device address (not a stream operation;
+        // make this first call before any stream capture starts)
+        float* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_noalloc_partials) != cudaSuccess || !p) { cudaGetLastError(); return 203; }
+        g_noalloc_addr[dev] = p;
+    }
+    // Nothing in the scratch has to start at zero: the first kernel overwrites rows
+    // [0, blocks) x [0, dim) of it and the second reads exactly those.
+    const int rc = ax_rmsnorm_bwd_acc(dt, x, w, g, res, dx, dw, g_noalloc_addr[dev], rows, dim, eps, (cudaStream_t)stream);
+    if (rc) return rc;
+    return cudaPeekAtLastError() == cudaSuccess ? 0 : 204;
 }

@@ -145,6 +145,32 @@ int eng_set_fallback(int mask);
 /* Bytes currently allocated through eng_alloc*. */
 long long eng_bytes_allocated(void);
 
+/* Fused RMSNorm backward that allocates nothing (no counterpart in the
+ * reference).  dx = (res ? res : 0) + d(rmsnorm)/dx, dw = sum over rows of
+ * g * x * inv_rms, on caller-owned DEVICE pointers, enqueued on `stream`
+ * (a cudaStream_t; NULL = default stream).  x, g, res, dx: [rows, dim] in the
+ * storage type dt (0 = fp32, 1 = bf16); w: [dim] in dt; dw: [dim] fp32 or NULL;
+ * res may be NULL.  It needs no eng_init and no engine buffer.
+ *
+ * Who needs it: callers that must not allocate on the device — code running
+ * while a stream is being captured into a CUDA graph, hosts that give the
+ * library a fixed memory budget, and loops that cannot afford an allocator call
+ * and the synchronisation it implies.  The scratch that the reduction of dw
+ * needs (per-block column partials) lives in a static device array inside the
+ * library instead of a caller-provided buffer: 296 x 8192 floats, about 9.7 MB,
+ * resident on every GPU that loads the library until the process exits.
+ *
+ * Limits and rules: dim <= 8192 (larger: returns 201 and prints a message to
+ * stderr).  The first call on a device looks up the array's address once
+ * (with that device current); make that first call before starting any stream
+ * capture.  Every call uses the same array and leaves its partials there;
+ * nothing in it has to be cleared between calls, but two calls that overlap on
+ * the GPU (different streams, no ordering) race on it — serialise them.
+ * Returns 0, or 201 dim too large, 202 bad argument, 203 device/symbol lookup
+ * failed, 204 launch failed. */
+int eng_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* g, const void* res, void* dx, float* dw,
+                            int rows, int dim, int dt, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
