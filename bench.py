@@ -296,8 +296,11 @@ def main():
             "step_tflops": step_flops(c) * K / (ms_dev / 1e3) / 1e12 / 1.0,
             "device_status": eng.device_status()}
 
-    if RANK == 0 and not args.no_kernel_table:
-        line.update(kernel_table(ct, c, batches[0]))
+    if not args.no_kernel_table:
+        # every rank runs the profiled step (it contains the collectives); rank 0 reports
+        table = kernel_table(ct, c, batches[0])
+        if RANK == 0:
+            line.update(table)
     if RANK == 0 and not args.no_cpu_baseline and WORLD == 1:
         line["cpu_baseline"] = cpu_reference(c)
     barrier()
