@@ -103,7 +103,11 @@ API int eng_shutdown(void) { release_all(); return 0; }
 API const char* eng_last_error(void) { return G.err; }
 API int eng_has_flash(void) { return 1; }
 API int eng_set_tf32(int on) { G.tf32 = on; return 0; }
-API int eng_set_fallback(int mask) { G.fallback = mask; return 0; }
+API int eng_set_fallback(int mask) {
+    G.fallback = mask;
+    ax_gemm_set_mode((mask >> 2) & 3);      // 4: single-CTA GEMM only, 8: paired-CTA GEMM whenever possible
+    return 0;
+}
 API long long eng_bytes_allocated(void) { return G.bytes; }
 API int eng_sync(void) {
     int rc = (int)cudaStreamSynchronize(G.stream);

@@ -55,62 +55,14 @@ template <int BN> struct GemmCfg {
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <typename TO> __device__ __forceinline__ void epi_store(TO* crow, const TO* drow, const uint32_t* acc, int col0,
-                                                                  int ncols_valid, float alpha, float beta, bool vec_ok);
-template <> __device__ __forceinline__ void epi_store<bf16>(bf16* crow, const bf16* drow, const uint32_t* acc, int col0,
-                                                            int nvalid, float alpha, float beta, bool vec_ok) {
-    if (vec_ok && nvalid >= 32) {
-#pragma unroll
-        for (int v = 0; v < 4; v++) {
-            float f[8];
-#pragma unroll
-            for (int q = 0; q < 8; q++) f[q] = alpha * __uint_as_float(acc[v * 8 + q]);
-            if (drow) {
-                float d[8];
-                Vec<bf16>::ld(drow + col0 + v * 8, d);
-#pragma unroll
-                for (int q = 0; q < 8; q++) f[q] += beta * d[q];
-            }
-            Vec<bf16>::st(crow + col0 + v * 8, f);
-        }
-    } else {
-        for (int q = 0; q < 32 && q < nvalid; q++) {
-            float f = alpha * __uint_as_float(acc[q]);
-            if (drow) f += beta * __bfloat162float(drow[col0 + q]);
-            crow[col0 + q] = __float2bfloat16(f);
-        }
-    }
-}
-template <> __device__ __forceinline__ void epi_store<float>(float* crow, const float* drow, const uint32_t* acc, int col0,
-                                                             int nvalid, float alpha, float beta, bool vec_ok) {
-    if (vec_ok && nvalid >= 32) {
-#pragma unroll
-        for (int v = 0; v < 8; v++) {
-            float f[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++) f[q] = alpha * __uint_as_float(acc[v * 4 + q]);
-            if (drow) {
-                float d[4];
-                Vec<float>::ld(drow + col0 + v * 4, d);
-#pragma unroll
-                for (int q = 0; q < 4; q++) f[q] += beta * d[q];
-            }
-            Vec<float>::st(crow + col0 + v * 4, f);
-        }
-    } else {
-        for (int q = 0; q < 32 && q < nvalid; q++) {
-            float f = alpha * __uint_as_float(acc[q]);
-            if (drow) f += beta * drow[col0 + q];
-            crow[col0 + q] = f;
-        }
-    }
-}
+#include "gemm_epi.cuh"
 
 // A_MN / B_MN: 1 when that operand is MN-major in global memory (see header).
 template <int BN, int A_MN, int B_MN, typename TO>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-          TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status) {
+          TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status,
+          int ksplit, float* __restrict__ ws) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -126,7 +78,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
-    const int kblocks = (k + BK - 1) / BK;
+    const int kblocks_all = (k + BK - 1) / BK;
+    // split-K: unit u = (split, tile); split s covers k-blocks [s*kb_per, min(all, (s+1)*kb_per)) and
+    // writes raw fp32 partial sums to ws[s][m][n]; a second kernel adds the splits in order
+    const int kb_per = (kblocks_all + ksplit - 1) / ksplit;
+    const int num_units = num_tiles * ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
@@ -146,9 +102,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         // ── TMA producer ──
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+            const int tile = unit % num_tiles, split = unit / num_tiles;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
-            for (int kb = 0; kb < kblocks; kb++, it++) {
+            const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
+            for (int kb = kb0; kb < kb1; kb++, it++) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (it >= (uint32_t)STAGES && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
@@ -179,13 +137,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         constexpr uint32_t idesc = tc_idesc_bf16(BM, BN, A_MN, B_MN);
         uint32_t it = 0, tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, tcount++) {
+            const int split = unit / num_tiles;
+            const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
             if (tcount >= 2 && !mbar_wait(bar_tempty + 8 * acc, aph ^ 1)) { ok = false; break; }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
-            for (int kb = 0; kb < kblocks; kb++, it++) {
+            for (int kb = kb0; kb < kb1; kb++, it++) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait(bar_full + 8 * s, ph) || *abort_flag) { ok = false; break; }
@@ -196,7 +156,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                     // K-major: 16 k-elements = 32 bytes inside the 128-byte row; MN-major: 16 k-rows = 2048 bytes
                     const uint64_t ad = A_MN ? tc_smem_desc(sa + kk * 2048, 8192, 1024) : tc_smem_desc(sa + kk * 32, 16, 1024);
                     const uint64_t bd = B_MN ? tc_smem_desc(sb + kk * 2048, 8192, 1024) : tc_smem_desc(sb + kk * 32, 16, 1024);
-                    tc_mma_ss(d_tmem, ad, bd, idesc, (kb | kk) != 0);
+                    tc_mma_ss(d_tmem, ad, bd, idesc, (kb != kb0) || (kk != 0));
                 }
                 tc_commit(bar_empty + 8 * s);          // frees the stage when these MMAs finish
             }
@@ -210,7 +170,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         bool ok = true;
         const bool vec_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (n % (16 / (int)sizeof(TO))) == 0 &&
                             (!D || (reinterpret_cast<uintptr_t>(D) & 15) == 0);
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+        for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, tcount++) {
+            const int tile = unit % num_tiles, split = unit / num_tiles;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
@@ -220,13 +181,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
             TO* crow = C + (long long)row * n;
             const TO* drow = (D && beta != 0.f) ? D + (long long)row * n : nullptr;
+            float* wrow = ws + ((long long)split * m + row) * n;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
                 tmem_ld_wait();
                 const int col0 = tn * BN + c;
-                if (row < m && col0 < n) epi_store<TO>(crow, drow, r, col0, n - col0, alpha, beta, vec_ok);
+                if (row < m && col0 < n) {
+                    if (ksplit > 1) epi_store<float>(wrow, nullptr, r, col0, n - col0, 1.f, 0.f, (n & 3) == 0);
+                    else epi_store<TO>(crow, drow, r, col0, n - col0, alpha, beta, vec_ok);
+                }
             }
             tc_fence_before();
             mbar_arrive(bar_tempty + 8 * acc);
@@ -238,6 +203,38 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, Cfg::TMEM_COLS); }
 }
 
+// C = alpha * (ws[0] + ws[1] + ... in split order) + beta * D
+template <typename TO>
+__global__ void k_splitk_reduce(const float* __restrict__ ws, int ksplit, TO* __restrict__ C, const TO* D,
+                                long long mn, float alpha, float beta) {
+    const long long n4 = mn / 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 a = *reinterpret_cast<const float4*>(ws + i * 4);
+        for (int s = 1; s < ksplit; s++) {
+            const float4 b = *reinterpret_cast<const float4*>(ws + (long long)s * mn + i * 4);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        float f[4] = {alpha * a.x, alpha * a.y, alpha * a.z, alpha * a.w};
+        if (D && beta != 0.f)
+            for (int q = 0; q < 4; q++) f[q] += beta * ldf(D, i * 4 + q);
+        for (int q = 0; q < 4; q++) stf(C, i * 4 + q, f[q]);
+    }
+}
+
+static float* g_splitk_ws = nullptr;
+static const size_t SPLITK_WS_BYTES = 160u << 20;
+static int g_pair_mode = 0;        // 0 auto, 1 never use the paired-CTA kernel, 2 use it whenever the shape allows
+static int g_pairs_avail = 0;      // co-resident CTA pairs of the paired kernel (0 = unavailable)
+float* ax_splitk_ws(size_t* bytes) { if (bytes) *bytes = SPLITK_WS_BYTES; return g_splitk_ws; }
+void ax_gemm_set_mode(int mode) { g_pair_mode = mode; }
+template <typename TO>
+void ax_splitk_reduce_launch(const float* ws, int ksplit, TO* C, const TO* D, long long mn, float alpha, float beta, cudaStream_t st) {
+    k_splitk_reduce<TO><<<ew_grid(mn / 4, 256), 256, 0, st>>>(ws, ksplit, C, D, mn, alpha, beta);
+}
+template void ax_splitk_reduce_launch<bf16>(const float*, int, bf16*, const bf16*, long long, float, float, cudaStream_t);
+template void ax_splitk_reduce_launch<float>(const float*, int, float*, const float*, long long, float, float, cudaStream_t);
+
 template <int BN, int A_MN, int B_MN, typename TO>
 static int gemm_set_attr() {
     return (int)cudaFuncSetAttribute(k_gemm_tc<BN, A_MN, B_MN, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM);
@@ -245,6 +242,9 @@ static int gemm_set_attr() {
 int ax_gemm_tc_init(void) {
     if (!tc_encode_fn()) return 1;
     int rc = 0;
+    if (!g_splitk_ws && cudaMalloc(&g_splitk_ws, SPLITK_WS_BYTES) != cudaSuccess) { g_splitk_ws = nullptr; cudaGetLastError(); }
+    g_pairs_avail = ax_gemm_tc2_init();
+    if (g_pairs_avail < 1) g_pairs_avail = 0;
     rc |= gemm_set_attr<128, 0, 1, bf16>(); rc |= gemm_set_attr<256, 0, 1, bf16>();
     rc |= gemm_set_attr<128, 0, 0, bf16>(); rc |= gemm_set_attr<256, 0, 0, bf16>();
     rc |= gemm_set_attr<128, 1, 1, bf16>(); rc |= gemm_set_attr<256, 1, 1, bf16>();
@@ -256,7 +256,7 @@ int ax_gemm_tc_init(void) {
 
 template <int BN, int A_MN, int B_MN, typename TO>
 static int gemm_launch(const void* A, const void* B, void* C, const void* D, int m, int n, int k,
-                       float alpha, float beta, int* status, cudaStream_t st) {
+                       float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
     CUtensorMap tmA, tmB;
     {
         // A: K-major [m,k] -> dims {k, m}, box {64, 128};  M-major [k,m] -> dims {m, k}, box {64, 64}
@@ -269,9 +269,14 @@ static int gemm_launch(const void* A, const void* B, void* C, const void* D, int
         else { dims[0] = k; dims[1] = n; strides[0] = (uint64_t)k * 2; box[0] = BK; box[1] = BN; }
         if (tc_make_tmap_bf16(&tmB, B, 2, dims, strides, box, true)) return 2;
     }
-    const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-    const int grid = tiles < AX_SMS ? tiles : AX_SMS;
-    k_gemm_tc<BN, A_MN, B_MN, TO><<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM, st>>>(tmA, tmB, (TO*)C, (const TO*)D, m, n, k, alpha, beta, status);
+    const int units = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * ksplit;
+    const int grid = units < AX_SMS ? units : AX_SMS;
+    k_gemm_tc<BN, A_MN, B_MN, TO><<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM, st>>>(tmA, tmB, (TO*)C, (const TO*)D, m, n, k, alpha, beta,
+                                                                                 status, ksplit, g_splitk_ws);
+    if (ksplit > 1) {
+        const long long mn = (long long)m * n;
+        k_splitk_reduce<TO><<<ew_grid(mn / 4, 256), 256, 0, st>>>(g_splitk_ws, ksplit, (TO*)C, (const TO*)D, mn, alpha, beta);
+    }
     return 0;
 }
 
@@ -284,15 +289,46 @@ int ax_gemm_tc(int out_bf16, int tb, const void* A, const void* B, void* C, cons
     if (tb == 0) { if (k % 8 || n % 8) return -1; }
     else if (tb == 1) { if (k % 8) return -1; }
     else { if (m % 8 || n % 8) return -1; }
-    // BN = 256 when it does not leave SMs idle compared with 128
-    const long long t256 = (long long)((m + BM - 1) / BM) * ((n + 255) / 256);
-    const long long t128 = (long long)((m + BM - 1) / BM) * ((n + 127) / 128);
+    // Tile width and split-K factor from a small cost model (unit: one 128x256 k-block):
+    // waves(units) * k-blocks per unit * cost(BN) + the split-K reduction traffic.
+    const int kblocks = (k + BK - 1) / BK;
+    const long long tm_ = (m + BM - 1) / BM;
     auto waves = [](long long t) { return (t + AX_SMS - 1) / AX_SMS; };
-    // a 256-wide tile costs two 128-wide ones; prefer it on ties (fewer smem reads per flop)
-    const bool use256 = n >= 256 && waves(t256) * 2 <= waves(t128);
+    int best_bn = 128, best_s = 1;
+    double best = 1e30;
+    for (int bn = 128; bn <= 256; bn += 128) {
+        if (bn == 256 && n < 256) break;
+        const long long tiles = tm_ * ((n + bn - 1) / bn);
+        for (int sk = 1; sk <= 4; sk++) {
+            if (sk > 1 && (kblocks < 16 * sk || (n & 3) || !g_splitk_ws ||
+                           (size_t)sk * m * n * 4 > SPLITK_WS_BYTES)) break;
+            const double per_kb = bn == 256 ? 1.0 : 0.72;
+            double cost = (double)waves(tiles * sk) * ((kblocks + sk - 1) / sk) * per_kb;
+            if (sk > 1) cost += (2.0 * sk + 1.0) * m * n * 4.0 / 4.0e12 / 0.45e-6 + 4.0;   // reduce pass, in k-block units
+            if (cost < best - 1e-9) { best = cost; best_bn = bn; best_s = sk; }
+        }
+    }
+    const bool use256 = best_bn == 256;
+    int ks = best_s;
+    // paired-CTA kernel (256 x 256 tile per two SMs): same cost model, cheaper k-blocks
+    if (g_pair_mode != 1 && g_pairs_avail > 0 && m >= 256 && n >= 256) {
+        const long long tiles2 = (long long)((m + 255) / 256) * ((n + 255) / 256);
+        int best2_s = 1;
+        double best2 = 1e30;
+        for (int sk = 1; sk <= 4; sk++) {
+            if (sk > 1 && (kblocks < 16 * sk || (n & 3) || !g_splitk_ws || (size_t)sk * m * n * 4 > SPLITK_WS_BYTES)) break;
+            double cost = (double)((tiles2 * sk + g_pairs_avail - 1) / g_pairs_avail) * ((kblocks + sk - 1) / sk) * 0.70;
+            if (sk > 1) cost += (2.0 * sk + 1.0) * m * n * 4.0 / 4.0e12 / 0.45e-6 + 4.0;
+            if (cost < best2 - 1e-9) { best2 = cost; best2_s = sk; }
+        }
+        if (g_pair_mode == 2 || best2 < best) {
+            const int rc = ax_gemm_tc2(out_bf16, tb, A, B, C, D, m, n, k, alpha, beta, status, best2_s, st);
+            if (rc >= 0) return rc;
+        }
+    }
 #define GL(BN_, AM, BMj)                                                                                       \
-    (out_bf16 ? gemm_launch<BN_, AM, BMj, bf16>(A, B, C, D, m, n, k, alpha, beta, status, st)                \
-              : gemm_launch<BN_, AM, BMj, float>(A, B, C, D, m, n, k, alpha, beta, status, st))
+    (out_bf16 ? gemm_launch<BN_, AM, BMj, bf16>(A, B, C, D, m, n, k, alpha, beta, status, ks, st)            \
+              : gemm_launch<BN_, AM, BMj, float>(A, B, C, D, m, n, k, alpha, beta, status, ks, st))
     if (tb == 0) return use256 ? GL(256, 0, 1) : GL(128, 0, 1);
     if (tb == 1) return use256 ? GL(256, 0, 0) : GL(128, 0, 0);
     return use256 ? GL(256, 1, 1) : GL(128, 1, 1);

@@ -1,0 +1,297 @@
+// bf16 GEMM with paired CTAs (tcgen05 cta_group::2): a cluster of two CTAs on
+// neighbouring SMs computes one 256 x 256 output tile.  Each CTA loads its own
+// 128 rows of A and its own 128 columns of B (plain TMA tile loads — nothing is
+// multicast; the pair shares B through the MMA unit, which reads both CTAs'
+// shared memory), so a k-block costs 32 KB of L2->smem traffic per SM instead of
+// the 48 KB of the single-CTA 128 x 256 tile, and half the smem operand reads
+// per flop.  CTA 0 of the pair issues the MMAs (M = 256); accumulators live in
+// both CTAs' TMEM (128 lanes x 256 columns each, double-buffered); completion is
+// signalled to both CTAs with multicast commits; every CTA writes its own 128
+// rows of C.
+//
+// Same operand layouts, epilogue and split-K scheme as the single-CTA kernel.
+// All mbarrier waits are bounded.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "gemm_epi.cuh"
+#include "kernels.h"
+#include "tc_common.cuh"
+
+#define BM2 128            // rows per CTA (256 per pair)
+#define BN2 256            // columns per pair (128 loaded by each CTA)
+#define BK2 64
+#define STAGES2 6
+#define THREADS2 192
+#define STAT_GEMM2 0x400
+#define A_BYTES2 (BM2 * BK2 * 2)
+#define B_BYTES2 (128 * BK2 * 2)
+#define STAGE_BYTES2 (A_BYTES2 + B_BYTES2)
+#define SMEM2 (STAGES2 * STAGE_BYTES2 + 1024 + 256)
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tile load whose completion is counted on an mbarrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ss2(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair once all prior MMAs finish
+__device__ __forceinline__ void tc_commit2(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+
+template <int A_MN, int B_MN, typename TO>
+__global__ void __launch_bounds__(THREADS2, 1)
+k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+           TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status,
+           int ksplit, float* __restrict__ ws) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE_BYTES2);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES2;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES2, bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t smem_base = smem_u32(smem);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                 // 0 = leader (issues the MMAs)
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int tiles_m = (m + 2 * BM2 - 1) / (2 * BM2), tiles_n = (n + BN2 - 1) / BN2;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kblocks_all = (k + BK2 - 1) / BK2;
+    const int kb_per = (kblocks_all + ksplit - 1) / ksplit;
+    const int num_units = num_tiles * ksplit;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES2; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 256); }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) { tmem_alloc2(smem_u32(tmem_slot), 512); tmem_relinquish2(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                   // peer barriers are initialised before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t full_leader = map_to_cta(bar_full, 0);  // cluster address of the leader's full[0]
+    const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
+
+    if (warp == 0 && lane == 0) {
+        // ── TMA producer (both CTAs): own 128 rows of A, own 128 columns of B ──
+        uint32_t it = 0;
+        bool ok = true;
+        for (int unit = pair; unit < num_units && ok; unit += npairs) {
+            const int tile = unit % num_tiles, split = unit / num_tiles;
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
+            const int row0 = tm * 2 * BM2 + rank * BM2, col0 = tn * BN2 + rank * 128;
+            for (int kb = kb0; kb < kb1; kb++, it++) {
+                const int s = it % STAGES2;
+                const uint32_t ph = (it / STAGES2) & 1;
+                if (it >= (uint32_t)STAGES2 && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
+                if (*abort_flag) { ok = false; break; }
+                const uint32_t sa = smem_base + s * STAGE_BYTES2, sb = sa + A_BYTES2;
+                const uint32_t fb = full_leader + 8 * s;
+                if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * STAGE_BYTES2);   // both CTAs' bytes land on this barrier
+                if (A_MN) {
+#pragma unroll
+                    for (int b = 0; b < 2; b++) tma_load_2d_pair(sa + b * 8192, &tmA, fb, row0 + b * 64, kb * BK2);
+                } else {
+                    tma_load_2d_pair(sa, &tmA, fb, kb * BK2, row0);
+                }
+                if (B_MN) {
+#pragma unroll
+                    for (int b = 0; b < 2; b++) tma_load_2d_pair(sb + b * 8192, &tmB, fb, col0 + b * 64, kb * BK2);
+                } else {
+                    tma_load_2d_pair(sb, &tmB, fb, kb * BK2, col0);
+                }
+            }
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(status, STAT_GEMM2 | 1); }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ── MMA issuer (leader CTA only) ──
+        constexpr uint32_t idesc = tc_idesc_bf16(256, BN2, A_MN, B_MN);
+        uint32_t it = 0, tcount = 0;
+        bool ok = true;
+        for (int unit = pair; unit < num_units && ok; unit += npairs, tcount++) {
+            const int split = unit / num_tiles;
+            const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
+            const int acc = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            if (tcount >= 2 && !mbar_wait(bar_tempty + 8 * acc, aph ^ 1)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN2;
+            for (int kb = kb0; kb < kb1; kb++, it++) {
+                const int s = it % STAGES2;
+                const uint32_t ph = (it / STAGES2) & 1;
+                if (!mbar_wait(bar_full + 8 * s, ph) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t sa = smem_base + s * STAGE_BYTES2, sb = sa + A_BYTES2;
+#pragma unroll
+                for (int kk = 0; kk < BK2 / 16; kk++) {
+                    const uint64_t ad = A_MN ? tc_smem_desc(sa + kk * 2048, 8192, 1024) : tc_smem_desc(sa + kk * 32, 16, 1024);
+                    const uint64_t bd = B_MN ? tc_smem_desc(sb + kk * 2048, 8192, 1024) : tc_smem_desc(sb + kk * 32, 16, 1024);
+                    tc_mma_ss2(d_tmem, ad, bd, idesc, (kb != kb0) || (kk != 0));
+                }
+                tc_commit2(bar_empty + 8 * s);         // frees the stage in both CTAs
+            }
+            if (ok) tc_commit2(bar_tfull + 8 * acc);   // accumulator ready in both CTAs
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(status, STAT_GEMM2 | 2); }
+    } else if (warp >= 2) {
+        // ── epilogue (both CTAs): own 128 rows x 256 columns ──
+        const int quad = warp & 3;
+        uint32_t tcount = 0;
+        bool ok = true;
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (n % (16 / (int)sizeof(TO))) == 0 &&
+                            (!D || (reinterpret_cast<uintptr_t>(D) & 15) == 0);
+        for (int unit = pair; unit < num_units && ok; unit += npairs, tcount++) {
+            const int tile = unit % num_tiles, split = unit / num_tiles;
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const int acc = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            if (!mbar_wait(bar_tfull + 8 * acc, aph) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+            const int row = tm * 2 * BM2 + rank * BM2 + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * BN2 + ((uint32_t)(quad * 32) << 16);
+            TO* crow = C + (long long)row * n;
+            const TO* drow = (D && beta != 0.f) ? D + (long long)row * n : nullptr;
+            float* wrow = ws + ((long long)split * m + row) * n;
+#pragma unroll 1
+            for (int c = 0; c < BN2; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c, r);
+                tmem_ld_wait();
+                const int col0 = tn * BN2 + c;
+                if (row < m && col0 < n) {
+                    if (ksplit > 1) epi_store<float>(wrow, nullptr, r, col0, n - col0, 1.f, 0.f, (n & 3) == 0);
+                    else epi_store<TO>(crow, drow, r, col0, n - col0, alpha, beta, vec_ok);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(tempty_leader + 8 * acc);   // 256 arrivals (both CTAs) free the accumulator
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_GEMM2 | 3); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();                                    // nobody frees TMEM while the peer may still use the pair
+    if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc2(tmem_base, 512); }
+}
+
+// ── host ────────────────────────────────────────────────────────────────────
+extern float* ax_splitk_ws(size_t* bytes);
+template <typename TO>
+void ax_splitk_reduce_launch(const float* ws, int ksplit, TO* C, const TO* D, long long mn, float alpha, float beta, cudaStream_t st);
+
+static int g_pairs[3][2];          // max co-resident pairs per kernel variant (0 = unknown)
+
+template <int A_MN, int B_MN, typename TO>
+static int pairs_for(int slot, int tslot) {
+    if (g_pairs[slot][tslot] == 0) {
+        cudaFuncSetAttribute(k_gemm_tc2<A_MN, B_MN, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * AX_SMS, 1, 1);
+        cfg.blockDim = dim3(THREADS2, 1, 1);
+        cfg.dynamicSmemBytes = SMEM2;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int nc = 0;
+        if (cudaOccupancyMaxActiveClusters(&nc, k_gemm_tc2<A_MN, B_MN, TO>, &cfg) != cudaSuccess || nc < 1) { cudaGetLastError(); nc = -1; }
+        g_pairs[slot][tslot] = nc;
+    }
+    return g_pairs[slot][tslot];
+}
+
+template <int A_MN, int B_MN, typename TO>
+static int gemm2_launch(int slot, const void* A, const void* B, void* C, const void* D, int m, int n, int k,
+                        float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
+    const int maxp = pairs_for<A_MN, B_MN, TO>(slot, sizeof(TO) == 2 ? 0 : 1);
+    if (maxp < 1) return -1;
+    CUtensorMap tmA, tmB;
+    uint64_t dims[2], strides[1]; uint32_t box[2];
+    if (A_MN) { dims[0] = m; dims[1] = k; strides[0] = (uint64_t)m * 2; box[0] = 64; box[1] = BK2; }
+    else { dims[0] = k; dims[1] = m; strides[0] = (uint64_t)k * 2; box[0] = BK2; box[1] = BM2; }
+    if (tc_make_tmap_bf16(&tmA, A, 2, dims, strides, box, true)) return 2;
+    if (B_MN) { dims[0] = n; dims[1] = k; strides[0] = (uint64_t)n * 2; box[0] = 64; box[1] = BK2; }
+    else { dims[0] = k; dims[1] = n; strides[0] = (uint64_t)k * 2; box[0] = BK2; box[1] = 128; }
+    if (tc_make_tmap_bf16(&tmB, B, 2, dims, strides, box, true)) return 2;
+    const int units = ((m + 255) / 256) * ((n + 255) / 256) * ksplit;
+    const int pairs = units < maxp ? units : maxp;
+    size_t wsb = 0;
+    float* ws = ax_splitk_ws(&wsb);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(THREADS2, 1, 1);
+    cfg.dynamicSmemBytes = SMEM2;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    TO* Cp = (TO*)C; const TO* Dp = (const TO*)D;
+    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA, tmB, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws) != cudaSuccess) return 3;
+    if (ksplit > 1) ax_splitk_reduce_launch<TO>(ws, ksplit, Cp, Dp, (long long)m * n, alpha, beta, st);
+    return 0;
+}
+
+// Resolve the co-resident pair count of every variant up front (not while a graph is being captured).
+int ax_gemm_tc2_init(void) {
+    int worst = 1 << 30;
+    int v[6] = {pairs_for<0, 1, bf16>(0, 0), pairs_for<0, 1, float>(0, 1), pairs_for<0, 0, bf16>(1, 0),
+                pairs_for<0, 0, float>(1, 1), pairs_for<1, 1, bf16>(2, 0), pairs_for<1, 1, float>(2, 1)};
+    for (int i = 0; i < 6; i++) worst = v[i] < worst ? v[i] : worst;
+    return worst;      // pairs that can run together (<= 0: the paired kernel is unavailable)
+}
+
+// Same argument meaning as ax_gemm_tc; returns -1 when the paired kernel cannot run here.
+int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, const void* D,
+                int m, int n, int k, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
+    if (tb == 0) return out_bf16 ? gemm2_launch<0, 1, bf16>(0, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st)
+                                 : gemm2_launch<0, 1, float>(0, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st);
+    if (tb == 1) return out_bf16 ? gemm2_launch<0, 0, bf16>(1, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st)
+                                 : gemm2_launch<0, 0, float>(1, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st);
+    return out_bf16 ? gemm2_launch<1, 1, bf16>(2, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st)
+                    : gemm2_launch<1, 1, float>(2, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st);
+}

@@ -68,6 +68,12 @@ int ax_gemm_tc_init(void);
 int ax_gemm_tc(int out_bf16, int tb, const void* A, const void* B, void* C, const void* D,
                int m, int n, int k, float alpha, float beta, int* status, cudaStream_t st);
 
+// gemm_tc2.cu — paired-CTA (cta_group::2) variant, 256 x 256 tile per two SMs
+int ax_gemm_tc2_init(void);
+int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, const void* D,
+                int m, int n, int k, float alpha, float beta, int* status, int ksplit, cudaStream_t st);
+void ax_gemm_set_mode(int mode);      // 0 auto, 1 single-CTA only, 2 paired whenever possible
+
 // attn_simt.cu — exact-fp32 causal GQA attention on strided layouts.
 struct AttnShape {
     int B, H, KV, T, DH;

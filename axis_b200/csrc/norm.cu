@@ -41,6 +41,106 @@ __global__ void k_rmsnorm(const T* __restrict__ x, const T* __restrict__ w, T* _
         }
     }
 }
+// ── warp-per-row forms (dim = 32 * VPL * 16-byte vectors) ──────────────────
+// A warp owns a row: every lane loads VPL 16-byte vectors (coalesced 512 B per
+// warp per load), the row stays in registers between the reduction and the
+// output pass, and the only synchronisation is a shuffle tree — so each row
+// costs one DRAM read and one write with many loads in flight per lane.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(256)
+k_rmsnorm_warp(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ o, int rows, float eps) {
+    constexpr int N = Vec<T>::N, DIM = 32 * VPL * N;
+    const int lane = threadIdx.x & 31;
+    const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nw = gridDim.x * (blockDim.x >> 5);
+    for (int r = gw; r < rows; r += nw) {
+        const T* xr = x + (long long)r * DIM;
+        float xv[VPL][N];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            Vec<T>::ld(xr + (lane + 32 * i) * N, xv[i]);
+#pragma unroll
+            for (int q = 0; q < N; q++) ss += xv[i][q] * xv[i][q];
+        }
+        const float inv = rsqrtf(warp_sum(ss) / DIM + eps);
+        T* orow = o + (long long)r * DIM;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            float wv[N];
+            Vec<T>::ld(w + (lane + 32 * i) * N, wv);
+#pragma unroll
+            for (int q = 0; q < N; q++) xv[i][q] = xv[i][q] * inv * wv[q];
+            Vec<T>::st(orow + (lane + 32 * i) * N, xv[i]);
+        }
+    }
+}
+
+#define RBW_WARPS 8
+template <typename T, int VPL>
+__global__ void __launch_bounds__(RBW_WARPS * 32)
+k_rmsnorm_bwd_warp(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ g, const T* res, T* dx,
+                   float* __restrict__ partial, int rows, float eps) {
+    constexpr int N = Vec<T>::N, DIM = 32 * VPL * N;
+    __shared__ float sdw[DIM];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int gw = blockIdx.x * RBW_WARPS + wib, nw = gridDim.x * RBW_WARPS;
+    float dw[VPL][N];
+#pragma unroll
+    for (int i = 0; i < VPL; i++)
+#pragma unroll
+        for (int q = 0; q < N; q++) dw[i][q] = 0.f;
+    for (int r = gw; r < rows; r += nw) {
+        const long long base = (long long)r * DIM;
+        float xv[VPL][N], gv[VPL][N];
+        float ss = 0.f, gwx = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            const int c = (lane + 32 * i) * N;
+            float wv[N];
+            Vec<T>::ld(x + base + c, xv[i]);
+            Vec<T>::ld(g + base + c, gv[i]);
+            Vec<T>::ld(w + c, wv);
+#pragma unroll
+            for (int q = 0; q < N; q++) {
+                ss += xv[i][q] * xv[i][q];
+                gwx += gv[i][q] * wv[q] * xv[i][q];
+            }
+        }
+        ss = warp_sum(ss);
+        gwx = warp_sum(gwx);
+        const float inv = rsqrtf(ss / DIM + eps);
+        const float coef = inv * inv * inv * (gwx / DIM);
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            const int c = (lane + 32 * i) * N;
+            float ov[N], wv[N];
+            Vec<T>::ld(w + c, wv);
+            if (res) Vec<T>::ld(res + base + c, ov);
+#pragma unroll
+            for (int q = 0; q < N; q++) {
+                const float d = gv[i][q] * wv[q] * inv - xv[i][q] * coef;
+                ov[q] = res ? ov[q] + d : d;
+                dw[i][q] += gv[i][q] * xv[i][q] * inv;
+            }
+            Vec<T>::st(dx + base + c, ov);
+        }
+    }
+    if (!partial) return;
+    // block partial: warps add their column sums one after another (fixed order)
+    for (int j = threadIdx.x; j < DIM; j += blockDim.x) sdw[j] = 0.f;
+    __syncthreads();
+    for (int turn = 0; turn < RBW_WARPS; turn++) {
+        if (wib == turn) {
+#pragma unroll
+            for (int i = 0; i < VPL; i++)
+#pragma unroll
+                for (int q = 0; q < N; q++) sdw[(lane + 32 * i) * N + q] += dw[i][q];
+        }
+        __syncthreads();
+    }
+    for (int j = threadIdx.x; j < DIM; j += blockDim.x) partial[(long long)blockIdx.x * DIM + j] = sdw[j];
+}
+
 static int norm_threads(int dim, int per) {
     int t = (dim / per + 31) / 32 * 32;
     if (t < 32) t = 32;
@@ -51,6 +151,14 @@ int ax_rmsnorm(int dt, const void* x, const void* w, void* o, int rows, int dim,
     if (rows <= 0 || dim <= 0) return 0;
     const int per = dt == 1 ? 8 : 4;
     const bool vec = dim % per == 0 && aligned16(x) && aligned16(w) && aligned16(o);
+    if (vec && dim % (32 * per) == 0 && dim / (32 * per) <= 8) {
+        const int vpl = dim / (32 * per);
+        const int g = (rows + 7) / 8 < AX_SMS * 8 ? (rows + 7) / 8 : AX_SMS * 8;
+#define NW(TT, V) case V: k_rmsnorm_warp<TT, V><<<g, 256, 0, st>>>((const TT*)x, (const TT*)w, (TT*)o, rows, eps); return 0;
+        if (dt == 1) { switch (vpl) { NW(bf16, 1) NW(bf16, 2) NW(bf16, 3) NW(bf16, 4) NW(bf16, 5) NW(bf16, 6) NW(bf16, 7) NW(bf16, 8) } }
+        else { switch (vpl) { NW(float, 1) NW(float, 2) NW(float, 3) NW(float, 4) NW(float, 5) NW(float, 6) NW(float, 7) NW(float, 8) } }
+#undef NW
+    }
     const int thr = norm_threads(dim, vec ? per : 1);
     const int grid = rows < AX_SMS * 32 ? rows : AX_SMS * 32;
     if (dt == 1) {
@@ -189,12 +297,21 @@ __global__ void k_rmsnorm_bwd_acc(const T* __restrict__ x, const T* __restrict__
     if (partial)
         for (int j = threadIdx.x; j < dim; j += blockDim.x) partial[(long long)blockIdx.x * dim + j] = sdw[j];
 }
+// dw[j] = sum over the nb block partials: 32 columns x 8 row lanes per block, then a fixed-order combine
 __global__ void k_colsum_partials(const float* __restrict__ partial, float* __restrict__ dw, int nb, int dim) {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= dim) return;
+    __shared__ float sh[8][33];
+    const int j = blockIdx.x * 32 + threadIdx.x;
     float acc = 0.f;
-    for (int b = 0; b < nb; b++) acc += partial[(long long)b * dim + j];
-    dw[j] = acc;
+    if (j < dim)
+        for (int b = threadIdx.y; b < nb; b += 8) acc += partial[(long long)b * dim + j];
+    sh[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && j < dim) {
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) t += sh[q][threadIdx.x];
+        dw[j] = t;
+    }
 }
 long long ax_rmsnorm_bwd_acc_scratch(int dim) { return (long long)RB_BLOCKS * dim * sizeof(float); }
 int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, const void* res, void* dx,
@@ -204,10 +321,21 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
     const int per = dt == 1 ? 8 : 4;
     const bool vec = dim % per == 0 && aligned16(x) && aligned16(w) && aligned16(g) && aligned16(dx) &&
                      (!res || aligned16(res));
+    float* part = dw ? scratch : nullptr;
+    if (vec && dim % (32 * per) == 0 && dim / (32 * per) <= 6) {      // more vectors per lane would spill
+        const int vpl = dim / (32 * per);
+        int nbw = (rows + RBW_WARPS - 1) / RBW_WARPS;
+        if (nbw > RB_BLOCKS) nbw = RB_BLOCKS;
+#define BW(TT, V) case V: k_rmsnorm_bwd_warp<TT, V><<<nbw, RBW_WARPS * 32, 0, st>>>((const TT*)x, (const TT*)w, (const TT*)g, (const TT*)res, (TT*)dx, part, rows, eps); break;
+        if (dt == 1) { switch (vpl) { BW(bf16, 1) BW(bf16, 2) BW(bf16, 3) BW(bf16, 4) BW(bf16, 5) BW(bf16, 6) } }
+        else { switch (vpl) { BW(float, 1) BW(float, 2) BW(float, 3) BW(float, 4) BW(float, 5) BW(float, 6) } }
+#undef BW
+        if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbw, dim);
+        return 0;
+    }
     const int thr = norm_threads(dim, vec ? per : 1);
     const int nb = rows < RB_BLOCKS ? rows : RB_BLOCKS;
     const size_t smem = (size_t)dim * 4;
-    float* part = dw ? scratch : nullptr;
 #define RB_LAUNCH(TT, VV)                                                                              \
     do {                                                                                               \
         if (smem > 48 * 1024)                                                                          \
@@ -218,7 +346,7 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
     if (dt == 1) { if (vec) RB_LAUNCH(bf16, true); else RB_LAUNCH(bf16, false); }
     else { if (vec) RB_LAUNCH(float, true); else RB_LAUNCH(float, false); }
 #undef RB_LAUNCH
-    if (dw) k_colsum_partials<<<(dim + 127) / 128, 128, 0, st>>>(scratch, dw, nb, dim);
+    if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nb, dim);
     return 0;
 }
 

@@ -140,7 +140,9 @@ long long eng_launch_count(int reset);
 /* NCCL bootstrap with a deadline in ms (non-blocking init, polled). 0 = ok,
  * 7 = timed out, other = NCCL error. */
 int eng_nccl_init_timeout(int rank, int world, const void* id128, int timeout_ms);
-/* Force the general (non-tensor-core) kernels: 1 = GEMM, 2 = attention. */
+/* Kernel selection overrides (bit mask): 1 = general GEMM instead of tensor-core GEMM,
+ * 2 = general attention, 4 = single-CTA tensor-core GEMM only, 8 = paired-CTA GEMM
+ * whenever the shape allows. */
 int eng_set_fallback(int mask);
 /* Bytes currently allocated through eng_alloc*. */
 long long eng_bytes_allocated(void);
