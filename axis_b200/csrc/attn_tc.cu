@@ -18,6 +18,9 @@
 // Every mbarrier wait is bounded; on a timeout the kernel records a status
 // code, unwinds and frees its TMEM.
 #include <cuda_bf16.h>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -68,8 +71,11 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x;       // heavy tiles first
-    const int h = blockIdx.y, b = blockIdx.z, g = h / (H / KV);
+    // 1-D grid ordered by decreasing work: all (head, batch) pairs of the last query tile first
+    const int nqt_ = T / AT, nhb = gridDim.x / nqt_;
+    const int qt = nqt_ - 1 - (int)(blockIdx.x / nhb);
+    const int hb = blockIdx.x % nhb;
+    const int h = hb % H, b = hb / H, g = h / (H / KV);
     const int nkt = qt + 1;
 
     if (threadIdx.x == 0) {
@@ -224,18 +230,25 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 }
 
 // ════════════════════════════════ backward ══════════════════════════════════
-// D[b,h,t] = sum_d dO*O on the [B,T,H,DH] layout, written as [B,H,T]; one warp per row.
+// D[b,h,t] = sum_d dO*O on the [B,T,H,DH] layout, written as [B,H,T].  Eight lanes
+// share a 64-element row (one 16-byte vector of each tensor per lane).
 __global__ void k_attn_bwd_prep(const bf16* __restrict__ o, const bf16* __restrict__ dO, float* __restrict__ Dv,
                                 int B, int T, int H) {
-    const int lane = threadIdx.x & 31;
-    const long long rows = (long long)B * T * H;
-    const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += wstride) {
-        const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(o + row * ADH)[lane];
-        const __nv_bfloat162 g = reinterpret_cast<const __nv_bfloat162*>(dO + row * ADH)[lane];
-        const float2 fa = __bfloat1622float2(a), fg = __bfloat1622float2(g);
-        float acc = warp_sum(fa.x * fg.x + fa.y * fg.y);
-        if (!lane) {
+    const long long nvec = (long long)B * T * H * (ADH / 8);
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec + 7; i += stride) {
+        float a[8], g[8], acc = 0.f;
+        if (i < nvec) {
+            Vec<bf16>::ld(o + i * 8, a);
+            Vec<bf16>::ld(dO + i * 8, g);
+#pragma unroll
+            for (int q = 0; q < 8; q++) acc += a[q] * g[q];
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        if ((i & 7) == 0 && i < nvec) {
+            const long long row = i >> 3;
             const int hh = (int)(row % H);
             const long long bt = row / H;
             const int t = (int)(bt % T), bb = (int)(bt / T);
@@ -244,48 +257,57 @@ __global__ void k_attn_bwd_prep(const bf16* __restrict__ o, const bf16* __restri
     }
 }
 
+#define BWD_THREADS 288        // 8 compute warps (two per TMEM lane quadrant) + 1 control warp
 struct BwdSmem {
     static constexpr int K = 0, V = 16384, Q0 = 32768, DO0 = Q0 + 2 * 16384, DS = DO0 + 2 * 16384, DQ = DS + 32768,
                          LSE = DQ + 32768, DD = LSE + 2 * 512, BARS = DD + 2 * 512, TOTAL = BARS + 128 + 1024;
 };
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
               const __grid_constant__ CUtensorMap tmdQ, const float* __restrict__ lse, const float* __restrict__ Dv,
-              bf16* __restrict__ dk, bf16* __restrict__ dv, int T, int H, int KV, float scale, int* status) {
+              bf16* __restrict__ dk, bf16* __restrict__ dv, int T, int H, int KV, float scale, int* status,
+              long long* prof) {
+    // prof (optional, normally null): per-CTA cycle counts of the phases of compute thread 0 —
+    // [0] wait S/dP, [1] softmax + stores, [2] wait dQ, [3] dQ drain, [4] total, [5] iterations
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sb = smem_u32(smem);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
-    // kv_full, q_full[2], q_empty[2], sdp_full, pds_full, dq_full
+    // kv_full, q_full[2], q_empty[2], sdp_full, pds_full, dq_full[2]
     const uint32_t b_kv = smem_u32(bars), b_qf = b_kv + 8, b_qe = b_qf + 16, b_sdp = b_qe + 16, b_pds = b_sdp + 8, b_dq = b_pds + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* s_lse = reinterpret_cast<float*>(smem + BwdSmem::LSE);     // [2][128], pre-multiplied by log2(e)
     float* s_D = reinterpret_cast<float*>(smem + BwdSmem::DD);        // [2][128]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int j = blockIdx.x, g = blockIdx.y, b = blockIdx.z;         // key tile (0 = most work), kv head, batch
+    // 1-D grid ordered by decreasing work: key tile 0 (attended by every query tile) of all
+    // (kv head, batch) pairs first
     const int rep = H / KV, nqt = T / AT;
+    const int ngb = gridDim.x / nqt;
+    const int j = blockIdx.x / ngb, gb = blockIdx.x % ngb;
+    const int g = gb % KV, b = gb / KV;
     const int per_head = nqt - j;                                     // causal: query tiles j .. nqt-1
     const int n_it = rep * per_head;
 
     if (threadIdx.x == 0) {
         mbar_init(b_kv, 1);
-        for (int s = 0; s < 2; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 1); }
-        mbar_init(b_sdp, 1); mbar_init(b_pds, 128); mbar_init(b_dq, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 1); mbar_init(b_dq + 8 * s, 1); }
+        mbar_init(b_sdp, 1); mbar_init(b_pds, 256);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 4) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+    if (warp == 8) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // columns: S^T/P^T 0..127, dP^T/dS^T 128..255, dV 256..319, dK 320..383, dQ[0] 384..447, dQ[1] 448..511
     const uint32_t t_S = tmem, t_dP = tmem + 128, t_dV = tmem + 256, t_dK = tmem + 320, t_dQ = tmem + 384;
 
-    if (warp == 4) {
+    if (warp == 8) {
         if (lane == 0) {
             bool ok = true;
             constexpr uint32_t id_s = tc_idesc_bf16(128, 128, 0, 0);       // S^T = K Q^T, dP^T = V dO^T
@@ -321,135 +343,157 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tc_commit(b_sdp);
                 if (!mbar_wait(b_pds, it & 1) || *abort_flag) { ok = false; break; }
                 tc_fence_after();
+                // P^T / dS^T in TMEM: queries 0..63 packed in columns 0..31, queries 64..127 in columns 64..95
 #pragma unroll
                 for (int kk = 0; kk < AT / 16; kk++)       // dV += P^T dO   (k = queries)
-                    tc_mma_ts(t_dV, t_S + kk * 8, tc_smem_desc(sdO + kk * 2048, 16384, 1024), id_acc, (it | kk) != 0);
+                    tc_mma_ts(t_dV, t_S + (kk >> 2) * 64 + (kk & 3) * 8, tc_smem_desc(sdO + kk * 2048, 16384, 1024), id_acc, (it | kk) != 0);
 #pragma unroll
                 for (int kk = 0; kk < AT / 16; kk++)       // dK += dS^T Q
-                    tc_mma_ts(t_dK, t_dP + kk * 8, tc_smem_desc(sQ + kk * 2048, 16384, 1024), id_acc, (it | kk) != 0);
+                    tc_mma_ts(t_dK, t_dP + (kk >> 2) * 64 + (kk & 3) * 8, tc_smem_desc(sQ + kk * 2048, 16384, 1024), id_acc, (it | kk) != 0);
 #pragma unroll
-                for (int kk = 0; kk < AT / 16; kk++)       // dQ = dS K      (k = keys)
-                    tc_mma_ss(t_dQ, tc_smem_desc(sb + BwdSmem::DS + kk * 2048, 16384, 1024),
+                for (int kk = 0; kk < AT / 16; kk++)       // dQ = dS K      (k = keys), double-buffered
+                    tc_mma_ss(t_dQ + (it & 1) * 64, tc_smem_desc(sb + BwdSmem::DS + kk * 2048, 16384, 1024),
                               tc_smem_desc(sb + BwdSmem::K + kk * 2048, 16384, 1024), id_dq, kk != 0);
                 tc_commit(b_qe + 8 * s);
-                tc_commit(b_dq);
+                tc_commit(b_dq + 8 * (it & 1));
             }
             if (!ok) { *abort_flag = 1; atomicExch(status, STAT_BWD | 1); }
         }
     } else {
-        const int r = threadIdx.x;                          // key row of S^T / query row of dQ == TMEM lane
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int r = threadIdx.x & 127;                    // key row of S^T / query row of dQ == TMEM lane
+        const int hf = threadIdx.x >> 7;                    // which half of the columns this thread handles
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float c = scale * LOG2E;
         bool ok = true;
-        // lse / D of the first query tile
+        // row statistics of the first query tile: half 0 threads fetch lse, half 1 threads fetch D
         {
-            const int h = g * rep, i = j;
-            s_lse[r] = lse[((long long)b * H + h) * T + i * AT + r] * LOG2E;
-            s_D[r] = Dv[((long long)b * H + h) * T + i * AT + r];
+            const long long idx = ((long long)b * H + g * rep) * T + j * AT + r;
+            if (hf == 0) s_lse[r] = lse[idx] * LOG2E; else s_D[r] = Dv[idx];
         }
-        for (int it = 0; it < n_it && ok; it++) {
-            const int hh = it / per_head, i = j + it % per_head, h = g * rep + hh;
-            const int cur = it & 1;
-            float n_lse = 0.f, n_D = 0.f;
-            if (it + 1 < n_it) {        // prefetch the next tile's row statistics into registers
-                const int h2 = g * rep + (it + 1) / per_head, i2 = j + (it + 1) % per_head;
-                n_lse = lse[((long long)b * H + h2) * T + i2 * AT + r] * LOG2E;
-                n_D = Dv[((long long)b * H + h2) * T + i2 * AT + r];
+        // drain of dQ(u): TMEM -> swizzled fp32 staging -> TMA reduce-add into the fp32 dq buffer
+        long long pc[5] = {0, 0, 0, 0, 0};
+        const bool timing = prof != nullptr && threadIdx.x == 0;
+        const long long t_begin = timing ? clock64() : 0;
+        auto drain = [&](int u) -> bool {
+            const long long d0 = timing ? clock64() : 0;
+            if (!mbar_wait(b_dq + 8 * (u & 1), (u >> 1) & 1) || *abort_flag) return false;
+            tc_fence_after();
+            if (timing) { const long long d1 = clock64(); pc[2] += d1 - d0; pc[3] -= d1; }
+            if (threadIdx.x == 0) bulk_wait_read0();         // the previous reduce has finished reading the staging
+            named_bar_sync(1, 256);
+            uint32_t v[32];
+            tmem_ld32(t_dQ + (u & 1) * 64 + lane_base + hf * 32, v);
+            tmem_ld_wait();
+            uint8_t* dq_row = smem + BwdSmem::DQ + hf * 16384 + r * 128;
+#pragma unroll
+            for (int k4 = 0; k4 < 8; k4++) {
+                float4 f = make_float4(__uint_as_float(v[k4 * 4]) * scale, __uint_as_float(v[k4 * 4 + 1]) * scale,
+                                       __uint_as_float(v[k4 * 4 + 2]) * scale, __uint_as_float(v[k4 * 4 + 3]) * scale);
+                *reinterpret_cast<float4*>(dq_row + ((k4 ^ (r & 7)) << 4)) = f;
             }
-            named_bar_sync(1, 128);                            // s_lse/s_D[cur] visible to all rows
+            fence_async_smem();
+            tc_fence_before();
+            named_bar_sync(1, 256);
+            if (threadIdx.x == 0) {
+                const int hh = u / per_head, i = j + u % per_head, h = g * rep + hh;
+                tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ, 0, h, i * AT, b);
+                tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ + 16384, 32, h, i * AT, b);
+                bulk_commit();
+            }
+            if (timing) pc[3] += clock64();
+            return true;
+        };
+        named_bar_sync(1, 256);
+        for (int it = 0; it < n_it && ok; it++) {
+            const int i = j + it % per_head;
+            const int cur = it & 1;
+            float nxt = 0.f;
+            if (it + 1 < n_it) {        // prefetch the next tile's row statistic into a register
+                const int h2 = g * rep + (it + 1) / per_head, i2 = j + (it + 1) % per_head;
+                const long long idx = ((long long)b * H + h2) * T + i2 * AT + r;
+                nxt = hf == 0 ? lse[idx] * LOG2E : Dv[idx];
+            }
+            // s_lse/s_D[cur] were published by a barrier: before the loop (it == 0), after the store
+            // below (it == 1), or inside the previous iteration's drain (it >= 2)
+            const long long c0t = timing ? clock64() : 0;
             if (!mbar_wait(b_sdp, it & 1) || *abort_flag) { ok = false; break; }
             tc_fence_after();
+            const long long c1t = timing ? clock64() : 0;
             const bool diag = i == j;
             const float* L = s_lse + cur * 128;
             const float* Dr = s_D + cur * 128;
-            uint8_t* ds_row = smem + BwdSmem::DS + r * 128;
+            uint8_t* ds_row = smem + BwdSmem::DS + hf * 16384 + r * 128;
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
+            for (int cc = 0; cc < 2; cc++) {
+                const int ch = hf * 2 + cc;                     // 32-column chunk of this thread's half
                 uint32_t sv[32], dp[32], wp[16], wd[16];
                 tmem_ld32(t_S + lane_base + ch * 32, sv);
                 tmem_ld32(t_dP + lane_base + ch * 32, dp);
                 tmem_ld_wait();
 #pragma unroll
-                for (int q = 0; q < 32; q += 2) {
+                for (int q = 0; q < 32; q += 4) {
                     const int c0 = ch * 32 + q;                 // query column within the tile
-                    float p0 = fast_exp2(__uint_as_float(sv[q]) * c - L[c0]);
-                    float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - L[c0 + 1]);
-                    if (diag) { if (c0 < r) p0 = 0.f; if (c0 + 1 < r) p1 = 0.f; }      // query < key: masked
-                    const float d0 = p0 * (__uint_as_float(dp[q]) - Dr[c0]);
-                    const float d1 = p1 * (__uint_as_float(dp[q + 1]) - Dr[c0 + 1]);
+                    const float4 l4 = *reinterpret_cast<const float4*>(L + c0);       // broadcast 16-byte loads
+                    const float4 d4 = *reinterpret_cast<const float4*>(Dr + c0);
+                    float p0 = fast_exp2(__uint_as_float(sv[q]) * c - l4.x);
+                    float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - l4.y);
+                    float p2 = fast_exp2(__uint_as_float(sv[q + 2]) * c - l4.z);
+                    float p3 = fast_exp2(__uint_as_float(sv[q + 3]) * c - l4.w);
+                    if (diag) {                                  // query < key: masked
+                        if (c0 < r) p0 = 0.f; if (c0 + 1 < r) p1 = 0.f; if (c0 + 2 < r) p2 = 0.f; if (c0 + 3 < r) p3 = 0.f;
+                    }
                     wp[q >> 1] = pack_bf16(p0, p1);
-                    wd[q >> 1] = pack_bf16(d0, d1);
+                    wp[(q >> 1) + 1] = pack_bf16(p2, p3);
+                    wd[q >> 1] = pack_bf16(p0 * (__uint_as_float(dp[q]) - d4.x), p1 * (__uint_as_float(dp[q + 1]) - d4.y));
+                    wd[(q >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[q + 2]) - d4.z), p3 * (__uint_as_float(dp[q + 3]) - d4.w));
                 }
-                tmem_st16(t_S + lane_base + ch * 16, wp);        // P^T over consumed S^T columns
-                tmem_st16(t_dP + lane_base + ch * 16, wd);       // dS^T over consumed dP^T columns
-                // dS^T also to shared memory, M-major (queries contiguous), 128-byte swizzle:
-                // half = query/64, 16-byte chunk (query%64)/8 XOR (row & 7)
-                const int half = ch >> 1;
+                // packed columns of this half: hf*64 + cc*16 — inside the columns this thread has already read
+                tmem_st16(t_S + lane_base + hf * 64 + cc * 16, wp);
+                tmem_st16(t_dP + lane_base + hf * 64 + cc * 16, wd);
+                // dS^T also to shared memory (A operand of dQ): half = query/64, 16-byte chunk index XOR (row & 7)
 #pragma unroll
                 for (int k4 = 0; k4 < 4; k4++) {
-                    const int chunk = (ch & 1) * 4 + k4;
+                    const int chunk = cc * 4 + k4;
                     uint4 pk = make_uint4(wd[k4 * 4], wd[k4 * 4 + 1], wd[k4 * 4 + 2], wd[k4 * 4 + 3]);
-                    *reinterpret_cast<uint4*>(ds_row + half * 16384 + ((chunk ^ (r & 7)) << 4)) = pk;
+                    *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) = pk;
                 }
             }
             tmem_st_wait();
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(b_pds);
-            if (it + 1 < n_it) { s_lse[(cur ^ 1) * 128 + r] = n_lse; s_D[(cur ^ 1) * 128 + r] = n_D; }
-            // ── drain dQ(it): TMEM -> swizzled fp32 staging -> TMA reduce-add into the fp32 dq buffer ──
-            if (!mbar_wait(b_dq, it & 1) || *abort_flag) { ok = false; break; }
-            tc_fence_after();
-            if (threadIdx.x == 0) bulk_wait_read0();             // staging free again (previous reduce has read it)
-            named_bar_sync(1, 128);
-            uint8_t* dq_row = smem + BwdSmem::DQ + r * 128;
+            if (timing) { const long long c2t = clock64(); pc[0] += c1t - c0t; pc[1] += c2t - c1t; }
+            if (it + 1 < n_it) { if (hf == 0) s_lse[(cur ^ 1) * 128 + r] = nxt; else s_D[(cur ^ 1) * 128 + r] = nxt; }
+            // dQ of the previous iteration: its MMA finished long ago, so this does not stall on the tensor pipe
+            if (it == 0) named_bar_sync(1, 256);
+            else if (!drain(it - 1)) { ok = false; break; }
+        }
+        if (ok && !drain(n_it - 1)) ok = false;
+        if (threadIdx.x == 0) bulk_wait0();
+        if (timing) {
+            long long* pp = prof + 8 * (long long)blockIdx.x;
+            pp[0] = pc[0]; pp[1] = pc[1]; pp[2] = pc[2]; pp[3] = pc[3]; pp[4] = clock64() - t_begin; pp[5] = n_it;
+        }
+        if (ok) {
+            // dV (half 0 threads) and dK (half 1 threads): complete once the last commit has fired — waited in drain
+            const int t = j * AT + r;
+            const uint32_t ta = hf ? t_dK : t_dV;
+            const float f = hf ? scale : 1.f;
+            bf16* dst = (hf ? dk : dv) + (((long long)b * T + t) * KV + g) * ADH;
 #pragma unroll 1
             for (int ch = 0; ch < 2; ch++) {
                 uint32_t v[32];
-                tmem_ld32(t_dQ + lane_base + ch * 32, v);
+                tmem_ld32(ta + lane_base + ch * 32, v);
                 tmem_ld_wait();
+                if (t < T) {
 #pragma unroll
-                for (int k4 = 0; k4 < 8; k4++) {
-                    float4 f = make_float4(__uint_as_float(v[k4 * 4]) * scale, __uint_as_float(v[k4 * 4 + 1]) * scale,
-                                           __uint_as_float(v[k4 * 4 + 2]) * scale, __uint_as_float(v[k4 * 4 + 3]) * scale);
-                    *reinterpret_cast<float4*>(dq_row + ch * 16384 + ((k4 ^ (r & 7)) << 4)) = f;
-                }
-            }
-            fence_async_smem();
-            named_bar_sync(1, 128);
-            if (threadIdx.x == 0) {
-                tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ, 0, h, i * AT, b);
-                tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ + 16384, 32, h, i * AT, b);
-                bulk_commit();
-            }
-            tc_fence_before();
-        }
-        if (threadIdx.x == 0) bulk_wait0();
-        if (ok) {
-            // dV, dK complete once the last commit (dq_full of the last iteration) has fired — already waited.
-            const int t = j * AT + r;
-            bf16* kr = dk + (((long long)b * T + t) * KV + g) * ADH;
-            bf16* vr = dv + (((long long)b * T + t) * KV + g) * ADH;
-#pragma unroll 1
-            for (int which = 0; which < 2; which++) {
-                const uint32_t ta = which ? t_dK : t_dV;
-                const float f = which ? scale : 1.f;
-                bf16* dst = which ? kr : vr;
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ch++) {
-                    uint32_t v[32];
-                    tmem_ld32(ta + lane_base + ch * 32, v);
-                    tmem_ld_wait();
-                    if (t < T) {
-#pragma unroll
-                        for (int q = 0; q < 32; q += 8) {
-                            uint4 pk;
-                            pk.x = pack_bf16(__uint_as_float(v[q]) * f, __uint_as_float(v[q + 1]) * f);
-                            pk.y = pack_bf16(__uint_as_float(v[q + 2]) * f, __uint_as_float(v[q + 3]) * f);
-                            pk.z = pack_bf16(__uint_as_float(v[q + 4]) * f, __uint_as_float(v[q + 5]) * f);
-                            pk.w = pack_bf16(__uint_as_float(v[q + 6]) * f, __uint_as_float(v[q + 7]) * f);
-                            *reinterpret_cast<uint4*>(dst + ch * 32 + q) = pk;
-                        }
+                    for (int q = 0; q < 32; q += 8) {
+                        uint4 pk;
+                        pk.x = pack_bf16(__uint_as_float(v[q]) * f, __uint_as_float(v[q + 1]) * f);
+                        pk.y = pack_bf16(__uint_as_float(v[q + 2]) * f, __uint_as_float(v[q + 3]) * f);
+                        pk.z = pack_bf16(__uint_as_float(v[q + 4]) * f, __uint_as_float(v[q + 5]) * f);
+                        pk.w = pack_bf16(__uint_as_float(v[q + 6]) * f, __uint_as_float(v[q + 7]) * f);
+                        *reinterpret_cast<uint4*>(dst + ch * 32 + q) = pk;
                     }
                 }
             }
@@ -460,7 +504,7 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
+    if (warp == 8) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
 // fp32 dq accumulator -> bf16 dq (same [B,T,H,DH] layout)
@@ -510,7 +554,7 @@ int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* 
     if (!served(s) || !lse || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return -1;
     CUtensorMap tq, tk, tv;
     if (map_bthd(&tq, q, s.B, s.T, s.H) || map_bthd(&tk, k, s.B, s.T, s.KV) || map_bthd(&tv, v, s.B, s.T, s.KV)) return 2;
-    dim3 grid(s.T / AT, s.H, s.B);
+    dim3 grid((s.T / AT) * s.H * s.B);
     k_attn_fwd_tc<<<grid, ATT_THREADS, FwdSmem::TOTAL, st>>>(tq, tk, tv, (bf16*)o, lse, s.T, s.H, s.KV, s.scale, status);
     return 0;
 }
@@ -526,10 +570,24 @@ int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, c
         map_bthd(&tdo, dO, s.B, s.T, s.H) || map_dq_f32(&tdq, g_dq_acc, s.B, s.T, s.H)) return 2;
     cudaMemsetAsync(g_dq_acc, 0, need, st);
     const long long rows = (long long)s.B * s.T * s.H;
-    k_attn_bwd_prep<<<ew_grid(rows * 32, 256), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, Dscratch, s.B, s.T, s.H);
-    dim3 grid(s.T / AT, s.KV, s.B);
-    k_attn_bwd_tc<<<grid, ATT_THREADS, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, lse, Dscratch, (bf16*)dk, (bf16*)dv,
-                                                              s.T, s.H, s.KV, s.scale, status);
+    k_attn_bwd_prep<<<ew_grid(rows * 8, 256), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, Dscratch, s.B, s.T, s.H);
+    dim3 grid((s.T / AT) * s.KV * s.B);
+    static const bool want_prof = getenv("AXENG_ATTN_PROF") != nullptr;
+    long long* prof = nullptr;
+    const int nblk = (s.T / AT) * s.KV * s.B;
+    if (want_prof && cudaMalloc(&prof, (size_t)nblk * 64) != cudaSuccess) prof = nullptr;
+    k_attn_bwd_tc<<<grid, BWD_THREADS, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, lse, Dscratch, (bf16*)dk, (bf16*)dv,
+                                                              s.T, s.H, s.KV, s.scale, status, prof);
+    if (prof) {     // debugging aid: phase cycle counts summed over CTAs, printed to stderr
+        std::vector<long long> h((size_t)nblk * 8);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h.data(), prof, (size_t)nblk * 64, cudaMemcpyDeviceToHost);
+        cudaFree(prof);
+        long long sum[6] = {0, 0, 0, 0, 0, 0}, mx = 0;
+        for (int i = 0; i < nblk; i++) { for (int q = 0; q < 6; q++) sum[q] += h[i * 8 + q]; if (h[i * 8 + 4] > mx) mx = h[i * 8 + 4]; }
+        fprintf(stderr, "attn_bwd phases (cycles/iteration): wait_sdp %.0f softmax %.0f wait_dq %.0f drain %.0f total %.0f | iterations %lld, longest CTA %lld cycles\n",
+                (double)sum[0] / sum[5], (double)sum[1] / sum[5], (double)sum[2] / sum[5], (double)sum[3] / sum[5], (double)sum[4] / sum[5], sum[5], mx);
+    }
     const long long n8 = rows * ADH / 8;
     k_dq_convert<<<ew_grid(n8, 256), 256, 0, st>>>(g_dq_acc, (bf16*)dq, n8);
     return 0;

@@ -141,6 +141,78 @@ k_rmsnorm_bwd_warp(const T* __restrict__ x, const T* __restrict__ w, const T* __
     for (int j = threadIdx.x; j < DIM; j += blockDim.x) partial[(long long)blockIdx.x * DIM + j] = sdw[j];
 }
 
+// bf16 specialisation: rows stay packed (16-byte vectors) in registers, so 4-warp blocks fit three
+// to an SM, every lane has 3*VPL loads in flight, and x, g and the residual are each read once.
+#define RBP_WARPS 4
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+template <int VPL>
+__global__ void __launch_bounds__(RBP_WARPS * 32, 3)
+k_rmsnorm_bwd_packed(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ g, const bf16* res,
+                     bf16* dx, float* __restrict__ partial, int rows, float eps) {
+    constexpr int DIM = 32 * VPL * 8;
+    __shared__ float sdw[DIM];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int gw = blockIdx.x * RBP_WARPS + wib, nw = gridDim.x * RBP_WARPS;
+    float dw[VPL][8];
+#pragma unroll
+    for (int i = 0; i < VPL; i++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) dw[i][q] = 0.f;
+    for (int r = gw; r < rows; r += nw) {
+        const long long base = (long long)r * DIM;
+        uint4 xp[VPL], gp[VPL], rp[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            const int c = (lane + 32 * i) * 8;
+            xp[i] = *reinterpret_cast<const uint4*>(x + base + c);
+            gp[i] = *reinterpret_cast<const uint4*>(g + base + c);
+            if (res) rp[i] = *reinterpret_cast<const uint4*>(res + base + c);
+        }
+        float ss = 0.f, gwx = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            float xv[8], gv[8], wv[8];
+            unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(__ldg(reinterpret_cast<const uint4*>(w + (lane + 32 * i) * 8)), wv);
+#pragma unroll
+            for (int q = 0; q < 8; q++) { ss += xv[q] * xv[q]; gwx += gv[q] * wv[q] * xv[q]; }
+        }
+        ss = warp_sum(ss);
+        gwx = warp_sum(gwx);
+        const float inv = rsqrtf(ss / DIM + eps);
+        const float coef = inv * inv * inv * (gwx / DIM);
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            float xv[8], gv[8], wv[8], ov[8];
+            unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(__ldg(reinterpret_cast<const uint4*>(w + (lane + 32 * i) * 8)), wv);
+            if (res) unpack8(rp[i], ov);
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float d = gv[q] * wv[q] * inv - xv[q] * coef;
+                ov[q] = res ? ov[q] + d : d;
+                dw[i][q] += gv[q] * xv[q] * inv;
+            }
+            Vec<bf16>::st(dx + base + (lane + 32 * i) * 8, ov);
+        }
+    }
+    if (!partial) return;
+    for (int j = threadIdx.x; j < DIM; j += blockDim.x) sdw[j] = 0.f;
+    __syncthreads();
+    for (int turn = 0; turn < RBP_WARPS; turn++) {      // fixed order
+        if (wib == turn) {
+#pragma unroll
+            for (int i = 0; i < VPL; i++)
+#pragma unroll
+                for (int q = 0; q < 8; q++) sdw[(lane + 32 * i) * 8 + q] += dw[i][q];
+        }
+        __syncthreads();
+    }
+    for (int j = threadIdx.x; j < DIM; j += blockDim.x) partial[(long long)blockIdx.x * DIM + j] = sdw[j];
+}
+
 static int norm_threads(int dim, int per) {
     int t = (dim / per + 31) / 32 * 32;
     if (t < 32) t = 32;
@@ -324,6 +396,15 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
     float* part = dw ? scratch : nullptr;
     if (vec && dim % (32 * per) == 0 && dim / (32 * per) <= 6) {      // more vectors per lane would spill
         const int vpl = dim / (32 * per);
+        if (dt == 1) {
+            int nbp = (rows + RBP_WARPS - 1) / RBP_WARPS;
+            if (nbp > RB_BLOCKS) nbp = RB_BLOCKS;            // 296 blocks: two per SM resident at once, one wave
+#define BP(V) case V: k_rmsnorm_bwd_packed<V><<<nbp, RBP_WARPS * 32, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
+            switch (vpl) { BP(1) BP(2) BP(3) BP(4) BP(5) BP(6) }
+#undef BP
+            if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
+            return 0;
+        }
         int nbw = (rows + RBW_WARPS - 1) / RBW_WARPS;
         if (nbw > RB_BLOCKS) nbw = RB_BLOCKS;
 #define BW(TT, V) case V: k_rmsnorm_bwd_warp<TT, V><<<nbw, RBW_WARPS * 32, 0, st>>>((const TT*)x, (const TT*)w, (const TT*)g, (const TT*)res, (TT*)dx, part, rows, eps); break;
