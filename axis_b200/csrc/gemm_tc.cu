@@ -12,6 +12,7 @@
 // 128 x BN x 64 with BN = 128 or 256.  All barrier waits are bounded.
 #include <cuda_bf16.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -97,6 +98,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: let the next kernel in the stream start its own set-up as
+    // SMs free up, and do not touch global memory until everything before this kernel is done.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0 && lane == 0) {
         // ── TMA producer ──
@@ -226,6 +231,16 @@ static float* g_splitk_ws = nullptr;
 static const size_t SPLITK_WS_BYTES = 160u << 20;
 static int g_pair_mode = 0;        // 0 auto, 1 never use the paired-CTA kernel, 2 use it whenever the shape allows
 static int g_pairs_avail = 0;      // co-resident CTA pairs of the paired kernel (0 = unavailable)
+// programmatic dependent launch of the GEMM kernels (AXENG_NO_PDL=1 turns it off)
+int ax_gemm_pdl(void) {
+    static const int on = getenv("AXENG_NO_PDL") ? 0 : 1;
+    return on;
+}
+// output tiles written by TMA stores from a shared-memory staging area (AXENG_NO_TMA_OUT=1: per-thread stores)
+int ax_gemm_tma_out(void) {
+    static const int on = getenv("AXENG_NO_TMA_OUT") ? 0 : 1;
+    return on;
+}
 float* ax_splitk_ws(size_t* bytes) { if (bytes) *bytes = SPLITK_WS_BYTES; return g_splitk_ws; }
 void ax_gemm_set_mode(int mode) { g_pair_mode = mode; }
 template <typename TO>
@@ -271,8 +286,18 @@ static int gemm_launch(const void* A, const void* B, void* C, const void* D, int
     }
     const int units = ((m + BM - 1) / BM) * ((n + BN - 1) / BN) * ksplit;
     const int grid = units < AX_SMS ? units : AX_SMS;
-    k_gemm_tc<BN, A_MN, B_MN, TO><<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM, st>>>(tmA, tmB, (TO*)C, (const TO*)D, m, n, k, alpha, beta,
-                                                                                 status, ksplit, g_splitk_ws);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = GemmCfg<BN>::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = ax_gemm_pdl() ? 1 : 0;
+    TO* Cp = (TO*)C; const TO* Dp = (const TO*)D;
+    float* wsp = g_splitk_ws;
+    if (cudaLaunchKernelEx(&cfg, k_gemm_tc<BN, A_MN, B_MN, TO>, tmA, tmB, Cp, Dp, m, n, k, alpha, beta, status, ksplit, wsp) != cudaSuccess) return 3;
     if (ksplit > 1) {
         const long long mn = (long long)m * n;
         k_splitk_reduce<TO><<<ew_grid(mn / 4, 256), 256, 0, st>>>(g_splitk_ws, ksplit, (TO*)C, (const TO*)D, mn, alpha, beta);

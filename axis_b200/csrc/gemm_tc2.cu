@@ -12,6 +12,8 @@
 // Same operand layouts, epilogue and split-K scheme as the single-CTA kernel.
 // All mbarrier waits are bounded.
 #include <cuda_bf16.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "gemm_epi.cuh"
@@ -27,7 +29,8 @@
 #define A_BYTES2 (BM2 * BK2 * 2)
 #define B_BYTES2 (128 * BK2 * 2)
 #define STAGE_BYTES2 (A_BYTES2 + B_BYTES2)
-#define SMEM2 (STAGES2 * STAGE_BYTES2 + 1024 + 256)
+#define STG_BYTES2 (4 * 2 * 4096)      // output staging: per epilogue warp two buffers of 32 rows x 128 B
+#define SMEM2 (STAGES2 * STAGE_BYTES2 + STG_BYTES2 + 1024 + 256)
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -44,6 +47,18 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tile store from this CTA's shared memory (3-D map: column, row, split); bulk-group completion
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void bulk_commit2() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
 }
 // tile load whose completion is counted on an mbarrier that may live in the peer CTA
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int x, int y) {
@@ -77,11 +92,20 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar) {
 template <int A_MN, int B_MN, typename TO>
 __global__ void __launch_bounds__(THREADS2, 1)
 k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+           const __grid_constant__ CUtensorMap tmC, int tma_out,
            TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status,
-           int ksplit, float* __restrict__ ws) {
+           int ksplit, float* __restrict__ ws, long long* prof) {
+    // tma_out != 0: the epilogue stages 32 x 128-byte pieces in shared memory (128-byte swizzle) and writes
+    // them with TMA tile stores through tmC — {n, m, 1} over C, or {n, m, ksplit} over the fp32 split-K
+    // workspace; the hardware clips pieces that overhang the matrix.  Otherwise threads store their rows.
+    // prof (optional, normally null): clock64 stamps of pair 0's leader CTA — [0] entry, [1] set-up done,
+    // [2] predecessor grid finished, [3] first operands landed, [4] last MMA issued, [5] last accumulator
+    // complete, [6] last tile stored, [7] exit
+    const bool timing = prof != nullptr && blockIdx.x == 0;
+    if (timing && threadIdx.x == 0) prof[0] = clock64();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE_BYTES2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE_BYTES2 + STG_BYTES2);
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES2;
     const uint32_t bar_tfull = bar_empty + 8 * STAGES2, bar_tempty = bar_tfull + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
@@ -104,6 +128,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         mbar_fence_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        if (tma_out) tma_prefetch_desc(&tmC);
     }
     if (warp == 1) { tmem_alloc2(smem_u32(tmem_slot), 512); tmem_relinquish2(); }
     tc_fence_before();
@@ -113,6 +138,11 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t full_leader = map_to_cta(bar_full, 0);  // cluster address of the leader's full[0]
     const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
+    // programmatic dependent launch: see the single-CTA kernel
+    if (timing && threadIdx.x == 0) prof[1] = clock64();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (timing && threadIdx.x == 0) prof[2] = clock64();
 
     if (warp == 0 && lane == 0) {
         // ── TMA producer (both CTAs): own 128 rows of A, own 128 columns of B ──
@@ -164,6 +194,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                 const uint32_t ph = (it / STAGES2) & 1;
                 if (!mbar_wait(bar_full + 8 * s, ph) || *abort_flag) { ok = false; break; }
                 tc_fence_after();
+                if (timing && it == 0) prof[3] = clock64();
                 const uint32_t sa = smem_base + s * STAGE_BYTES2, sb = sa + A_BYTES2;
 #pragma unroll
                 for (int kk = 0; kk < BK2 / 16; kk++) {
@@ -174,15 +205,20 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                 tc_commit2(bar_empty + 8 * s);         // frees the stage in both CTAs
             }
             if (ok) tc_commit2(bar_tfull + 8 * acc);   // accumulator ready in both CTAs
+            if (timing) prof[4] = clock64();
         }
         if (!ok) { *abort_flag = 1; atomicExch(status, STAT_GEMM2 | 2); }
     } else if (warp >= 2) {
         // ── epilogue (both CTAs): own 128 rows x 256 columns ──
         const int quad = warp & 3;
-        uint32_t tcount = 0;
+        uint32_t tcount = 0, pieces = 0;
         bool ok = true;
         const bool vec_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (n % (16 / (int)sizeof(TO))) == 0 &&
                             (!D || (reinterpret_cast<uintptr_t>(D) & 15) == 0);
+        const bool f32_out = ksplit > 1 || sizeof(TO) == 4;
+        const float a_eff = ksplit > 1 ? 1.f : alpha;
+        uint8_t* stg = smem + STAGES2 * STAGE_BYTES2 + quad * 8192;
+        const uint32_t stg_u32 = smem_base + STAGES2 * STAGE_BYTES2 + quad * 8192;
         for (int unit = pair; unit < num_units && ok; unit += npairs, tcount++) {
             const int tile = unit % num_tiles, split = unit / num_tiles;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
@@ -190,25 +226,73 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const uint32_t aph = (tcount >> 1) & 1;
             if (!mbar_wait(bar_tfull + 8 * acc, aph) || *abort_flag) { ok = false; break; }
             tc_fence_after();
-            const int row = tm * 2 * BM2 + rank * BM2 + quad * 32 + lane;
+            if (timing && threadIdx.x == 64) prof[5] = clock64();
+            const int row0 = tm * 2 * BM2 + rank * BM2 + quad * 32;
+            const int row = row0 + lane;
             const uint32_t taddr = tmem_base + acc * BN2 + ((uint32_t)(quad * 32) << 16);
-            TO* crow = C + (long long)row * n;
-            const TO* drow = (D && beta != 0.f) ? D + (long long)row * n : nullptr;
-            float* wrow = ws + ((long long)split * m + row) * n;
+            if (tma_out) {
+                const int cw = f32_out ? 32 : 64;              // columns per 128-byte piece
 #pragma unroll 1
-            for (int c = 0; c < BN2; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c, r);
-                tmem_ld_wait();
-                const int col0 = tn * BN2 + c;
-                if (row < m && col0 < n) {
-                    if (ksplit > 1) epi_store<float>(wrow, nullptr, r, col0, n - col0, 1.f, 0.f, (n & 3) == 0);
-                    else epi_store<TO>(crow, drow, r, col0, n - col0, alpha, beta, vec_ok);
+                for (int c = 0; c < BN2; c += cw) {
+                    const int col0 = tn * BN2 + c;
+                    if (row0 >= m || col0 >= n) continue;       // warp-uniform
+                    uint8_t* buf = stg + (pieces & 1) * 4096 + lane * 128;
+                    if (lane == 0) bulk_wait_read_le1();        // the store issued two pieces ago has read this buffer
+                    __syncwarp();
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_ld_wait();
+                    if (f32_out) {
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            float4 f = make_float4(a_eff * __uint_as_float(r[q * 4]), a_eff * __uint_as_float(r[q * 4 + 1]),
+                                                   a_eff * __uint_as_float(r[q * 4 + 2]), a_eff * __uint_as_float(r[q * 4 + 3]));
+                            *reinterpret_cast<float4*>(buf + ((q ^ (lane & 7)) << 4)) = f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int half = 0; half < 2; half++) {
+                            if (half) { tmem_ld32(taddr + c + 32, r); tmem_ld_wait(); }
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                uint4 pk;
+                                pk.x = pack2_bf16(a_eff * __uint_as_float(r[q * 8]), a_eff * __uint_as_float(r[q * 8 + 1]));
+                                pk.y = pack2_bf16(a_eff * __uint_as_float(r[q * 8 + 2]), a_eff * __uint_as_float(r[q * 8 + 3]));
+                                pk.z = pack2_bf16(a_eff * __uint_as_float(r[q * 8 + 4]), a_eff * __uint_as_float(r[q * 8 + 5]));
+                                pk.w = pack2_bf16(a_eff * __uint_as_float(r[q * 8 + 6]), a_eff * __uint_as_float(r[q * 8 + 7]));
+                                *reinterpret_cast<uint4*>(buf + (((half * 4 + q) ^ (lane & 7)) << 4)) = pk;
+                            }
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(&tmC, stg_u32 + (pieces & 1) * 4096, col0, row0, ksplit > 1 ? split : 0);
+                        bulk_commit2();
+                    }
+                    pieces++;
+                }
+            } else {
+                TO* crow = C + (long long)row * n;
+                const TO* drow = (D && beta != 0.f) ? D + (long long)row * n : nullptr;
+                float* wrow = ws + ((long long)split * m + row) * n;
+#pragma unroll 1
+                for (int c = 0; c < BN2; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    tmem_ld_wait();
+                    const int col0 = tn * BN2 + c;
+                    if (row < m && col0 < n) {
+                        if (ksplit > 1) epi_store<float>(wrow, nullptr, r, col0, n - col0, 1.f, 0.f, (n & 3) == 0);
+                        else epi_store<TO>(crow, drow, r, col0, n - col0, alpha, beta, vec_ok);
+                    }
                 }
             }
             tc_fence_before();
             mbar_arrive_cluster(tempty_leader + 8 * acc);   // 256 arrivals (both CTAs) free the accumulator
+            if (timing && threadIdx.x == 64) prof[6] = clock64();
         }
+        if (tma_out && lane == 0) bulk_wait_read_all();       // staging stays valid until the last store has read it
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_GEMM2 | 3); }
     }
     tc_fence_before();
@@ -216,10 +300,13 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     __syncwarp();
     cluster_sync_all();                                    // nobody frees TMEM while the peer may still use the pair
     if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc2(tmem_base, 512); }
+    if (timing && threadIdx.x == 0) prof[7] = clock64();
 }
 
 // ── host ────────────────────────────────────────────────────────────────────
 extern float* ax_splitk_ws(size_t* bytes);
+extern int ax_gemm_pdl(void);
+extern int ax_gemm_tma_out(void);
 template <typename TO>
 void ax_splitk_reduce_launch(const float* ws, int ksplit, TO* C, const TO* D, long long mn, float alpha, float beta, cudaStream_t st);
 
@@ -257,6 +344,28 @@ static int gemm2_launch(int slot, const void* A, const void* B, void* C, const v
     if (B_MN) { dims[0] = n; dims[1] = k; strides[0] = (uint64_t)n * 2; box[0] = 64; box[1] = BK2; }
     else { dims[0] = k; dims[1] = n; strides[0] = (uint64_t)k * 2; box[0] = BK2; box[1] = 128; }
     if (tc_make_tmap_bf16(&tmB, B, 2, dims, strides, box, true)) return 2;
+    // output through TMA tile stores when the destination allows it and no addend has to be read
+    const int osz = ksplit > 1 ? 4 : (int)sizeof(TO);
+    const bool tma_out = ax_gemm_tma_out() && (D == nullptr || beta == 0.f) && ((uintptr_t)C & 15) == 0 &&
+                         ((long long)n * osz) % 16 == 0;
+    CUtensorMap tmC;
+    if (tma_out) {
+        PFN_tmapEncodeTiled enc = tc_encode_fn();
+        if (!enc) return 2;
+        size_t wsb0 = 0;
+        void* base = ksplit > 1 ? (void*)ax_splitk_ws(&wsb0) : C;
+        cuuint64_t gd[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)(ksplit > 1 ? ksplit : 1)};
+        cuuint64_t gs[2] = {(cuuint64_t)n * osz, (cuuint64_t)m * n * osz};
+        cuuint32_t bx[3] = {(cuuint32_t)(128 / osz), 32, 1};
+        cuuint32_t es[3] = {1, 1, 1};
+        if (gs[1] % 16 != 0) gs[1] = (gs[1] + 15) / 16 * 16;     // only reached with a single split (never indexed)
+        CUresult r = enc(&tmC, osz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, gd, gs, bx,
+                         es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return 2;
+    } else {
+        tmC = tmA;
+    }
     const int units = ((m + 255) / 256) * ((n + 255) / 256) * ksplit;
     const int pairs = units < maxp ? units : maxp;
     size_t wsb = 0;
@@ -266,12 +375,25 @@ static int gemm2_launch(int slot, const void* A, const void* B, void* C, const v
     cfg.blockDim = dim3(THREADS2, 1, 1);
     cfg.dynamicSmemBytes = SMEM2;
     cfg.stream = st;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = ax_gemm_pdl() ? 2 : 1;
     TO* Cp = (TO*)C; const TO* Dp = (const TO*)D;
-    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA, tmB, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws) != cudaSuccess) return 3;
+    static const bool want_prof = getenv("AXENG_GEMM_PROF") != nullptr;     // debugging aid, prints to stderr
+    long long* prof = nullptr;
+    if (want_prof && (cudaMalloc(&prof, 64) != cudaSuccess || cudaMemset(prof, 0, 64) != cudaSuccess)) prof = nullptr;
+    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA, tmB, tmC, (int)tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
+    if (prof) {
+        long long h[8];
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h, prof, 64, cudaMemcpyDeviceToHost);
+        cudaFree(prof);
+        fprintf(stderr, "gemm2 %dx%dx%d split %d pairs %d (cycles from entry): setup %lld dep %lld first_full %lld last_mma %lld last_acc %lld stored %lld exit %lld\n",
+                m, n, k, ksplit, pairs, h[1] - h[0], h[2] - h[0], h[3] - h[0], h[4] - h[0], h[5] - h[0], h[6] - h[0], h[7] - h[0]);
+    }
     if (ksplit > 1) ax_splitk_reduce_launch<TO>(ws, ksplit, Cp, Dp, (long long)m * n, alpha, beta, st);
     return 0;
 }

@@ -294,6 +294,80 @@ __global__ void k_ce_rows(const T* logits, const int* tgt, T* dlogits, float* lo
         if (threadIdx.x == 0) loss[0] = acc * inv;
     }
 }
+// bf16 rows of up to 512 * 8 * 8 = 32768 logits: the row is read from DRAM once into registers
+// (8 packed 16-byte vectors per thread), reduced, and written back — one read and one write per element.
+#define CE_VPT 8
+__global__ void __launch_bounds__(512, 2)
+k_ce_rows_reg(const bf16* logits, const int* __restrict__ tgt, bf16* dlogits, float* loss, const float* denom,
+              float* rowloss, unsigned int* counter, int Nrows, int V) {
+    __shared__ float sh[40];
+    __shared__ float s_xt;
+    __shared__ bool s_last;
+    const float inv = 1.f / denom[0];
+    const int nvec = V >> 3;
+    for (int r = blockIdx.x; r < Nrows; r += gridDim.x) {
+        const bf16* lr = logits + (long long)r * V;
+        bf16* dr = dlogits + (long long)r * V;
+        const int t = tgt[r];
+        if (t < 0) {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int j = threadIdx.x; j < nvec; j += 512) reinterpret_cast<uint4*>(dr)[j] = z;
+            if (threadIdx.x == 0) rowloss[r] = 0.f;
+            continue;
+        }
+        uint4 pk[CE_VPT];
+#pragma unroll
+        for (int i = 0; i < CE_VPT; i++) {
+            const int j = threadIdx.x + i * 512;
+            pk[i] = j < nvec ? reinterpret_cast<const uint4*>(lr)[j] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);  // -inf
+        }
+        if (threadIdx.x == 0) s_xt = __bfloat162float(lr[t]);
+        float m = -3.0e38f;
+#pragma unroll
+        for (int i = 0; i < CE_VPT; i++) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk[i]);
+#pragma unroll
+            for (int q = 0; q < 4; q++) { const float2 f = __bfloat1622float2(h[q]); m = fmaxf(m, fmaxf(f.x, f.y)); }
+        }
+        const float M = block_max(m, sh);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < CE_VPT; i++) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk[i]);
+#pragma unroll
+            for (int q = 0; q < 4; q++) { const float2 f = __bfloat1622float2(h[q]); s += __expf(f.x - M) + __expf(f.y - M); }
+        }
+        const float S = block_sum(s, sh);
+        const float sc = inv / S;
+#pragma unroll
+        for (int i = 0; i < CE_VPT; i++) {
+            const int j = threadIdx.x + i * 512;
+            if (j < nvec) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk[i]);
+                float f[8];
+#pragma unroll
+                for (int q = 0; q < 4; q++) { const float2 v = __bfloat1622float2(h[q]); f[2 * q] = v.x; f[2 * q + 1] = v.y; }
+#pragma unroll
+                for (int q = 0; q < 8; q++) f[q] = __expf(f[q] - M) * sc - ((j * 8 + q) == t ? inv : 0.f);
+                Vec<bf16>::st(dr + j * 8, f);
+            }
+        }
+        if (threadIdx.x == 0) rowloss[r] = logf(S) - (s_xt - M);
+        __syncthreads();
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        float acc = 0.f;
+        for (int i = threadIdx.x; i < Nrows; i += blockDim.x) acc += __ldcg(rowloss + i);
+        acc = block_sum(acc, sh);
+        if (threadIdx.x == 0) loss[0] = acc * inv;
+    }
+}
+
 int ax_ce_fused(int dt, const void* logits, const int* tgt, void* dlogits, float* loss, float* denom,
                 float* scratch, int N, int V, cudaStream_t st) {
     if (N <= 0 || V <= 0) return 0;
@@ -304,6 +378,11 @@ int ax_ce_fused(int dt, const void* logits, const int* tgt, void* dlogits, float
     const bool vec = V % per == 0 && aligned16(logits) && aligned16(dlogits);
     const int thr = V >= 4096 ? 512 : 256;
     const int grid = N < AX_SMS * 16 ? N : AX_SMS * 16;
+    if (dt == 1 && vec && V >= 2048 && V <= 512 * 8 * CE_VPT) {
+        const int g2 = N < AX_SMS * 8 ? N : AX_SMS * 8;
+        k_ce_rows_reg<<<g2, 512, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V);
+        return 0;
+    }
     if (dt == 1) {
         if (vec) k_ce_rows<bf16, true><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V);
         else k_ce_rows<bf16, false><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V);
