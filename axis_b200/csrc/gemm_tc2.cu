@@ -30,7 +30,7 @@
 #define B_BYTES2 (128 * BK2 * 2)
 #define STAGE_BYTES2 (A_BYTES2 + B_BYTES2)
 #define STG_BYTES2 (4 * 2 * 4096)      // output staging: per epilogue warp two buffers of 32 rows x 128 B
-#define SMEM2 (STAGES2 * STAGE_BYTES2 + STG_BYTES2 + 1024 + 256)
+#define SMEM2 (STAGES2 * STAGE_BYTES2 + STG_BYTES2 + 1024 + 512)
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -54,6 +54,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src,
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
 }
 __device__ __forceinline__ void bulk_commit2() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_le2() { asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
@@ -92,12 +98,15 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar) {
 template <int A_MN, int B_MN, typename TO>
 __global__ void __launch_bounds__(THREADS2, 1)
 k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-           const __grid_constant__ CUtensorMap tmC, int tma_out,
+           const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, int tma_out,
            TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status,
            int ksplit, float* __restrict__ ws, long long* prof) {
     // tma_out != 0: the epilogue stages 32 x 128-byte pieces in shared memory (128-byte swizzle) and writes
     // them with TMA tile stores through tmC — {n, m, 1} over C, or {n, m, ksplit} over the fp32 split-K
     // workspace; the hardware clips pieces that overhang the matrix.  Otherwise threads store their rows.
+    // tma_out == 2: the addend D is fetched the same way (TMA tile loads through tmD, two pieces ahead, into
+    // the staging buffer where the result then replaces it); the operand ring then runs with five stages and
+    // the sixth stage's memory doubles the staging area (four buffers per epilogue warp).
     // prof (optional, normally null): clock64 stamps of pair 0's leader CTA — [0] entry, [1] set-up done,
     // [2] predecessor grid finished, [3] first operands landed, [4] last MMA issued, [5] last accumulator
     // complete, [6] last tile stored, [7] exit
@@ -111,6 +120,8 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t smem_base = smem_u32(smem);
+    const int nst = tma_out == 2 ? STAGES2 - 1 : STAGES2;          // operand stages in use
+    const uint32_t bar_d = smem_u32(bars + 20);                    // [4 warps][4 buffers] addend-arrival barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                 // 0 = leader (issues the MMAs)
@@ -124,11 +135,13 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES2; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
         for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 256); }
+        for (int a = 0; a < 16; a++) mbar_init(bar_d + 8 * a, 1);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
         if (tma_out) tma_prefetch_desc(&tmC);
+        if (tma_out == 2) tma_prefetch_desc(&tmD);
     }
     if (warp == 1) { tmem_alloc2(smem_u32(tmem_slot), 512); tmem_relinquish2(); }
     tc_fence_before();
@@ -146,17 +159,16 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 
     if (warp == 0 && lane == 0) {
         // ── TMA producer (both CTAs): own 128 rows of A, own 128 columns of B ──
-        uint32_t it = 0;
+        uint32_t it = 0, ph = 0;
+        int s = 0;
         bool ok = true;
         for (int unit = pair; unit < num_units && ok; unit += npairs) {
             const int tile = unit % num_tiles, split = unit / num_tiles;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
             const int row0 = tm * 2 * BM2 + rank * BM2, col0 = tn * BN2 + rank * 128;
-            for (int kb = kb0; kb < kb1; kb++, it++) {
-                const int s = it % STAGES2;
-                const uint32_t ph = (it / STAGES2) & 1;
-                if (it >= (uint32_t)STAGES2 && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
+            for (int kb = kb0; kb < kb1; kb++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
+                if (it >= (uint32_t)nst && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
                 const uint32_t sa = smem_base + s * STAGE_BYTES2, sb = sa + A_BYTES2;
                 const uint32_t fb = full_leader + 8 * s;
@@ -179,7 +191,8 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ── MMA issuer (leader CTA only) ──
         constexpr uint32_t idesc = tc_idesc_bf16(256, BN2, A_MN, B_MN);
-        uint32_t it = 0, tcount = 0;
+        uint32_t it = 0, tcount = 0, ph = 0;
+        int s = 0;
         bool ok = true;
         for (int unit = pair; unit < num_units && ok; unit += npairs, tcount++) {
             const int split = unit / num_tiles;
@@ -189,9 +202,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             if (tcount >= 2 && !mbar_wait(bar_tempty + 8 * acc, aph ^ 1)) { ok = false; break; }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN2;
-            for (int kb = kb0; kb < kb1; kb++, it++) {
-                const int s = it % STAGES2;
-                const uint32_t ph = (it / STAGES2) & 1;
+            for (int kb = kb0; kb < kb1; kb++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
                 if (!mbar_wait(bar_full + 8 * s, ph) || *abort_flag) { ok = false; break; }
                 tc_fence_after();
                 if (timing && it == 0) prof[3] = clock64();
@@ -217,27 +228,51 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                             (!D || (reinterpret_cast<uintptr_t>(D) & 15) == 0);
         const bool f32_out = ksplit > 1 || sizeof(TO) == 4;
         const float a_eff = ksplit > 1 ? 1.f : alpha;
-        uint8_t* stg = smem + STAGES2 * STAGE_BYTES2 + quad * 8192;
-        const uint32_t stg_u32 = smem_base + STAGES2 * STAGE_BYTES2 + quad * 8192;
+        // staging: two 4 KB buffers per warp behind the operand ring; four when the addend is fetched by TMA
+        // (the ring's last stage is then unused and adjoins the staging area)
+        const int nbuf = tma_out == 2 ? 4 : 2;
+        const uint32_t stg_off = tma_out == 2 ? (STAGES2 - 1) * STAGE_BYTES2 + quad * 16384 : STAGES2 * STAGE_BYTES2 + quad * 8192;
+        uint8_t* stg = smem + stg_off;
+        const uint32_t stg_u32 = smem_base + stg_off;
+        const uint32_t my_bar_d = bar_d + 32 * quad;
+        uint32_t dpar = 0;                                      // phase parity of each addend barrier
         for (int unit = pair; unit < num_units && ok; unit += npairs, tcount++) {
             const int tile = unit % num_tiles, split = unit / num_tiles;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
+            const int row0 = tm * 2 * BM2 + rank * BM2 + quad * 32;
+            const int row = row0 + lane;
+            const int cw = f32_out ? 32 : 64;                   // columns per 128-byte piece
+            const int ncols = min(BN2, n - tn * BN2);
+            const int npc = (tma_out && row0 < m) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
+            const uint32_t pbase = pieces;
+            auto fetch_d = [&](int j) {                          // lane 0: addend piece j of this tile -> its buffer
+                const uint32_t bi = (pbase + j) & 3;
+                mbar_expect_tx(my_bar_d + 8 * bi, 4096);
+                tma_load_3d(stg_u32 + bi * 4096, &tmD, my_bar_d + 8 * bi, tn * BN2 + j * cw, row0, 0);
+            };
+            if (tma_out == 2 && lane == 0 && npc > 0) {          // the first two addend pieces travel during the main loop
+                bulk_wait_read_le2();
+                fetch_d(0);
+                if (npc > 1) fetch_d(1);
+            }
             if (!mbar_wait(bar_tfull + 8 * acc, aph) || *abort_flag) { ok = false; break; }
             tc_fence_after();
             if (timing && threadIdx.x == 64) prof[5] = clock64();
-            const int row0 = tm * 2 * BM2 + rank * BM2 + quad * 32;
-            const int row = row0 + lane;
             const uint32_t taddr = tmem_base + acc * BN2 + ((uint32_t)(quad * 32) << 16);
             if (tma_out) {
-                const int cw = f32_out ? 32 : 64;              // columns per 128-byte piece
 #pragma unroll 1
-                for (int c = 0; c < BN2; c += cw) {
-                    const int col0 = tn * BN2 + c;
-                    if (row0 >= m || col0 >= n) continue;       // warp-uniform
-                    uint8_t* buf = stg + (pieces & 1) * 4096 + lane * 128;
-                    if (lane == 0) bulk_wait_read_le1();        // the store issued two pieces ago has read this buffer
+                for (int j = 0; j < npc && ok; j++) {
+                    const int c = j * cw;
+                    const uint32_t bi = pieces & (nbuf - 1);
+                    uint8_t* buf = stg + bi * 4096 + lane * 128;
+                    if (lane == 0) bulk_wait_read_le1();        // all but the latest store have read their buffers
+                    if (tma_out == 2) {
+                        if (lane == 0 && j + 2 < npc) fetch_d(j + 2);
+                        if (!mbar_wait(my_bar_d + 8 * bi, (dpar >> bi) & 1)) { ok = false; break; }
+                        dpar ^= 1u << bi;
+                    }
                     __syncwarp();
                     uint32_t r[32];
                     tmem_ld32(taddr + c, r);
@@ -245,9 +280,14 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                     if (f32_out) {
 #pragma unroll
                         for (int q = 0; q < 8; q++) {
+                            float4* slot = reinterpret_cast<float4*>(buf + ((q ^ (lane & 7)) << 4));
                             float4 f = make_float4(a_eff * __uint_as_float(r[q * 4]), a_eff * __uint_as_float(r[q * 4 + 1]),
                                                    a_eff * __uint_as_float(r[q * 4 + 2]), a_eff * __uint_as_float(r[q * 4 + 3]));
-                            *reinterpret_cast<float4*>(buf + ((q ^ (lane & 7)) << 4)) = f;
+                            if (tma_out == 2) {
+                                const float4 d = *slot;
+                                f.x += beta * d.x; f.y += beta * d.y; f.z += beta * d.z; f.w += beta * d.w;
+                            }
+                            *slot = f;
                         }
                     } else {
 #pragma unroll
@@ -255,23 +295,35 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                             if (half) { tmem_ld32(taddr + c + 32, r); tmem_ld_wait(); }
 #pragma unroll
                             for (int q = 0; q < 4; q++) {
+                                uint4* slot = reinterpret_cast<uint4*>(buf + (((half * 4 + q) ^ (lane & 7)) << 4));
+                                float f[8];
+#pragma unroll
+                                for (int e = 0; e < 8; e++) f[e] = a_eff * __uint_as_float(r[q * 8 + e]);
+                                if (tma_out == 2) {
+                                    const uint4 d = *slot;
+                                    const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                                    for (int e = 0; e < 4; e++) {
+                                        f[2 * e] += beta * __uint_as_float(dw[e] << 16);
+                                        f[2 * e + 1] += beta * __uint_as_float(dw[e] & 0xffff0000u);
+                                    }
+                                }
                                 uint4 pk;
-                                pk.x = pack2_bf16(a_eff * __uint_as_float(r[q * 8]), a_eff * __uint_as_float(r[q * 8 + 1]));
-                                pk.y = pack2_bf16(a_eff * __uint_as_float(r[q * 8 + 2]), a_eff * __uint_as_float(r[q * 8 + 3]));
-                                pk.z = pack2_bf16(a_eff * __uint_as_float(r[q * 8 + 4]), a_eff * __uint_as_float(r[q * 8 + 5]));
-                                pk.w = pack2_bf16(a_eff * __uint_as_float(r[q * 8 + 6]), a_eff * __uint_as_float(r[q * 8 + 7]));
-                                *reinterpret_cast<uint4*>(buf + (((half * 4 + q) ^ (lane & 7)) << 4)) = pk;
+                                pk.x = pack2_bf16(f[0], f[1]); pk.y = pack2_bf16(f[2], f[3]);
+                                pk.z = pack2_bf16(f[4], f[5]); pk.w = pack2_bf16(f[6], f[7]);
+                                *slot = pk;
                             }
                         }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_3d(&tmC, stg_u32 + (pieces & 1) * 4096, col0, row0, ksplit > 1 ? split : 0);
+                        tma_store_3d(&tmC, stg_u32 + bi * 4096, tn * BN2 + c, row0, ksplit > 1 ? split : 0);
                         bulk_commit2();
                     }
                     pieces++;
                 }
+                if (!ok) break;
             } else {
                 TO* crow = C + (long long)row * n;
                 const TO* drow = (D && beta != 0.f) ? D + (long long)row * n : nullptr;
@@ -344,11 +396,13 @@ static int gemm2_launch(int slot, const void* A, const void* B, void* C, const v
     if (B_MN) { dims[0] = n; dims[1] = k; strides[0] = (uint64_t)n * 2; box[0] = 64; box[1] = BK2; }
     else { dims[0] = k; dims[1] = n; strides[0] = (uint64_t)k * 2; box[0] = BK2; box[1] = 128; }
     if (tc_make_tmap_bf16(&tmB, B, 2, dims, strides, box, true)) return 2;
-    // output through TMA tile stores when the destination allows it and no addend has to be read
+    // output through TMA tile stores when the destination allows it: 1 = no addend to read, 2 = addend by TMA too
     const int osz = ksplit > 1 ? 4 : (int)sizeof(TO);
-    const bool tma_out = ax_gemm_tma_out() && (D == nullptr || beta == 0.f) && ((uintptr_t)C & 15) == 0 &&
-                         ((long long)n * osz) % 16 == 0;
-    CUtensorMap tmC;
+    const bool has_d = D != nullptr && beta != 0.f && ksplit == 1;
+    int tma_out = 0;
+    if (ax_gemm_tma_out() && ((uintptr_t)C & 15) == 0 && ((long long)n * osz) % 16 == 0 && (!has_d || ((uintptr_t)D & 15) == 0))
+        tma_out = has_d ? 2 : 1;
+    CUtensorMap tmC, tmD;
     if (tma_out) {
         PFN_tmapEncodeTiled enc = tc_encode_fn();
         if (!enc) return 2;
@@ -359,12 +413,18 @@ static int gemm2_launch(int slot, const void* A, const void* B, void* C, const v
         cuuint32_t bx[3] = {(cuuint32_t)(128 / osz), 32, 1};
         cuuint32_t es[3] = {1, 1, 1};
         if (gs[1] % 16 != 0) gs[1] = (gs[1] + 15) / 16 * 16;     // only reached with a single split (never indexed)
-        CUresult r = enc(&tmC, osz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, gd, gs, bx,
-                         es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const CUtensorMapDataType dtp = osz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        CUresult r = enc(&tmC, dtp, 3, base, gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return 2;
+        tmD = tmC;
+        if (tma_out == 2) {
+            r = enc(&tmD, dtp, 3, const_cast<void*>(D), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return 2;
+        }
     } else {
-        tmC = tmA;
+        tmC = tmA; tmD = tmA;
     }
     const int units = ((m + 255) / 256) * ((n + 255) / 256) * ksplit;
     const int pairs = units < maxp ? units : maxp;
@@ -385,7 +445,7 @@ static int gemm2_launch(int slot, const void* A, const void* B, void* C, const v
     static const bool want_prof = getenv("AXENG_GEMM_PROF") != nullptr;     // debugging aid, prints to stderr
     long long* prof = nullptr;
     if (want_prof && (cudaMalloc(&prof, 64) != cudaSuccess || cudaMemset(prof, 0, 64) != cudaSuccess)) prof = nullptr;
-    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA, tmB, tmC, (int)tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
+    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA, tmB, tmC, tmD, tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
     if (prof) {
         long long h[8];
         cudaStreamSynchronize(st);

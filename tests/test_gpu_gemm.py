@@ -97,6 +97,23 @@ def test_bf16_epilogues_and_addend(eng, tb):
 
 
 @pytest.mark.parametrize("tb", [0, 1, 2])
+@pytest.mark.parametrize("dt", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(520, 776, 320), (256, 264, 64), (1032, 256, 2112)])
+def test_paired_kernel_staged_output(eng, tb, dt, m, n, k):
+    """Paired-CTA kernel forced (mask 8): output pieces staged in shared memory and written by TMA
+    stores clipped at ragged edges; in-place accumulation and a separate addend arrive by TMA loads;
+    the long-k shape also runs the split-K workspace through the same stores."""
+    rng = np.random.default_rng(m + n + k + tb + dt)
+    got, ref = run_gemm(eng, rng, m, n, k, tb, dt, fallback=8)
+    check(got, ref, dt == 1, k)
+    got, ref = run_gemm(eng, rng, m, n, k, tb, dt, alpha=0.5, beta=1.0, fallback=8)
+    check(got, ref, dt == 1, k)
+    got, ref = run_gemm(eng, rng, m, n, k, tb, dt, beta=-2.0, addend=True, fallback=8)
+    check(got, ref, dt == 1, k)
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("tb", [0, 1, 2])
 def test_tensor_core_and_general_path_agree(eng, tb):
     for dt in (1, 2):
         a = run_gemm(eng, np.random.default_rng(9), 256, 256, 256, tb, dt)[0]
