@@ -115,7 +115,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (!mbar_wait(b_q, 0)) ok = false;
             for (int j = 0; j < nkt && ok; j++) {
                 const int s = j & 1;
-                if (!mbar_wait(b_kvf + 8 * s, (j >> 1) & 1) || *abort_flag) { ok = false; break; }
+                if (!mbar_wait(b_kvf + 8 * s, (j >> 1) & 1)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < ADH / 16; kk++)
@@ -128,7 +128,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     tma_load_4d(sb + FwdSmem::K0 + s2 * 16384, &tmK, b_kvf + 8 * s2, 0, g, (j + 1) * AT, b);
                     tma_load_4d(sb + FwdSmem::V0 + s2 * 16384, &tmV, b_kvf + 8 * s2, 0, g, (j + 1) * AT, b);
                 }
-                if (!mbar_wait(b_p, j & 1) || *abort_flag) { ok = false; break; }
+                if (!mbar_wait(b_p, j & 1)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < AT / 16; kk++)
@@ -363,7 +363,7 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             for (int u = 0; u < n_sub && ok; u++) {
                 const int e = u & 1, it = u >> 1, sl = u & 3;
-                if (!mbar_wait(b_pds + 8 * e, (u >> 1) & 1) || *abort_flag) { ok = false; break; }
+                if (!mbar_wait(b_pds + 8 * e, (u >> 1) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t so = (uint32_t)sl * 512;
                 // P^T / dS^T in TMEM: the 64 queries packed in columns 0..31 of the buffer
