@@ -1,5 +1,7 @@
 // Index-based ops: embedding gather / scatter-add, valid-target count and
 // token-mean cross-entropy with ignored targets (target < 0).
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -330,12 +332,21 @@ k_ce_rows_reg(const bf16* logits, const int* __restrict__ tgt, bf16* dlogits, fl
             for (int q = 0; q < 4; q++) { const float2 f = __bfloat1622float2(h[q]); m = fmaxf(m, fmaxf(f.x, f.y)); }
         }
         const float M = block_max(m, sh);
+        // one exponential per element: e = exp(x - M) replaces x in the same registers as packed fp16 (e <= 1,
+        // 11-bit mantissa: finer than the bf16 the gradient is stored in); the sum uses the fp32 values
         float s = 0.f;
 #pragma unroll
         for (int i = 0; i < CE_VPT; i++) {
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk[i]);
+            __half2 eh[4];
 #pragma unroll
-            for (int q = 0; q < 4; q++) { const float2 f = __bfloat1622float2(h[q]); s += __expf(f.x - M) + __expf(f.y - M); }
+            for (int q = 0; q < 4; q++) {
+                const float2 f = __bfloat1622float2(h[q]);
+                const float e0 = __expf(f.x - M), e1 = __expf(f.y - M);
+                s += e0 + e1;
+                eh[q] = __floats2half2_rn(e0, e1);
+            }
+            pk[i] = *reinterpret_cast<const uint4*>(eh);
         }
         const float S = block_sum(s, sh);
         const float sc = inv / S;
@@ -343,12 +354,12 @@ k_ce_rows_reg(const bf16* logits, const int* __restrict__ tgt, bf16* dlogits, fl
         for (int i = 0; i < CE_VPT; i++) {
             const int j = threadIdx.x + i * 512;
             if (j < nvec) {
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk[i]);
+                const __half2* h = reinterpret_cast<const __half2*>(&pk[i]);
                 float f[8];
 #pragma unroll
-                for (int q = 0; q < 4; q++) { const float2 v = __bfloat1622float2(h[q]); f[2 * q] = v.x; f[2 * q + 1] = v.y; }
+                for (int q = 0; q < 4; q++) { const float2 v = __half22float2(h[q]); f[2 * q] = v.x; f[2 * q + 1] = v.y; }
 #pragma unroll
-                for (int q = 0; q < 8; q++) f[q] = __expf(f[q] - M) * sc - ((j * 8 + q) == t ? inv : 0.f);
+                for (int q = 0; q < 8; q++) f[q] = f[q] * sc - ((j * 8 + q) == t ? inv : 0.f);
                 Vec<bf16>::st(dr + j * 8, f);
             }
         }

@@ -141,27 +141,30 @@ k_rmsnorm_bwd_warp(const T* __restrict__ x, const T* __restrict__ w, const T* __
     for (int j = threadIdx.x; j < DIM; j += blockDim.x) partial[(long long)blockIdx.x * DIM + j] = sdw[j];
 }
 
-// bf16 specialisation: rows stay packed (16-byte vectors) in registers, so 4-warp blocks fit three
-// to an SM, every lane has 3*VPL loads in flight, and x, g and the residual are each read once.
-#define RBP_WARPS 4
+// bf16 specialisation: rows stay packed (16-byte vectors) in registers and the dw partial of every warp
+// accumulates in its own shared-memory row (a lane only ever touches its own columns, so no synchronisation),
+// which leaves room for 8-warp blocks, two to an SM: sixteen rows with 3*VPL 16-byte loads per lane in flight
+// per SM, and x, g and the residual are each read once.
+#define RBP_WARPS 8
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
     for (int i = 0; i < 4; i++) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
 template <int VPL>
-__global__ void __launch_bounds__(RBP_WARPS * 32, 3)
+__global__ void __launch_bounds__(RBP_WARPS * 32, 2)
 k_rmsnorm_bwd_packed(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ g, const bf16* res,
                      bf16* dx, float* __restrict__ partial, int rows, float eps) {
     constexpr int DIM = 32 * VPL * 8;
-    __shared__ float sdw[DIM];
+    extern __shared__ float sdw_all[];                     // [RBP_WARPS][DIM]
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int gw = blockIdx.x * RBP_WARPS + wib, nw = gridDim.x * RBP_WARPS;
-    float dw[VPL][8];
+    float* sdw = sdw_all + wib * DIM;
 #pragma unroll
-    for (int i = 0; i < VPL; i++)
-#pragma unroll
-        for (int q = 0; q < 8; q++) dw[i][q] = 0.f;
+    for (int i = 0; i < VPL; i++) {
+        float4* p = reinterpret_cast<float4*>(sdw + (lane + 32 * i) * 8);
+        p[0] = make_float4(0.f, 0.f, 0.f, 0.f); p[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (int r = gw; r < rows; r += nw) {
         const long long base = (long long)r * DIM;
         uint4 xp[VPL], gp[VPL], rp[VPL];
@@ -189,28 +192,27 @@ k_rmsnorm_bwd_packed(const bf16* __restrict__ x, const bf16* __restrict__ w, con
             float xv[8], gv[8], wv[8], ov[8];
             unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(__ldg(reinterpret_cast<const uint4*>(w + (lane + 32 * i) * 8)), wv);
             if (res) unpack8(rp[i], ov);
+            float4* p = reinterpret_cast<float4*>(sdw + (lane + 32 * i) * 8);
+            float4 a0 = p[0], a1 = p[1];
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const float d = gv[q] * wv[q] * inv - xv[q] * coef;
                 ov[q] = res ? ov[q] + d : d;
-                dw[i][q] += gv[q] * xv[q] * inv;
             }
+            a0.x += gv[0] * xv[0] * inv; a0.y += gv[1] * xv[1] * inv; a0.z += gv[2] * xv[2] * inv; a0.w += gv[3] * xv[3] * inv;
+            a1.x += gv[4] * xv[4] * inv; a1.y += gv[5] * xv[5] * inv; a1.z += gv[6] * xv[6] * inv; a1.w += gv[7] * xv[7] * inv;
+            p[0] = a0; p[1] = a1;
             Vec<bf16>::st(dx + base + (lane + 32 * i) * 8, ov);
         }
     }
     if (!partial) return;
-    for (int j = threadIdx.x; j < DIM; j += blockDim.x) sdw[j] = 0.f;
     __syncthreads();
-    for (int turn = 0; turn < RBP_WARPS; turn++) {      // fixed order
-        if (wib == turn) {
+    for (int j = threadIdx.x; j < DIM; j += blockDim.x) {   // fixed order over the warps' rows
+        float t = 0.f;
 #pragma unroll
-            for (int i = 0; i < VPL; i++)
-#pragma unroll
-                for (int q = 0; q < 8; q++) sdw[(lane + 32 * i) * 8 + q] += dw[i][q];
-        }
-        __syncthreads();
+        for (int q = 0; q < RBP_WARPS; q++) t += sdw_all[q * DIM + j];
+        partial[(long long)blockIdx.x * DIM + j] = t;
     }
-    for (int j = threadIdx.x; j < DIM; j += blockDim.x) partial[(long long)blockIdx.x * DIM + j] = sdw[j];
 }
 
 static int norm_threads(int dim, int per) {
@@ -399,7 +401,7 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
         if (dt == 1) {
             int nbp = (rows + RBP_WARPS - 1) / RBP_WARPS;
             if (nbp > RB_BLOCKS) nbp = RB_BLOCKS;            // 296 blocks: two per SM resident at once, one wave
-#define BP(V) case V: k_rmsnorm_bwd_packed<V><<<nbp, RBP_WARPS * 32, 0, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
+#define BP(V) case V: k_rmsnorm_bwd_packed<V><<<nbp, RBP_WARPS * 32, (size_t)RBP_WARPS * dim * 4, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
             switch (vpl) { BP(1) BP(2) BP(3) BP(4) BP(5) BP(6) }
 #undef BP
             if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
