@@ -203,7 +203,29 @@ def barrier():
         dist.barrier()
 
 
+_RESULT_FD = None
+
+
+def _guard_stdout():
+    """Libraries loaded below (NCCL with NCCL_DEBUG set in the environment, for one) may write to
+    file descriptor 1.  The contract is ONE JSON line on stdout, so everything else is sent to stderr
+    and the result line is written to a private copy of the original descriptor."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode()); sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    _guard_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -228,7 +250,7 @@ def main():
                 "config": {"workload": c["name"]}, "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
-        print(json.dumps(line))
+        emit(line)
         return
 
     if WORLD > 1:
@@ -305,7 +327,7 @@ def main():
         line["cpu_baseline"] = cpu_reference(c)
     barrier()
     if RANK == 0:
-        print(json.dumps(line))
+        emit(line)
     if WORLD > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
@@ -353,12 +375,11 @@ def kernel_table(ct, c, batch):
         if o[0] in (E.GEMM, E.GEMM_SB, E.GEMM_EX):
             gemm_flops += 2.0 * o[5] * o[6] * o[7] * max(o[8], 1)
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            traffic = json.load(f).get("gemm_tc_bytes_per_launch")
-    out = {"roofline": {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 bf16 GEMM, all GEMM ops of the step)",
+    # DRAM bytes per GEMM launch inside this step (dram__bytes_read.sum + dram__bytes_write.sum averaged over
+    # 972 launches of one ncu capture of this command line; summary: profiles/step_1b_launch_list.md).
+    # It belongs to the 1B-class workload only.
+    traffic = 83.5e6 if c.get("name", "").startswith("1B-class") and "LoRA" not in c.get("name", "") else None
+    out = {"roofline": {"bound": "tensor", "kernel": "k_gemm_tc2 / k_gemm_tc (tcgen05 bf16 GEMM, all GEMM ops of the step)",
                         "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s", "frac": achieved / tf_sus,
                         "peak_source": f"{src} (sustained cuBLAS bf16)", "launches": gemm_calls,
                         "avg_launch_ms": gemm_ms / max(gemm_calls, 1), "traffic": traffic},
