@@ -1,5 +1,5 @@
 // Causal grouped-query flash attention on the 5th-generation tensor cores
-// (tcgen05 + TMEM), bf16, head_dim 64, on the [B,T,H,DH] layout that the
+// (tcgen05 + TMEM), bf16, head_dim 64 (head_dim 128: attn_tc128.cu), on the [B,T,H,DH] layout that the
 // projections produce.  Q/K/V/dO tiles arrive by TMA (128-byte swizzle, no
 // multicast); scores and gradients live in TMEM; probabilities go back into
 // TMEM as packed bf16 and feed the next MMA as its A operand.
@@ -25,41 +25,13 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "tc_common.cuh"
+#include "attn_common.cuh"
 
 #define AT 128                 // queries / keys per tile
 #define ADH 64                 // head dim served
 #define ATT_THREADS 160        // 4 softmax warps + 1 control warp
 #define STAT_FWD 0x200
 #define STAT_BWD 0x300
-#define LOG2E 1.4426950408889634f
-#define LN2 0.6931471805599453f
-
-__device__ __forceinline__ void named_bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-// Shared-memory descriptors of these kernels all use SBO = 1024 and 128-byte swizzle, so their upper
-// word is one constant and the lower word is (address >> 4) | (LBO >> 4) << 16: the MMA-issuing thread
-// keeps a few base words and adds tile offsets (in 16-byte units) instead of rebuilding descriptors.
-#define DESC_HI ((1024u >> 4) | (1u << 14) | (2u << 29))
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
-    return ((saddr & 0x3FFFF) >> 4) | ((lbo_bytes >> 4) << 16);
-}
-__device__ __forceinline__ uint64_t desc_of(uint32_t lo) { return ((uint64_t)DESC_HI << 32) | (uint64_t)lo; }
-__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, uint32_t src, int x, int y, int z, int w) {
-    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ════════════════════════════════ forward ═══════════════════════════════════
 struct FwdSmem {
@@ -581,7 +553,7 @@ __global__ void k_dq_convert(const float* __restrict__ src, bf16* __restrict__ d
 
 // ── host ────────────────────────────────────────────────────────────────────
 int ax_attn_tc_init(void) {
-    int rc = 0;
+    int rc = ax_attn_tc128_init();
     rc |= (int)cudaFuncSetAttribute(k_attn_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::TOTAL);
     rc |= (int)cudaFuncSetAttribute(k_attn_bwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
     return rc;
@@ -612,6 +584,7 @@ static int map_dq_f32(CUtensorMap* m, const void* base, int B, int T, int heads)
 
 int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
                    const AttnShape& s, int* status, cudaStream_t st) {
+    if (s.DH == 128) return ax_attn_fwd_tc128(q, k, v, o, lse, s, status, st);
     if (!served(s) || !lse || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return -1;
     CUtensorMap tq, tk, tv;
     if (map_bthd(&tq, q, s.B, s.T, s.H) || map_bthd(&tk, k, s.B, s.T, s.KV) || map_bthd(&tv, v, s.B, s.T, s.KV)) return 2;
@@ -623,6 +596,7 @@ int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* 
 int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dO,
                    const float* lse, float* Dscratch, float* g_dq_acc, void* dq, void* dk, void* dv,
                    const AttnShape& s, int* status, cudaStream_t st) {
+    if (s.DH == 128) return ax_attn_bwd_tc128(q, k, v, o, dO, lse, Dscratch, g_dq_acc, dq, dk, dv, s, status, st);
     if (!served(s) || !g_dq_acc || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) ||
         !aligned16(dq) || !aligned16(dk) || !aligned16(dv) || !aligned16(g_dq_acc)) return -1;
     const size_t need = (size_t)s.B * s.T * s.H * ADH * 4;

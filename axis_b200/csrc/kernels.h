@@ -92,9 +92,16 @@ int ax_attn_bwd_simt(int dt, int out_dt, const void* q, const void* k, const voi
 
 // attn_tc.cu — tcgen05 flash attention (bf16, DH 64/128). -1 when not served.
 int ax_attn_tc_init(void);
+int ax_attn_tc128_init(void);
 int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
                    const AttnShape& s, int* status, cudaStream_t st);
 // dq_acc: fp32 accumulator of B*T*H*DH elements for the dQ reduce-add (null -> not served)
 int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dO,
                    const float* lse, float* Dscratch, float* dq_acc, void* dq, void* dk, void* dv,
                    const AttnShape& s, int* status, cudaStream_t st);
+// attn_tc128.cu — the head_dim-128 kernels behind the two entry points above.
+int ax_attn_fwd_tc128(const void* q, const void* k, const void* v, void* o, float* lse,
+                      const AttnShape& s, int* status, cudaStream_t st);
+int ax_attn_bwd_tc128(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                      const float* lse, float* Dscratch, float* dq_acc, void* dq, void* dk, void* dv,
+                      const AttnShape& s, int* status, cudaStream_t st);

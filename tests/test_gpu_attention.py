@@ -50,7 +50,9 @@ def make(rng, B, H, KV, T, DH, dt):
 
 CASES = [(2, 4, 2, 32, 32), (1, 6, 2, 17, 16), (2, 2, 2, 64, 64), (1, 4, 1, 40, 128), (1, 3, 3, 130, 64),
          # head_dim 64 with whole 128-token tiles: the tcgen05 kernels when fallback == 0
-         (1, 4, 4, 128, 64), (2, 6, 2, 256, 64), (2, 3, 1, 384, 64), (1, 4, 2, 1024, 64)]
+         (1, 4, 4, 128, 64), (2, 6, 2, 256, 64), (2, 3, 1, 384, 64), (1, 4, 2, 1024, 64),
+         # head_dim 128 with whole tiles: the head_dim-128 tcgen05 kernels when fallback == 0
+         (1, 2, 2, 128, 128), (2, 4, 2, 256, 128), (1, 3, 1, 640, 128)]
 
 
 @pytest.mark.parametrize("dt", [0, 1])
@@ -63,7 +65,8 @@ def test_fused_attention_bthd(eng, dt, B, H, KV, T, DH, fallback):
     o_ref, lse_ref = O.attention_fwd(q, k, v, scale)
     t = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1, 3))
     iq, ik, iv, ido = put(eng, t(q), dt), put(eng, t(k), dt), put(eng, t(v), dt), put(eng, t(do), dt)
-    io, ilse, iD = eng.alloc(q.size), eng.alloc(B * H * T), eng.alloc(B * H * T)
+    # scratch of the backward: D = rowsum(dO*O) followed by the fp32 dQ accumulator of the tensor-core path
+    io, ilse, iD = eng.alloc(q.size), eng.alloc(B * H * T), eng.alloc(B * H * T + q.size)
     idq, idk, idv = eng.alloc(q.size), eng.alloc(k.size), eng.alloc(k.size)
     eng.set_fallback(fallback)
     eng.run([op(E.ATTN_FWD, a=iq, b=ik, d=iv, c=io, sa=ilse, m=T, n=DH, k=KV, batch=B, tb=H, dt=dt, alpha=scale)])
@@ -74,9 +77,13 @@ def test_fused_attention_bthd(eng, dt, B, H, KV, T, DH, fallback):
     assert np.abs(lse - lse_ref).max() <= (2e-2 if dt else 2e-5)
     o_in = bf(o) if dt else o
     dq_ref, dk_ref, dv_ref = O.attention_bwd(q, k, v, do, scale)
+    eng.launch_count(reset=True)
     eng.run([op(E.ATTN_BWD, a=iq, b=ik, d=iv, c=ido, sa=ilse, sb=io, tb=idq, sc=idk, oa=idv, ob=H, oc=iD,
                 m=T, n=DH, k=KV, batch=B, dt=dt, alpha=scale)])
     eng.set_fallback(0)
+    # the tensor-core backward is four launches (memset, prep, main, convert), the general one three
+    tc_expected = dt == 1 and fallback == 0 and DH in (64, 128) and T % 128 == 0
+    assert eng.launch_count() == (4 if tc_expected else 3)
     dq = get(eng, idq, (B, T, H, DH), dt).transpose(0, 2, 1, 3)
     dk = get(eng, idk, (B, T, KV, DH), dt).transpose(0, 2, 1, 3)
     dv = get(eng, idv, (B, T, KV, DH), dt).transpose(0, 2, 1, 3)
@@ -114,18 +121,19 @@ def test_reference_layout_flash_ops(eng):
     assert rel(eng.download(idv, k.shape), dv_ref) <= 2e-2
 
 
+@pytest.mark.parametrize("DH", [64, 128])
 @pytest.mark.parametrize("fallback", [0, 2])
-def test_attention_backward_is_deterministic(eng, fallback):
+def test_attention_backward_is_deterministic(eng, fallback, DH):
     """dK/dV are summed on chip in a fixed order in both paths.  dQ is bit-stable in the
     general path; the tensor-core path adds its per-key-tile dQ pieces with an unordered
     fp32 reduce-add (as the reference's atomics do), so dQ is only checked there for
     closeness."""
     rng = np.random.default_rng(1)
-    B, H, KV, T, DH = 1, 6, 2, 256, 64
+    B, H, KV, T = 1, 6, 2, 256
     q, k, v, do = make(rng, B, H, KV, T, DH, 1)
     t = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1, 3))
     iq, ik, iv, ido = put(eng, t(q), 1), put(eng, t(k), 1), put(eng, t(v), 1), put(eng, t(do), 1)
-    io, ilse, iD = eng.alloc(q.size, 2), eng.alloc(B * H * T), eng.alloc(B * H * T)
+    io, ilse, iD = eng.alloc(q.size, 2), eng.alloc(B * H * T), eng.alloc(B * H * T + q.size)
     idq, idk, idv = eng.alloc(q.size, 2), eng.alloc(k.size, 2), eng.alloc(k.size, 2)
     plan = [op(E.ATTN_FWD, a=iq, b=ik, d=iv, c=io, sa=ilse, m=T, n=DH, k=KV, batch=B, tb=H, dt=1, alpha=0.125),
             op(E.ATTN_BWD, a=iq, b=ik, d=iv, c=ido, sa=ilse, sb=io, tb=idq, sc=idk, oa=idv, ob=H, oc=iD,
