@@ -29,7 +29,7 @@ import numpy as np
 
 from axis_b200.engine import (
     ADAMW_FLAT, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, EMBED_BWD_DET,
-    EMBED_I32, FORK, GEMM_EX, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
+    EMBED_I32, FORK, GEMM_EX, GEMM_GROUP, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
     ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, Engine, f32_to_bf16_bits, op)
 
 LIN_ORDER = ("attn.q_proj", "attn.k_proj", "attn.v_proj", "attn.o_proj",
@@ -324,6 +324,55 @@ class CompiledTransformer:
                        op(GEMM_SB, a=u, b=g, c=G[key + ".lora_b"], m=lora_r, n=fout, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l)]
             return o_
 
+        def lora_f(x, i, pref, y):
+            """y += s*(x@A)@B for an adapted projection, u = x@A saved"""
+            if not (lora and pref.split(".")[-1] in lset):
+                return []
+            fin, fout = lin_geom[pref]
+            key = f"blocks.{i}.{pref}"
+            u = u_l[(i, pref)]
+            return [op(GEMM_SB, a=x, b=P[key + ".lora_a"], c=u, m=N, k=fin, n=lora_r, batch=1, dt=DT),
+                    op(GEMM_SB, a=u, b=P[key + ".lora_b"], c=y, m=N, k=lora_r, n=fout, batch=1, dt=DT,
+                       alpha=sc_l, beta=1.0)]
+
+        def lin_f_group(x, i, prefs, ys_):
+            """ys_[g] = x@W_g for projections that share their input: one grouped launch (+ adapters)"""
+            fin = lin_geom[prefs[0]][0]
+            fo = [lin_geom[p][1] for p in prefs] + [0]
+            w = [P[f"blocks.{i}.{p}.weight"] for p in prefs] + [0]
+            yy = list(ys_) + [0]
+            o_ = [op(GEMM_GROUP, a=x, b=w[0], sa=w[1], sb=w[2], c=yy[0], d=yy[1], sc=yy[2], m=N, k=fin,
+                     n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, dt=DT)]
+            for p_, y_ in zip(prefs, ys_):
+                o_ += lora_f(x, i, p_, y_)
+            return o_
+
+        def lin_b_group(gs_, x, i, prefs, dx):
+            """dx = sum_g gs_[g]@W_g^T in one launch; weight grads of all g in one launch (or adapter grads)"""
+            fin = lin_geom[prefs[0]][0]
+            fo = [lin_geom[p][1] for p in prefs] + [0]
+            keys = [f"blocks.{i}.{p}" for p in prefs]
+            w = [P[k_ + ".weight"] for k_ in keys] + [0]
+            gg = list(gs_) + [0]
+            o_ = [op(GEMM_GROUP, c=dx, a=gg[0], sa=gg[1], sb=gg[2], b=w[0], d=w[1], sc=w[2], m=N, n=fin,
+                     k=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=2, tb=1, dt=DT)]
+            if not lora:
+                gw = [G[k_ + ".weight"] for k_ in keys] + [0]
+                o_ += [op(GEMM_GROUP, a=x, b=gg[0], sa=gg[1], sb=gg[2], c=gw[0], d=gw[1], sc=gw[2], m=fin, k=N,
+                          n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, tb=2, dt=DTW)]
+            else:
+                for p_, g_, k_ in zip(prefs, gs_, keys):
+                    if p_.split(".")[-1] not in lset:
+                        continue
+                    fout = lin_geom[p_][1]
+                    u = u_l[(i, p_)]
+                    o_ += [op(GEMM_SB, a=g_, b=P[k_ + ".lora_b"], c=t1, m=N, k=fout, n=lora_r, batch=1, tb=1, dt=DT),
+                           op(GEMM_SB, a=t1, b=P[k_ + ".lora_a"], c=dx, m=N, k=lora_r, n=fin, batch=1, tb=1, dt=DT,
+                              alpha=sc_l, beta=1.0),
+                           op(GEMM_SB, a=x, b=t1, c=G[k_ + ".lora_a"], m=fin, n=lora_r, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l),
+                           op(GEMM_SB, a=u, b=g_, c=G[k_ + ".lora_b"], m=lora_r, n=fout, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l)]
+            return o_
+
         def norm_b(x, wname, g, res, out):
             """out = res + rmsnorm_bwd(x, w, g); dw -> G[wname] unless frozen"""
             return [op(RMSNORM_BWD_ACC, a=x, b=P[wname], d=g, c=out, tb=(res if res >= 0 else 0),
@@ -334,9 +383,7 @@ class CompiledTransformer:
         for i in range(L):
             p = f"blocks.{i}."
             plan += [op(RMSNORM, a=xs[i], b=P[p + "attn_norm.weight"], c=ys[i], m=N, n=D, dt=DT, alpha=eps)]
-            plan += lin_f(ys[i], i, "attn.q_proj", q2s[i])
-            plan += lin_f(ys[i], i, "attn.k_proj", k2s[i])
-            plan += lin_f(ys[i], i, "attn.v_proj", vs[i])
+            plan += lin_f_group(ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), (q2s[i], k2s[i], vs[i]))
             plan += [
                 op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT),
                 op(ROPE_BTHD, a=k2s[i], b=b_cos, d=b_sin, c=k2s[i], batch=B, m=T, k=KV, n=DH, dt=DT),
@@ -345,8 +392,7 @@ class CompiledTransformer:
             ]
             plan += lin_f(at2s[i], i, "attn.o_proj", r1s[i], res=xs[i])
             plan += [op(RMSNORM, a=r1s[i], b=P[p + "mlp_norm.weight"], c=zs[i], m=N, n=D, dt=DT, alpha=eps)]
-            plan += lin_f(zs[i], i, "mlp.gate_proj", gs[i])
-            plan += lin_f(zs[i], i, "mlp.up_proj", us[i])
+            plan += lin_f_group(zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), (gs[i], us[i]))
             plan += [op(SILU_MUL, a=gs[i], b=us[i], c=hs[i], n=N * MLP, dt=DT)]
             plan += lin_f(hs[i], i, "mlp.down_proj", xs[i + 1], res=r1s[i])
 
@@ -377,8 +423,7 @@ class CompiledTransformer:
             p = f"blocks.{i}."
             plan += lin_b(dcur, hs[i], i, "mlp.down_proj", dh_)
             plan += [op(SILU_BWD, a=gs[i], b=us[i], d=dh_, c=dg_, tb=du_, n=N * MLP, dt=DT)]
-            plan += lin_b(dg_, zs[i], i, "mlp.gate_proj", dz)
-            plan += lin_b(du_, zs[i], i, "mlp.up_proj", dz, acc=True)
+            plan += lin_b_group((dg_, du_), zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), dz)
             plan += norm_b(r1s[i], p + "mlp_norm.weight", dz, dcur, dr1)
             plan += lin_b(dr1, at2s[i], i, "attn.o_proj", dat2)
             plan += [
@@ -387,9 +432,7 @@ class CompiledTransformer:
                 op(ROPE_BTHD, a=dq, b=b_cos, d=b_sin, c=dq, batch=B, m=T, k=H, n=DH, tb=1, dt=DT),
                 op(ROPE_BTHD, a=dk, b=b_cos, d=b_sin, c=dk, batch=B, m=T, k=KV, n=DH, tb=1, dt=DT),
             ]
-            plan += lin_b(dq, ys[i], i, "attn.q_proj", dy)
-            plan += lin_b(dk, ys[i], i, "attn.k_proj", dy, acc=True)
-            plan += lin_b(dv, ys[i], i, "attn.v_proj", dy, acc=True)
+            plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
             if (L - 1 - i) % bucket_layers == bucket_layers - 1 and i > 0:
                 marks[1 + (L - 1 - i) // bucket_layers] = len(plan)

@@ -95,10 +95,26 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar) {
                  ::"r"(bar), "h"(mask) : "memory");
 }
 
+// Grouped launch: several GEMMs of one layer run as one persistent kernel.
+//   mode 1: `count` problems share A; problem g has its own B (n[g] columns) and its own C — their column
+//           tiles form one tile space (q/k/v or gate/up projections of the same input; their weight gradients).
+//   mode 2: one output accumulates over `count` K-segments, each with its own A and B (kb[s] k-blocks):
+//           dX = dY0 W0^T + dY1 W1^T + ... without round trips of the partial sums through memory.
+// Grouped launches write through TMA stores, take no addend and do not split K.
+struct GemmGroup {
+    int mode, count;
+    int n[3];
+    int kb[3];
+};
+
 template <int A_MN, int B_MN, typename TO>
 __global__ void __launch_bounds__(THREADS2, 1)
 k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-           const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, int tma_out,
+           const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+           const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
+           const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
+           const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
+           const GemmGroup grp, int tma_out,
            TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status,
            int ksplit, float* __restrict__ ws, long long* prof) {
     // tma_out != 0: the epilogue stages 32 x 128-byte pieces in shared memory (128-byte swizzle) and writes
@@ -126,9 +142,19 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                 // 0 = leader (issues the MMAs)
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int tiles_m = (m + 2 * BM2 - 1) / (2 * BM2), tiles_n = (n + BN2 - 1) / BN2;
+    const int tiles_m = (m + 2 * BM2 - 1) / (2 * BM2);
+    int tiles_n = (n + BN2 - 1) / BN2, kblocks_all = (k + BK2 - 1) / BK2;
+    if (grp.mode == 1) { tiles_n = 0; for (int q = 0; q < grp.count; q++) tiles_n += (grp.n[q] + BN2 - 1) / BN2; }
+    if (grp.mode == 2) { kblocks_all = 0; for (int q = 0; q < grp.count; q++) kblocks_all += grp.kb[q]; }
     const int num_tiles = tiles_m * tiles_n;
-    const int kblocks_all = (k + BK2 - 1) / BK2;
+    // column tile -> (problem, column tile inside it) for mode 1
+    auto problem_of = [&](int tn, int& tl) -> int {
+        int q = 0;
+        if (grp.mode == 1)
+            for (; q + 1 < grp.count; q++) { const int tq = (grp.n[q] + BN2 - 1) / BN2; if (tn < tq) break; tn -= tq; }
+        tl = tn;
+        return q;
+    };
     const int kb_per = (kblocks_all + ksplit - 1) / ksplit;
     const int num_units = num_tiles * ksplit;
 
@@ -140,6 +166,8 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         mbar_fence_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        if (grp.count > 1) { tma_prefetch_desc(grp.mode == 2 ? &tmA1 : &tmC1); tma_prefetch_desc(&tmB1); }
+        if (grp.count > 2) { tma_prefetch_desc(grp.mode == 2 ? &tmA2 : &tmC2); tma_prefetch_desc(&tmB2); }
         if (tma_out) tma_prefetch_desc(&tmC);
         if (tma_out == 2) tma_prefetch_desc(&tmD);
     }
@@ -166,8 +194,20 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const int tile = unit % num_tiles, split = unit / num_tiles;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
-            const int row0 = tm * 2 * BM2 + rank * BM2, col0 = tn * BN2 + rank * 128;
-            for (int kb = kb0; kb < kb1; kb++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
+            int tl;
+            const int g = problem_of(tn, tl);
+            const int row0 = tm * 2 * BM2 + rank * BM2, col0 = tl * BN2 + rank * 128;
+            // operand maps: mode 1 picks B by problem, mode 2 walks A and B through the K-segments
+            const CUtensorMap* pA = &tmA;
+            const CUtensorMap* pB = grp.mode == 1 ? (g == 0 ? &tmB : (g == 1 ? &tmB1 : &tmB2)) : &tmB;
+            int seg = 0, kl = kb0;                       // segment and k-block inside it
+            if (grp.mode == 2) while (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl -= grp.kb[seg]; seg++; }
+            for (int kb = kb0; kb < kb1; kb++, kl++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
+                if (grp.mode == 2) {
+                    if (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl = 0; seg++; }
+                    pA = seg == 0 ? &tmA : (seg == 1 ? &tmA1 : &tmA2);
+                    pB = seg == 0 ? &tmB : (seg == 1 ? &tmB1 : &tmB2);
+                }
                 if (it >= (uint32_t)nst && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
                 const uint32_t sa = smem_base + s * STAGE_BYTES2, sb = sa + A_BYTES2;
@@ -175,15 +215,15 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                 if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * STAGE_BYTES2);   // both CTAs' bytes land on this barrier
                 if (A_MN) {
 #pragma unroll
-                    for (int b = 0; b < 2; b++) tma_load_2d_pair(sa + b * 8192, &tmA, fb, row0 + b * 64, kb * BK2);
+                    for (int b = 0; b < 2; b++) tma_load_2d_pair(sa + b * 8192, pA, fb, row0 + b * 64, kl * BK2);
                 } else {
-                    tma_load_2d_pair(sa, &tmA, fb, kb * BK2, row0);
+                    tma_load_2d_pair(sa, pA, fb, kl * BK2, row0);
                 }
                 if (B_MN) {
 #pragma unroll
-                    for (int b = 0; b < 2; b++) tma_load_2d_pair(sb + b * 8192, &tmB, fb, col0 + b * 64, kb * BK2);
+                    for (int b = 0; b < 2; b++) tma_load_2d_pair(sb + b * 8192, pB, fb, col0 + b * 64, kl * BK2);
                 } else {
-                    tma_load_2d_pair(sb, &tmB, fb, kb * BK2, col0);
+                    tma_load_2d_pair(sb, pB, fb, kl * BK2, col0);
                 }
             }
         }
@@ -244,7 +284,10 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const int row0 = tm * 2 * BM2 + rank * BM2 + quad * 32;
             const int row = row0 + lane;
             const int cw = f32_out ? 32 : 64;                   // columns per 128-byte piece
-            const int ncols = min(BN2, n - tn * BN2);
+            int tl;
+            const int g = problem_of(tn, tl);                    // grouped launch: which output, which column tile of it
+            const CUtensorMap* pC = g == 0 ? &tmC : (g == 1 ? &tmC1 : &tmC2);
+            const int ncols = min(BN2, (grp.mode == 1 ? grp.n[g] : n) - tl * BN2);
             const int npc = (tma_out && row0 < m) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
             const uint32_t pbase = pieces;
             auto fetch_d = [&](int j) {                          // lane 0: addend piece j of this tile -> its buffer
@@ -318,7 +361,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_3d(&tmC, stg_u32 + bi * 4096, tn * BN2 + c, row0, ksplit > 1 ? split : 0);
+                        tma_store_3d(pC, stg_u32 + bi * 4096, tl * BN2 + c, row0, ksplit > 1 ? split : 0);
                         bulk_commit2();
                     }
                     pieces++;
@@ -383,50 +426,90 @@ static int pairs_for(int slot, int tslot) {
     return g_pairs[slot][tslot];
 }
 
-template <int A_MN, int B_MN, typename TO>
-static int gemm2_launch(int slot, const void* A, const void* B, void* C, const void* D, int m, int n, int k,
-                        float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
-    const int maxp = pairs_for<A_MN, B_MN, TO>(slot, sizeof(TO) == 2 ? 0 : 1);
-    if (maxp < 1) return -1;
-    CUtensorMap tmA, tmB;
+// operand / output tensor maps of one problem
+template <int A_MN> static int map_a(CUtensorMap* t, const void* A, int m, int k) {
     uint64_t dims[2], strides[1]; uint32_t box[2];
     if (A_MN) { dims[0] = m; dims[1] = k; strides[0] = (uint64_t)m * 2; box[0] = 64; box[1] = BK2; }
     else { dims[0] = k; dims[1] = m; strides[0] = (uint64_t)k * 2; box[0] = BK2; box[1] = BM2; }
-    if (tc_make_tmap_bf16(&tmA, A, 2, dims, strides, box, true)) return 2;
+    return tc_make_tmap_bf16(t, A, 2, dims, strides, box, true);
+}
+template <int B_MN> static int map_b(CUtensorMap* t, const void* B, int n, int k) {
+    uint64_t dims[2], strides[1]; uint32_t box[2];
     if (B_MN) { dims[0] = n; dims[1] = k; strides[0] = (uint64_t)n * 2; box[0] = 64; box[1] = BK2; }
     else { dims[0] = k; dims[1] = n; strides[0] = (uint64_t)k * 2; box[0] = BK2; box[1] = 128; }
-    if (tc_make_tmap_bf16(&tmB, B, 2, dims, strides, box, true)) return 2;
+    return tc_make_tmap_bf16(t, B, 2, dims, strides, box, true);
+}
+// {n, m, nz} tensor of osz-byte elements, pieces of 128 bytes x 32 rows
+static int map_c(CUtensorMap* t, void* base, int m, int n, int nz, int osz) {
+    PFN_tmapEncodeTiled enc = tc_encode_fn();
+    if (!enc) return 2;
+    cuuint64_t gd[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)nz};
+    cuuint64_t gs[2] = {(cuuint64_t)n * osz, (cuuint64_t)m * n * osz};
+    cuuint32_t bx[3] = {(cuuint32_t)(128 / osz), 32, 1};
+    cuuint32_t es[3] = {1, 1, 1};
+    if (gs[1] % 16 != 0) gs[1] = (gs[1] + 15) / 16 * 16;     // only reached with nz == 1 (never indexed)
+    const CUtensorMapDataType dtp = osz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    return enc(t, dtp, 3, base, gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : 2;
+}
+
+// One launch.  grp.mode 0: the plain GEMM (A, B, C, D are element 0 of the arrays).  Grouped modes: see GemmGroup;
+// n[] / k[] then hold the per-problem widths (mode 1) or per-segment depths (mode 2).
+template <int A_MN, int B_MN, typename TO>
+static int gemm2_launch(int slot, int mode, int count, const void* const* A, const void* const* B, void* const* C, const void* D,
+                        int m, const int* nv, const int* kv, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
+    const int maxp = pairs_for<A_MN, B_MN, TO>(slot, sizeof(TO) == 2 ? 0 : 1);
+    if (maxp < 1) return -1;
+    const int n = nv[0], k = kv[0];
+    GemmGroup grp = {};
+    grp.mode = mode; grp.count = count;
+    CUtensorMap tmA[3], tmB[3], tmC[3], tmD;
+    int tiles_n = 0;
+    if (mode == 0) {
+        if (map_a<A_MN>(&tmA[0], A[0], m, k) || map_b<B_MN>(&tmB[0], B[0], n, k)) return 2;
+        tiles_n = (n + 255) / 256;
+    } else if (mode == 1) {
+        if (map_a<A_MN>(&tmA[0], A[0], m, k)) return 2;
+        for (int g = 0; g < count; g++) {
+            if (map_b<B_MN>(&tmB[g], B[g], nv[g], k)) return 2;
+            grp.n[g] = nv[g];
+            tiles_n += (nv[g] + 255) / 256;
+        }
+    } else {
+        for (int g = 0; g < count; g++) {
+            if (map_a<A_MN>(&tmA[g], A[g], m, kv[g]) || map_b<B_MN>(&tmB[g], B[g], n, kv[g])) return 2;
+            grp.kb[g] = (kv[g] + BK2 - 1) / BK2;
+        }
+        tiles_n = (n + 255) / 256;
+    }
     // output through TMA tile stores when the destination allows it: 1 = no addend to read, 2 = addend by TMA too
     const int osz = ksplit > 1 ? 4 : (int)sizeof(TO);
     const bool has_d = D != nullptr && beta != 0.f && ksplit == 1;
     int tma_out = 0;
-    if (ax_gemm_tma_out() && ((uintptr_t)C & 15) == 0 && ((long long)n * osz) % 16 == 0 && (!has_d || ((uintptr_t)D & 15) == 0))
-        tma_out = has_d ? 2 : 1;
-    CUtensorMap tmC, tmD;
+    bool c_ok = ax_gemm_tma_out() != 0;
+    for (int g = 0; g < (mode == 1 ? count : 1); g++)
+        c_ok = c_ok && ((uintptr_t)C[g] & 15) == 0 && ((long long)nv[mode == 1 ? g : 0] * osz) % 16 == 0;
+    if (c_ok && (!has_d || ((uintptr_t)D & 15) == 0)) tma_out = has_d ? 2 : 1;
+    if (mode != 0 && (tma_out != 1 || ksplit != 1)) return -1;          // grouped launches need the plain TMA-store epilogue
     if (tma_out) {
-        PFN_tmapEncodeTiled enc = tc_encode_fn();
-        if (!enc) return 2;
         size_t wsb0 = 0;
-        void* base = ksplit > 1 ? (void*)ax_splitk_ws(&wsb0) : C;
-        cuuint64_t gd[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)(ksplit > 1 ? ksplit : 1)};
-        cuuint64_t gs[2] = {(cuuint64_t)n * osz, (cuuint64_t)m * n * osz};
-        cuuint32_t bx[3] = {(cuuint32_t)(128 / osz), 32, 1};
-        cuuint32_t es[3] = {1, 1, 1};
-        if (gs[1] % 16 != 0) gs[1] = (gs[1] + 15) / 16 * 16;     // only reached with a single split (never indexed)
-        const CUtensorMapDataType dtp = osz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-        CUresult r = enc(&tmC, dtp, 3, base, gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return 2;
-        tmD = tmC;
-        if (tma_out == 2) {
-            r = enc(&tmD, dtp, 3, const_cast<void*>(D), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS) return 2;
+        if (mode == 1) {
+            for (int g = 0; g < count; g++) if (map_c(&tmC[g], C[g], m, nv[g], 1, osz)) return 2;
+        } else {
+            void* base = ksplit > 1 ? (void*)ax_splitk_ws(&wsb0) : C[0];
+            if (map_c(&tmC[0], base, m, n, ksplit > 1 ? ksplit : 1, osz)) return 2;
         }
+        tmD = tmC[0];
+        if (tma_out == 2 && map_c(&tmD, const_cast<void*>(D), m, n, 1, osz)) return 2;
     } else {
-        tmC = tmA; tmD = tmA;
+        tmC[0] = tmA[0]; tmD = tmA[0];
     }
-    const int units = ((m + 255) / 256) * ((n + 255) / 256) * ksplit;
+    for (int g = 1; g < 3; g++) {           // unused slots carry valid (ignored) maps
+        if (mode != 2 || g >= count) tmA[g] = tmA[0];
+        if (mode == 0 || g >= count) tmB[g] = tmB[0];
+        if (mode != 1 || g >= count || !tma_out) tmC[g] = tmC[0];
+    }
+    const int units = ((m + 255) / 256) * tiles_n * ksplit;
     const int pairs = units < maxp ? units : maxp;
     size_t wsb = 0;
     float* ws = ax_splitk_ws(&wsb);
@@ -441,18 +524,19 @@ static int gemm2_launch(int slot, const void* A, const void* B, void* C, const v
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = ax_gemm_pdl() ? 2 : 1;
-    TO* Cp = (TO*)C; const TO* Dp = (const TO*)D;
+    TO* Cp = (TO*)C[0]; const TO* Dp = (const TO*)D;
     static const bool want_prof = getenv("AXENG_GEMM_PROF") != nullptr;     // debugging aid, prints to stderr
     long long* prof = nullptr;
     if (want_prof && (cudaMalloc(&prof, 64) != cudaSuccess || cudaMemset(prof, 0, 64) != cudaSuccess)) prof = nullptr;
-    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA, tmB, tmC, tmD, tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
+    if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA[0], tmB[0], tmC[0], tmD, tmA[1], tmA[2], tmB[1], tmB[2], tmC[1], tmC[2],
+                           grp, tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
     if (prof) {
         long long h[8];
         cudaStreamSynchronize(st);
         cudaMemcpy(h, prof, 64, cudaMemcpyDeviceToHost);
         cudaFree(prof);
-        fprintf(stderr, "gemm2 %dx%dx%d split %d pairs %d (cycles from entry): setup %lld dep %lld first_full %lld last_mma %lld last_acc %lld stored %lld exit %lld\n",
-                m, n, k, ksplit, pairs, h[1] - h[0], h[2] - h[0], h[3] - h[0], h[4] - h[0], h[5] - h[0], h[6] - h[0], h[7] - h[0]);
+        fprintf(stderr, "gemm2 %dx%dx%d mode %d split %d pairs %d (cycles from entry): setup %lld dep %lld first_full %lld last_mma %lld last_acc %lld stored %lld exit %lld\n",
+                m, n, k, mode, ksplit, pairs, h[1] - h[0], h[2] - h[0], h[3] - h[0], h[4] - h[0], h[5] - h[0], h[6] - h[0], h[7] - h[0]);
     }
     if (ksplit > 1) ax_splitk_reduce_launch<TO>(ws, ksplit, Cp, Dp, (long long)m * n, alpha, beta, st);
     return 0;
@@ -470,10 +554,35 @@ int ax_gemm_tc2_init(void) {
 // Same argument meaning as ax_gemm_tc; returns -1 when the paired kernel cannot run here.
 int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, const void* D,
                 int m, int n, int k, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
-    if (tb == 0) return out_bf16 ? gemm2_launch<0, 1, bf16>(0, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st)
-                                 : gemm2_launch<0, 1, float>(0, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st);
-    if (tb == 1) return out_bf16 ? gemm2_launch<0, 0, bf16>(1, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st)
-                                 : gemm2_launch<0, 0, float>(1, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st);
-    return out_bf16 ? gemm2_launch<1, 1, bf16>(2, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st)
-                    : gemm2_launch<1, 1, float>(2, A, B, C, D, m, n, k, alpha, beta, status, ksplit, st);
+    const void* Av[1] = {A}; const void* Bv[1] = {B}; void* Cv[1] = {C};
+#define G2(AM, BMj, SL)                                                                                                        \
+    (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, 0, 1, Av, Bv, Cv, D, m, &n, &k, alpha, beta, status, ksplit, st)              \
+              : gemm2_launch<AM, BMj, float>(SL, 0, 1, Av, Bv, Cv, D, m, &n, &k, alpha, beta, status, ksplit, st))
+    if (tb == 0) return G2(0, 1, 0);
+    if (tb == 1) return G2(0, 0, 1);
+    return G2(1, 1, 2);
+#undef G2
+}
+
+// Grouped launch (see GemmGroup).  mode 1: A[0] shared, B[g] / C[g] / n[g] per problem, k[0].  mode 2: A[s] / B[s] / k[s]
+// per segment, C[0], n[0].  Returns -1 when this kernel cannot serve the request (the caller then runs the
+// problems one by one).
+int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
+                      int m, const int* n, const int* k, float alpha, int* status, cudaStream_t st) {
+    if (count < 2 || count > 3 || (mode != 1 && mode != 2) || m < 256) return -1;
+    for (int g = 0; g < count; g++) {
+        if (!aligned16(A[mode == 2 ? g : 0]) || !aligned16(B[g])) return -1;
+        const int ng = n[mode == 1 ? g : 0], kg = k[mode == 2 ? g : 0];
+        if (ng < 8 || kg < 8) return -1;
+        if (tb == 0) { if (kg % 8 || ng % 8) return -1; }
+        else if (tb == 1) { if (kg % 8) return -1; }
+        else { if (m % 8 || ng % 8) return -1; }
+    }
+#define G2(AM, BMj, SL)                                                                                                        \
+    (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, mode, count, A, B, C, nullptr, m, n, k, alpha, 0.f, status, 1, st)            \
+              : gemm2_launch<AM, BMj, float>(SL, mode, count, A, B, C, nullptr, m, n, k, alpha, 0.f, status, 1, st))
+    if (tb == 0) return G2(0, 1, 0);
+    if (tb == 1) return G2(0, 0, 1);
+    return G2(1, 1, 2);
+#undef G2
 }

@@ -27,15 +27,16 @@ import numpy as np
 # fused kinds of this engine (include/axeng.h)
 (GEMM_EX, ROPE_BTHD, ATTN_FWD, ATTN_BWD, RMSNORM_BWD_ACC, CE_FUSED, EMBED_BWD_DET,
  GNORM_FLAT, ADAMW_FLAT, EMBED_I32, REDUCE, ALLGATHER_F32, FORK, JOIN, STREAM,
- SILU_MUL_BWD_RC) = range(32, 48)
-KIND_COUNT = 48
+ SILU_MUL_BWD_RC, GEMM_GROUP) = range(32, 49)
+KIND_COUNT = 49
 KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "COPY", "GEMM_SB",
               "PERM_0213", "ROPE", "SOFTMAX_CAUSAL", "REPEAT_KV", "RMSNORM_BWD", "COLSUM",
               "REPEAT_KV_BWD", "SOFTMAX_BWD", "SILU_BWD", "EMBED", "EMBED_BWD", "CE", "TICK", "CAST",
               "FLASH", "ROWDOT", "FLASH_BWD", "ALLREDUCE", "GROUP", "L2ACC", "CLIPSCALE",
               "COUNTVALID", "BROADCAST", "GEMM_EX", "ROPE_BTHD", "ATTN_FWD", "ATTN_BWD",
               "RMSNORM_BWD_ACC", "CE_FUSED", "EMBED_BWD_DET", "GNORM_FLAT", "ADAMW_FLAT",
-              "EMBED_I32", "REDUCE", "ALLGATHER_F32", "FORK", "JOIN", "STREAM", "SILU_MUL_BWD_RC"]
+              "EMBED_I32", "REDUCE", "ALLGATHER_F32", "FORK", "JOIN", "STREAM", "SILU_MUL_BWD_RC",
+              "GEMM_GROUP"]
 
 CHUNK = 1024          # arena granularity of the flat optimizer / collective ops
 GNORM_CHUNK = 8192    # elements per grad-norm partial
@@ -95,6 +96,10 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
     REDUCE / BROADCAST / ALLREDUCE with m>0: m chunks at chunk offset oa of a
     ALLGATHER_F32: a=send (offset oa) c=recv; n=count per rank
     FORK / JOIN / STREAM(tb): side-stream control for overlapped collectives
+    GEMM_GROUP: batch = 2 or 3 GEMMs of one layer as one launch; m, tb, dt, alpha as GEMM_SB.
+               oc=1 (one input, several outputs): a=A; b,sa,sb = B_g; c,d,sc = C_g; n,oa,ob = n_g; k
+               oc=2 (one output summed over K-segments): c=C; a,sa,sb = A_s; b,d,sc = B_s;
+               k,oa,ob = k_s; n
     """
     return (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc,
             alpha, beta, gamma)

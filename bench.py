@@ -368,12 +368,17 @@ def kernel_table(ct, c, batch):
     prof = eng.profile_read()
     eng.profile(False)
     total = sum(v[0] for v in prof.values()) or 1.0
-    gemm_ms = sum(prof.get(k, (0, 0))[0] for k in ("GEMM", "GEMM_SB", "GEMM_EX"))
-    gemm_calls = sum(prof.get(k, (0, 0))[1] for k in ("GEMM", "GEMM_SB", "GEMM_EX"))
+    gemm_kinds = ("GEMM", "GEMM_SB", "GEMM_EX", "GEMM_GROUP")
+    gemm_ms = sum(prof.get(k, (0, 0))[0] for k in gemm_kinds)
+    gemm_calls = sum(prof.get(k, (0, 0))[1] for k in gemm_kinds)
     gemm_flops = 0.0
     for o in ct.plan_step:
         if o[0] in (E.GEMM, E.GEMM_SB, E.GEMM_EX):
             gemm_flops += 2.0 * o[5] * o[6] * o[7] * max(o[8], 1)
+        elif o[0] == E.GEMM_GROUP:
+            # o = (kind, a, b, c, d, m, n, k, batch=count, tb, sa, sb, sc, dt, oa, ob, oc=mode, ...)
+            extra = sum((o[14], o[15])[:o[8] - 1])
+            gemm_flops += 2.0 * o[5] * ((o[6] + extra) * o[7] if o[16] == 1 else o[6] * (o[7] + extra))
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     # DRAM bytes per GEMM launch inside this step (dram__bytes_read.sum + dram__bytes_write.sum averaged over
     # 972 launches of one ncu capture of this command line; summary: profiles/step_1b_launch_list.md).

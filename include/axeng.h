@@ -61,6 +61,7 @@ enum EngOpKind {
     ENG_JOIN = 45,            /* main stream waits for the comm stream                      */
     ENG_STREAM = 46,          /* tb=1: following ops go to the comm stream, tb=0: main      */
     ENG_SILU_MUL_BWD_RC = 47, /* SwiGLU backward that also rewrites h for recompute-free dW */
+    ENG_GEMM_GROUP = 48,      /* 2-3 GEMMs of a layer as one launch: shared input, or one output summed over K-segments */
     ENG_KIND_COUNT
 };
 

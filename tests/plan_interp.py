@@ -139,6 +139,20 @@ class InterpEngine:
             return self._gemm(o, False)
         if kind == E.GEMM_EX:
             return self._gemm(o, True)
+        if kind == E.GEMM_GROUP:
+            # expanded into the plain GEMMs it stands for (same semantics as the library's fallback)
+            self.launches -= 1
+            ia, ic, dims = (a, sa, sb), (c, d, sc), (n if oc == 1 else k, oa, ob)
+            ib = (b, sa, sb) if oc == 1 else (b, d, sc)
+            for g_ in range(batch):
+                if oc == 1:
+                    sub = E.op(E.GEMM_SB, a=a, b=ib[g_], c=ic[g_], m=m, n=dims[g_], k=k, batch=1, tb=tb, dt=dt, alpha=alpha)
+                else:
+                    sub = E.op(E.GEMM_SB, a=ia[g_], b=ib[g_], c=c, m=m, n=n, k=dims[g_], batch=1, tb=tb, dt=dt, alpha=alpha,
+                               beta=1.0 if g_ else 0.0)
+                self.launches += 1
+                self._gemm(sub, False)
+            return None
         if kind == E.EMBED_I32:
             ids = self.bufs[b].view(np.int32)[:m]
             tab = self._get(a, self.bufs[a].size // (2 if dt == 1 else 4), dt).reshape(-1, n)

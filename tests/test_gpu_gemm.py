@@ -140,3 +140,56 @@ def test_small_and_unaligned_bf16_and_batched_offsets(eng, dt):
     ref = 0.25 * np.einsum("bqd,bkd->bqk", q[:, j, qs:qs + qt], kk[:, :kl])
     got = eng.download_bf16(ic, ref.shape) if dt else eng.download(ic, ref.shape)
     check(got, ref, dt == 1, DH)
+
+
+@pytest.mark.parametrize("dt", [0, 1, 2])
+@pytest.mark.parametrize("tb", [0, 1, 2])
+@pytest.mark.parametrize("count", [2, 3])
+def test_grouped_gemm_shared_input(eng, dt, tb, count):
+    """GEMM_GROUP mode 1: one input, several outputs with their own widths (ragged ones included)."""
+    rng = np.random.default_rng(10 * tb + count + dt)
+    m, k, ns = 520, 320, (520, 264, 136)[:count]
+    in_bf, out_bf = dt >= 1, dt == 1
+    A = rng.standard_normal((k, m) if tb == 2 else (m, k)).astype(np.float32)
+    Bs = [rng.standard_normal((n, k) if tb == 1 else (k, n)).astype(np.float32) for n in ns]
+    if in_bf:
+        A, Bs = bf(A), [bf(b) for b in Bs]
+    ia = put(eng, A, in_bf)
+    ib = [put(eng, b, in_bf) for b in Bs] + [0]
+    ic = [eng.alloc(m * n, 2 if out_bf else 4) for n in ns] + [0]
+    nn = list(ns) + [0]
+    eng.run([op(E.GEMM_GROUP, a=ia, b=ib[0], sa=ib[1], sb=ib[2], c=ic[0], d=ic[1], sc=ic[2], m=m, k=k,
+                n=nn[0], oa=nn[1], ob=nn[2], batch=count, oc=1, tb=tb, dt=dt, alpha=0.5)])
+    Aop = A.T if tb == 2 else A
+    for g, n in enumerate(ns):
+        got = eng.download_bf16(ic[g], (m, n)) if out_bf else eng.download(ic[g], (m, n))
+        Bop = Bs[g].T if tb == 1 else Bs[g]
+        check(got, (0.5 * (Aop.astype(np.float64) @ Bop.astype(np.float64))).astype(np.float32), out_bf, k)
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [0, 1, 2])
+@pytest.mark.parametrize("tb", [0, 1, 2])
+@pytest.mark.parametrize("count", [2, 3])
+def test_grouped_gemm_summed_segments(eng, dt, tb, count):
+    """GEMM_GROUP mode 2: one output accumulated over K-segments of different depths (one not a multiple
+    of the 64-wide k-block)."""
+    rng = np.random.default_rng(100 + 10 * tb + count + dt)
+    m, n, ks = 520, 392, (320, 136, 200)[:count]
+    in_bf, out_bf = dt >= 1, dt == 1
+    As = [rng.standard_normal((k, m) if tb == 2 else (m, k)).astype(np.float32) for k in ks]
+    Bs = [rng.standard_normal((n, k) if tb == 1 else (k, n)).astype(np.float32) for k in ks]
+    if in_bf:
+        As, Bs = [bf(a) for a in As], [bf(b) for b in Bs]
+    ia = [put(eng, a, in_bf) for a in As] + [0]
+    ib = [put(eng, b, in_bf) for b in Bs] + [0]
+    ic = eng.alloc(m * n, 2 if out_bf else 4)
+    kk = list(ks) + [0]
+    eng.run([op(E.GEMM_GROUP, c=ic, a=ia[0], sa=ia[1], sb=ia[2], b=ib[0], d=ib[1], sc=ib[2], m=m, n=n,
+                k=kk[0], oa=kk[1], ob=kk[2], batch=count, oc=2, tb=tb, dt=dt)])
+    ref = np.zeros((m, n), np.float64)
+    for a, b_ in zip(As, Bs):
+        ref += (a.T if tb == 2 else a).astype(np.float64) @ (b_.T if tb == 1 else b_).astype(np.float64)
+    got = eng.download_bf16(ic, (m, n)) if out_bf else eng.download(ic, (m, n))
+    check(got, ref.astype(np.float32), out_bf, sum(ks))
+    assert eng.device_status() == 0
