@@ -126,12 +126,17 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 uint32_t v[32];
                 tmem_ld32(t_S + lane_base + ch * 32, v);
                 tmem_ld_wait();
+                // raw maximum first (c > 0), one multiply at the end; the mask test only on the diagonal tile
+                if (diag) {
 #pragma unroll
-                for (int q = 0; q < 32; q++) {
-                    const float sv = __uint_as_float(v[q]) * c;
-                    if (!diag || ch * 32 + q <= r) mx = fmaxf(mx, sv);
+                    for (int q = 0; q < 32; q++)
+                        if (ch * 32 + q <= r) mx = fmaxf(mx, __uint_as_float(v[q]));
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 32; q++) mx = fmaxf(mx, __uint_as_float(v[q]));
                 }
             }
+            mx *= c;
             if (j == 0) {
                 m_used = mx;
             } else {
@@ -162,13 +167,24 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 uint32_t v[32], w[16];
                 tmem_ld32(t_S + lane_base + ch * 32, v);
                 tmem_ld_wait();
+                if (diag) {
 #pragma unroll
-                for (int q = 0; q < 32; q += 2) {
-                    float p0 = fast_exp2(__uint_as_float(v[q]) * c - m_used);
-                    float p1 = fast_exp2(__uint_as_float(v[q + 1]) * c - m_used);
-                    if (diag) { if (ch * 32 + q > r) p0 = 0.f; if (ch * 32 + q + 1 > r) p1 = 0.f; }
-                    l += p0 + p1;
-                    w[q >> 1] = pack_bf16(p0, p1);
+                    for (int q = 0; q < 32; q += 2) {
+                        float p0 = fast_exp2(__uint_as_float(v[q]) * c - m_used);
+                        float p1 = fast_exp2(__uint_as_float(v[q + 1]) * c - m_used);
+                        if (ch * 32 + q > r) p0 = 0.f;
+                        if (ch * 32 + q + 1 > r) p1 = 0.f;
+                        l += p0 + p1;
+                        w[q >> 1] = pack_bf16(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 32; q += 2) {
+                        const float p0 = fast_exp2(__uint_as_float(v[q]) * c - m_used);
+                        const float p1 = fast_exp2(__uint_as_float(v[q + 1]) * c - m_used);
+                        l += p0 + p1;
+                        w[q >> 1] = pack_bf16(p0, p1);
+                    }
                 }
                 tmem_st16(t_S + lane_base + ch * 16, w);       // P overwrites S columns already consumed
             }
@@ -464,19 +480,20 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tmem_ld32(t_S + e * 64 + lane_base + ch * 32, sv);
                 tmem_ld32(t_dP + e * 64 + lane_base + ch * 32, dp);
                 tmem_ld_wait();
+                if (diag) {                                      // query < key: masked (score -> -inf, so P = dS = 0)
+#pragma unroll
+                    for (int q = 0; q < 32; q++)
+                        if (e * 64 + ch * 32 + q < r) sv[q] = 0xff800000u;
+                }
 #pragma unroll
                 for (int q = 0; q < 32; q += 4) {
                     const int cs = ch * 32 + q;                  // query column within the sub-tile
-                    const int c0 = e * 64 + cs;                  // ... within the 128-query tile
                     const float4 l4 = *reinterpret_cast<const float4*>(L + cs);       // broadcast 16-byte loads
                     const float4 d4 = *reinterpret_cast<const float4*>(Dr + cs);
-                    float p0 = fast_exp2(__uint_as_float(sv[q]) * c - l4.x);
-                    float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - l4.y);
-                    float p2 = fast_exp2(__uint_as_float(sv[q + 2]) * c - l4.z);
-                    float p3 = fast_exp2(__uint_as_float(sv[q + 3]) * c - l4.w);
-                    if (diag) {                                  // query < key: masked
-                        if (c0 < r) p0 = 0.f; if (c0 + 1 < r) p1 = 0.f; if (c0 + 2 < r) p2 = 0.f; if (c0 + 3 < r) p3 = 0.f;
-                    }
+                    const float p0 = fast_exp2(__uint_as_float(sv[q]) * c - l4.x);
+                    const float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - l4.y);
+                    const float p2 = fast_exp2(__uint_as_float(sv[q + 2]) * c - l4.z);
+                    const float p3 = fast_exp2(__uint_as_float(sv[q + 3]) * c - l4.w);
                     wp[q >> 1] = pack_bf16(p0, p1);
                     wp[(q >> 1) + 1] = pack_bf16(p2, p3);
                     wd[q >> 1] = pack_bf16(p0 * (__uint_as_float(dp[q]) - d4.x), p1 * (__uint_as_float(dp[q + 1]) - d4.y));

@@ -4,6 +4,7 @@
     python -m axis_b200.opbench attn_bwd --B 4 --H 24 --KV 8 --T 2048 --DH 64
     python -m axis_b200.opbench rmsnorm_bwd --rows 8192 --dim 1536
     python -m axis_b200.opbench all            # the step's kernels at the 1B-class shapes
+    python -m axis_b200.opbench rmsnorm --chain 8   # eight instances back to back in one timed plan
 
 Each run prints one JSON line: mean milliseconds over `--reps` launches (CUDA
 events on the engine stream, L2 flushed between launches unless --no-flush),
@@ -141,35 +142,52 @@ def check_attn(b, q, kk, v, do, o, lse, dq, dk, dv, B, H, KV, T, DH, dt):
     return {k: round(v, 5) for k, v in worst.items()}
 
 
-def run_rows(b, which, rows, dim, dt):
+def run_rows(b, which, rows, dim, dt, chain=1):
+    """chain > 1: that many instances on separate buffers in one timed plan (together far larger than L2),
+    the figure is per instance — how the kernel runs inside a captured step, without the per-launch floor."""
     es = 2 if dt else 4
-    x, w, g, res = b.buf(rows * dim, dt), b.buf(dim, dt), b.buf(rows * dim, dt), b.buf(rows * dim, dt)
-    y, dw, scr = b.eng.alloc(rows * dim, es), b.eng.alloc(dim), b.eng.alloc(296 * dim)
+    plan = []
+    for _ in range(chain):
+        x, w, g, res = b.buf(rows * dim, dt), b.buf(dim, dt), b.buf(rows * dim, dt), b.buf(rows * dim, dt)
+        y, dw, scr = b.eng.alloc(rows * dim, es), b.eng.alloc(dim), b.eng.alloc(296 * dim)
+        if which == "rmsnorm":
+            plan.append(op(E.RMSNORM, a=x, b=w, c=y, m=rows, n=dim, dt=dt, alpha=1e-5))
+        else:
+            plan.append(op(E.RMSNORM_BWD_ACC, a=x, b=w, d=g, c=y, tb=res, sa=dw, sb=scr, m=rows, n=dim, dt=dt, alpha=1e-5))
+    ms = b.time(plan) / chain
+    tag = f" (chain of {chain})" if chain > 1 else ""
     if which == "rmsnorm":
-        ms = b.time([op(E.RMSNORM, a=x, b=w, c=y, m=rows, n=dim, dt=dt, alpha=1e-5)])
-        return b.report(f"rmsnorm {rows}x{dim} dt={dt}", ms, bytes_=2 * rows * dim * es)
-    ms = b.time([op(E.RMSNORM_BWD_ACC, a=x, b=w, d=g, c=y, tb=res, sa=dw, sb=scr, m=rows, n=dim, dt=dt, alpha=1e-5)])
-    return b.report(f"rmsnorm_bwd (dx + residual + dw) {rows}x{dim} dt={dt}", ms, bytes_=4 * rows * dim * es)
+        return b.report(f"rmsnorm {rows}x{dim} dt={dt}{tag}", ms, bytes_=2 * rows * dim * es)
+    return b.report(f"rmsnorm_bwd (dx + residual + dw) {rows}x{dim} dt={dt}{tag}", ms, bytes_=4 * rows * dim * es)
 
 
-def run_elem(b, which, n, dt, B=4, T=2048, H=24, DH=64):
+def run_elem(b, which, n, dt, B=4, T=2048, H=24, DH=64, chain=1):
     es = 2 if dt else 4
+    tag = f" (chain of {chain})" if chain > 1 else ""
     if which == "rope":
         n = B * T * H * DH
-        x = b.buf(n, dt)
         from axis_b200.compile import np as _np
         half = DH // 2
         ang = _np.outer(_np.arange(T, dtype=_np.float32), 1.0 / (10000.0 ** (_np.arange(half, dtype=_np.float32) / half)))
         cs, sn = b.eng.new_tensor(_np.cos(ang).astype(_np.float32)), b.eng.new_tensor(_np.sin(ang).astype(_np.float32))
-        ms = b.time([op(E.ROPE_BTHD, a=x, b=cs, d=sn, c=x, batch=B, m=T, k=H, n=DH, dt=dt)])
-        return b.report(f"rope in place B{B} T{T} H{H} DH{DH} dt={dt}", ms, bytes_=2 * n * es)
-    a, c_, d = b.buf(n, dt), b.buf(n, dt), b.buf(n, dt)
-    o1, o2 = b.eng.alloc(n, es), b.eng.alloc(n, es)
+        plan = []
+        for _ in range(chain):
+            x = b.buf(n, dt)
+            plan.append(op(E.ROPE_BTHD, a=x, b=cs, d=sn, c=x, batch=B, m=T, k=H, n=DH, dt=dt))
+        ms = b.time(plan) / chain
+        return b.report(f"rope in place B{B} T{T} H{H} DH{DH} dt={dt}{tag}", ms, bytes_=2 * n * es)
+    plan = []
+    for _ in range(chain):
+        a, c_, d = b.buf(n, dt), b.buf(n, dt), b.buf(n, dt)
+        o1, o2 = b.eng.alloc(n, es), b.eng.alloc(n, es)
+        if which == "silu":
+            plan.append(op(E.SILU_MUL, a=a, b=c_, c=o1, n=n, dt=dt))
+        else:
+            plan.append(op(E.SILU_BWD, a=a, b=c_, d=d, c=o1, tb=o2, n=n, dt=dt))
+    ms = b.time(plan) / chain
     if which == "silu":
-        ms = b.time([op(E.SILU_MUL, a=a, b=c_, c=o1, n=n, dt=dt)])
-        return b.report(f"silu_mul n={n} dt={dt}", ms, bytes_=3 * n * es)
-    ms = b.time([op(E.SILU_BWD, a=a, b=c_, d=d, c=o1, tb=o2, n=n, dt=dt)])
-    return b.report(f"silu_bwd n={n} dt={dt}", ms, bytes_=5 * n * es)
+        return b.report(f"silu_mul n={n} dt={dt}{tag}", ms, bytes_=3 * n * es)
+    return b.report(f"silu_bwd n={n} dt={dt}{tag}", ms, bytes_=5 * n * es)
 
 
 def run_ce(b, N, V, dt):
@@ -202,7 +220,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what")
     for a, d in (("m", 8192), ("n", 1536), ("k", 1536), ("tb", 0), ("dt", 1), ("B", 4), ("H", 24), ("KV", 8), ("T", 2048),
-                 ("DH", 64), ("rows", 8192), ("dim", 1536), ("V", 32000), ("count", 8192 * 4096), ("reps", 20), ("fallback", 0)):
+                 ("DH", 64), ("rows", 8192), ("dim", 1536), ("V", 32000), ("count", 8192 * 4096), ("reps", 20), ("fallback", 0),
+                 ("chain", 1)):
         ap.add_argument("--" + a, type=int, default=d)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--check", action="store_true")
@@ -214,9 +233,9 @@ def main():
     elif w in ("attn_fwd", "attn_bwd"):
         run_attn(b, w, a.B, a.H, a.KV, a.T, a.DH, a.dt, a.fallback, a.check)
     elif w in ("rmsnorm", "rmsnorm_bwd"):
-        run_rows(b, w, a.rows, a.dim, a.dt)
+        run_rows(b, w, a.rows, a.dim, a.dt, a.chain)
     elif w in ("rope", "silu", "silu_bwd"):
-        run_elem(b, w, a.count, a.dt, a.B, a.T, a.H, a.DH)
+        run_elem(b, w, a.count, a.dt, a.B, a.T, a.H, a.DH, a.chain)
     elif w == "ce":
         run_ce(b, a.rows, a.V, a.dt)
     elif w == "adamw":
