@@ -19,6 +19,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// max of three floats in one instruction (3-input max.f32 of sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // Shared-memory descriptors of these kernels all use SBO = 1024 and 128-byte swizzle, so their upper
 // word is one constant and the lower word is (address >> 4) | (LBO >> 4) << 16: the MMA-issuing thread
 // keeps a few base words and adds tile offsets (in 16-byte units) instead of rebuilding descriptors.

@@ -38,7 +38,7 @@ struct FwdSmem {
     static constexpr int Q = 0, K0 = 16384, V0 = K0 + 2 * 16384, BARS = V0 + 2 * 16384, TOTAL = BARS + 128 + 1024;
 };
 
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse,
               int T, int H, int KV, float scale, int* status) {
@@ -120,21 +120,28 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (!mbar_wait(b_s, j & 1) || *abort_flag) { ok = false; break; }
             tc_fence_after();
             const bool diag = j == qt;
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
-                uint32_t v[32];
-                tmem_ld32(t_S + lane_base + ch * 32, v);
-                tmem_ld_wait();
-                // raw maximum first (c > 0), one multiply at the end; the mask test only on the diagonal tile
-                if (diag) {
+            // the whole S row (128 scores) stays in registers between the max pass and the exp pass
+            uint32_t sv[128];
 #pragma unroll
-                    for (int q = 0; q < 32; q++)
-                        if (ch * 32 + q <= r) mx = fmaxf(mx, __uint_as_float(v[q]));
-                } else {
+            for (int ch = 0; ch < 4; ch++) tmem_ld32(t_S + lane_base + ch * 32, sv + ch * 32);
+            tmem_ld_wait();
+            // raw maximum first (c > 0), one multiply at the end; the mask only on the diagonal tile
+            if (diag) {
 #pragma unroll
-                    for (int q = 0; q < 32; q++) mx = fmaxf(mx, __uint_as_float(v[q]));
+                for (int q = 0; q < 128; q++)
+                    if (q > r) sv[q] = 0xff800000u;              // -inf: exp2 gives 0
+            }
+            float mx;
+            {
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                for (int q = 0; q < 128; q += 8) {
+                    m0 = fmax3(m0, __uint_as_float(sv[q]), __uint_as_float(sv[q + 1]));
+                    m1 = fmax3(m1, __uint_as_float(sv[q + 2]), __uint_as_float(sv[q + 3]));
+                    m2 = fmax3(m2, __uint_as_float(sv[q + 4]), __uint_as_float(sv[q + 5]));
+                    m3 = fmax3(m3, __uint_as_float(sv[q + 6]), __uint_as_float(sv[q + 7]));
                 }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
             mx *= c;
             if (j == 0) {
@@ -162,31 +169,25 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     tmem_st_wait();
                 }
             }
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ch++) {
-                uint32_t v[32], w[16];
-                tmem_ld32(t_S + lane_base + ch * 32, v);
-                tmem_ld_wait();
-                if (diag) {
+            {
+                float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-                    for (int q = 0; q < 32; q += 2) {
-                        float p0 = fast_exp2(__uint_as_float(v[q]) * c - m_used);
-                        float p1 = fast_exp2(__uint_as_float(v[q + 1]) * c - m_used);
-                        if (ch * 32 + q > r) p0 = 0.f;
-                        if (ch * 32 + q + 1 > r) p1 = 0.f;
-                        l += p0 + p1;
-                        w[q >> 1] = pack_bf16(p0, p1);
-                    }
-                } else {
+                for (int ch = 0; ch < 4; ch++) {
+                    uint32_t w[16];
 #pragma unroll
-                    for (int q = 0; q < 32; q += 2) {
-                        const float p0 = fast_exp2(__uint_as_float(v[q]) * c - m_used);
-                        const float p1 = fast_exp2(__uint_as_float(v[q + 1]) * c - m_used);
-                        l += p0 + p1;
+                    for (int q = 0; q < 32; q += 4) {
+                        const float p0 = fast_exp2(__uint_as_float(sv[ch * 32 + q]) * c - m_used);
+                        const float p1 = fast_exp2(__uint_as_float(sv[ch * 32 + q + 1]) * c - m_used);
+                        const float p2 = fast_exp2(__uint_as_float(sv[ch * 32 + q + 2]) * c - m_used);
+                        const float p3 = fast_exp2(__uint_as_float(sv[ch * 32 + q + 3]) * c - m_used);
+                        l0 += p0 + p1;
+                        l1 += p2 + p3;
                         w[q >> 1] = pack_bf16(p0, p1);
+                        w[(q >> 1) + 1] = pack_bf16(p2, p3);
                     }
+                    tmem_st16(t_S + lane_base + ch * 16, w);   // P replaces S (all of it is in registers by now)
                 }
-                tmem_st16(t_S + lane_base + ch * 16, w);       // P overwrites S columns already consumed
+                l += l0 + l1;
             }
             tmem_st_wait();
             tc_fence_before();
