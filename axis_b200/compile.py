@@ -307,14 +307,15 @@ class CompiledTransformer:
                           alpha=sc_l, beta=1.0)]
             return o_
 
-        def lin_b(g, x, i, pref, dx, acc=False):
-            """dx (+)= g@W_eff^T ; weight grads: dW (full) or dA/dB (LoRA)"""
+        def lin_b(g, x, i, pref, dx, acc=False, dw=True):
+            """dx (+)= g@W_eff^T ; weight grads: dW (full; dw=False leaves it to a later grouped launch) or dA/dB (LoRA)"""
             fin, fout = lin_geom[pref]
             key = f"blocks.{i}.{pref}"
             o_ = [op(GEMM_SB, a=g, b=P[key + ".weight"], c=dx, m=N, k=fout, n=fin, batch=1, tb=1, dt=DT,
                      beta=1.0 if acc else 0.0)]
             if not lora:
-                o_ += [op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)]
+                if dw:
+                    o_ += [op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)]
             elif pref.split(".")[-1] in lset:
                 u = u_l[(i, pref)]
                 o_ += [op(GEMM_SB, a=g, b=P[key + ".lora_b"], c=t1, m=N, k=fout, n=lora_r, batch=1, tb=1, dt=DT),

@@ -301,11 +301,12 @@ static int do_gemm(const EngOp* op, bool ex) {
 // Several GEMMs of one layer as one launch.  tb/dt/alpha as GEMM; batch = count (2 or 3); oc = mode.
 //   mode 1 (shared input): A = a; B_g = b, sa, sb; C_g = c, d, sc; n_g = n, oa, ob; k = k.
 //   mode 2 (summed over K-segments): C = c; A_s = a, sa, sb; B_s = b, d, sc; k_s = k, oa, ob; n = n.
+//   mode 3 (two independent problems of one depth k): A = a, sa; B = b, sb; C = c, d; m = m, oa; n = n, ob.
 // When the grouped tensor-core kernel cannot serve the request (fp32 plan, shapes, alignment) the problems run
 // one after another through the ordinary GEMM path: mode 2 as one GEMM plus accumulating ones.
 static int do_gemm_group(const EngOp* op) {
     const int count = op->batch, mode = op->oc;
-    if (count < 2 || count > 3 || (mode != 1 && mode != 2)) { set_err("gemm_group: bad count/mode"); return 112; }
+    if (count < 2 || count > 3 || mode < 1 || mode > 3 || (mode == 3 && count != 2)) { set_err("gemm_group: bad count/mode"); return 112; }
     const int ia[3] = {op->a, op->sa, op->sb}, ib[3] = {op->b, mode == 1 ? op->sa : op->d, mode == 1 ? op->sb : op->sc};
     const int ic[3] = {op->c, op->d, op->sc}, dims[3] = {mode == 1 ? op->n : op->k, op->oa, op->ob};
     EngOp sub[3];
@@ -314,19 +315,23 @@ static int do_gemm_group(const EngOp* op) {
         sub[g].kind = ENG_GEMM_SB;
         sub[g].batch = 1; sub[g].sa = sub[g].sb = sub[g].sc = 0; sub[g].oa = sub[g].ob = sub[g].oc = 0; sub[g].d = -1;
         if (mode == 1) { sub[g].a = op->a; sub[g].b = ib[g]; sub[g].c = ic[g]; sub[g].n = dims[g]; sub[g].beta = 0.f; }
-        else { sub[g].a = ia[g]; sub[g].b = ib[g]; sub[g].c = op->c; sub[g].k = dims[g]; sub[g].beta = g ? 1.f : 0.f; }
+        else if (mode == 2) { sub[g].a = ia[g]; sub[g].b = ib[g]; sub[g].c = op->c; sub[g].k = dims[g]; sub[g].beta = g ? 1.f : 0.f; }
+        else {
+            sub[g].a = g ? op->sa : op->a; sub[g].b = g ? op->sb : op->b; sub[g].c = g ? op->d : op->c;
+            sub[g].m = g ? op->oa : op->m; sub[g].n = g ? op->ob : op->n; sub[g].beta = 0.f;
+        }
     }
     const int dt = op->dt;
     if (dt >= 1 && !(G.fallback & 1) && !(G.fallback & 4)) {
         const long long ei = 2, eo = dt == 1 ? 2 : 4;
-        const void* A[3]; const void* B[3]; void* C[3]; int nv[3], kv[3];
+        const void* A[3]; const void* B[3]; void* C[3]; int mv[3], nv[3], kv[3];
         for (int g = 0; g < count; g++) {
             const EngOp* q = &sub[g];
             NEED(q->a, (long long)q->m * q->k * ei); NEED(q->b, (long long)q->k * q->n * ei); NEED(q->c, (long long)q->m * q->n * eo);
-            A[g] = BUFP(q->a); B[g] = BUFP(q->b); C[g] = BUFP(q->c); nv[g] = q->n; kv[g] = q->k;
+            A[g] = BUFP(q->a); B[g] = BUFP(q->b); C[g] = BUFP(q->c); mv[g] = q->m; nv[g] = q->n; kv[g] = q->k;
         }
         const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
-        const int rc = ax_gemm_tc2_group(dt == 1, op->tb, mode, count, A, B, C, op->m, nv, kv, alpha, G.d_status, G.cur);
+        const int rc = ax_gemm_tc2_group(dt == 1, op->tb, mode, count, A, B, C, mv, nv, kv, alpha, G.d_status, G.cur);
         if (rc == 0) { G.launches++; return 0; }
         if (rc > 0) { set_err("grouped tensor-core gemm failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
     }

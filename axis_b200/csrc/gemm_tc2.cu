@@ -100,11 +100,15 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar) {
 //           tiles form one tile space (q/k/v or gate/up projections of the same input; their weight gradients).
 //   mode 2: one output accumulates over `count` K-segments, each with its own A and B (kb[s] k-blocks):
 //           dX = dY0 W0^T + dY1 W1^T + ... without round trips of the partial sums through memory.
+//   mode 3: `count` independent problems of the same depth k, each with its own A, B, C, m[g] and n[g] (weight
+//           gradients of different projections of a layer): their tiles form one tile space, so the second
+//           problem fills the wave the first one leaves half empty.
 // Grouped launches write through TMA stores, take no addend and do not split K.
 struct GemmGroup {
     int mode, count;
     int n[3];
     int kb[3];
+    int m[3];
 };
 
 template <int A_MN, int B_MN, typename TO>
@@ -146,10 +150,27 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     int tiles_n = (n + BN2 - 1) / BN2, kblocks_all = (k + BK2 - 1) / BK2;
     if (grp.mode == 1) { tiles_n = 0; for (int q = 0; q < grp.count; q++) tiles_n += (grp.n[q] + BN2 - 1) / BN2; }
     if (grp.mode == 2) { kblocks_all = 0; for (int q = 0; q < grp.count; q++) kblocks_all += grp.kb[q]; }
-    const int num_tiles = tiles_m * tiles_n;
-    // column tile -> (problem, column tile inside it) for mode 1
-    auto problem_of = [&](int tn, int& tl) -> int {
+    int num_tiles = tiles_m * tiles_n;
+    if (grp.mode == 3) {
+        num_tiles = 0;
+        for (int q = 0; q < grp.count; q++) num_tiles += ((grp.m[q] + 2 * BM2 - 1) / (2 * BM2)) * ((grp.n[q] + BN2 - 1) / BN2);
+    }
+    // tile index -> problem g, row tile tm and column tile tl inside it (row tiles fastest)
+    auto locate = [&](int tile, int& tm, int& tl) -> int {
         int q = 0;
+        if (grp.mode == 3) {
+            int tmq = (grp.m[0] + 2 * BM2 - 1) / (2 * BM2);
+            for (; q + 1 < grp.count; q++) {
+                const int tq = tmq * ((grp.n[q] + BN2 - 1) / BN2);
+                if (tile < tq) break;
+                tile -= tq;
+                tmq = (grp.m[q + 1] + 2 * BM2 - 1) / (2 * BM2);
+            }
+            tm = tile % tmq; tl = tile / tmq;
+            return q;
+        }
+        tm = tile % tiles_m;
+        int tn = tile / tiles_m;
         if (grp.mode == 1)
             for (; q + 1 < grp.count; q++) { const int tq = (grp.n[q] + BN2 - 1) / BN2; if (tn < tq) break; tn -= tq; }
         tl = tn;
@@ -192,14 +213,13 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         bool ok = true;
         for (int unit = pair; unit < num_units && ok; unit += npairs) {
             const int tile = unit % num_tiles, split = unit / num_tiles;
-            const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
-            int tl;
-            const int g = problem_of(tn, tl);
+            int tm, tl;
+            const int g = locate(tile, tm, tl);
             const int row0 = tm * 2 * BM2 + rank * BM2, col0 = tl * BN2 + rank * 128;
-            // operand maps: mode 1 picks B by problem, mode 2 walks A and B through the K-segments
-            const CUtensorMap* pA = &tmA;
-            const CUtensorMap* pB = grp.mode == 1 ? (g == 0 ? &tmB : (g == 1 ? &tmB1 : &tmB2)) : &tmB;
+            // operand maps: modes 1 and 3 pick B by problem (mode 3 also A), mode 2 walks A and B through the K-segments
+            const CUtensorMap* pA = grp.mode == 3 ? (g == 0 ? &tmA : (g == 1 ? &tmA1 : &tmA2)) : &tmA;
+            const CUtensorMap* pB = (grp.mode == 1 || grp.mode == 3) ? (g == 0 ? &tmB : (g == 1 ? &tmB1 : &tmB2)) : &tmB;
             int seg = 0, kl = kb0;                       // segment and k-block inside it
             if (grp.mode == 2) while (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl -= grp.kb[seg]; seg++; }
             for (int kb = kb0; kb < kb1; kb++, kl++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
@@ -278,17 +298,18 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         uint32_t dpar = 0;                                      // phase parity of each addend barrier
         for (int unit = pair; unit < num_units && ok; unit += npairs, tcount++) {
             const int tile = unit % num_tiles, split = unit / num_tiles;
-            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            int tm, tl;
+            const int g = locate(tile, tm, tl);                  // grouped launch: which output, which tile of it
+            const int tn = tl;
             const int acc = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
             const int row0 = tm * 2 * BM2 + rank * BM2 + quad * 32;
             const int row = row0 + lane;
             const int cw = f32_out ? 32 : 64;                   // columns per 128-byte piece
-            int tl;
-            const int g = problem_of(tn, tl);                    // grouped launch: which output, which column tile of it
             const CUtensorMap* pC = g == 0 ? &tmC : (g == 1 ? &tmC1 : &tmC2);
-            const int ncols = min(BN2, (grp.mode == 1 ? grp.n[g] : n) - tl * BN2);
-            const int npc = (tma_out && row0 < m) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
+            const int ncols = min(BN2, ((grp.mode == 1 || grp.mode == 3) ? grp.n[g] : n) - tl * BN2);
+            const int m_g = grp.mode == 3 ? grp.m[g] : m;
+            const int npc = (tma_out && row0 < m_g) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
             const uint32_t pbase = pieces;
             auto fetch_d = [&](int j) {                          // lane 0: addend piece j of this tile -> its buffer
                 const uint32_t bi = (pbase + j) & 3;
@@ -457,10 +478,10 @@ static int map_c(CUtensorMap* t, void* base, int m, int n, int nz, int osz) {
 // n[] / k[] then hold the per-problem widths (mode 1) or per-segment depths (mode 2).
 template <int A_MN, int B_MN, typename TO>
 static int gemm2_launch(int slot, int mode, int count, const void* const* A, const void* const* B, void* const* C, const void* D,
-                        int m, const int* nv, const int* kv, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
+                        const int* mv, const int* nv, const int* kv, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
     const int maxp = pairs_for<A_MN, B_MN, TO>(slot, sizeof(TO) == 2 ? 0 : 1);
     if (maxp < 1) return -1;
-    const int n = nv[0], k = kv[0];
+    const int m = mv[0], n = nv[0], k = kv[0];
     GemmGroup grp = {};
     grp.mode = mode; grp.count = count;
     CUtensorMap tmA[3], tmB[3], tmC[3], tmD;
@@ -475,26 +496,32 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
             grp.n[g] = nv[g];
             tiles_n += (nv[g] + 255) / 256;
         }
-    } else {
+    } else if (mode == 2) {
         for (int g = 0; g < count; g++) {
             if (map_a<A_MN>(&tmA[g], A[g], m, kv[g]) || map_b<B_MN>(&tmB[g], B[g], n, kv[g])) return 2;
             grp.kb[g] = (kv[g] + BK2 - 1) / BK2;
         }
         tiles_n = (n + 255) / 256;
+    } else {
+        for (int g = 0; g < count; g++) {
+            if (map_a<A_MN>(&tmA[g], A[g], mv[g], k) || map_b<B_MN>(&tmB[g], B[g], nv[g], k)) return 2;
+            grp.m[g] = mv[g]; grp.n[g] = nv[g];
+        }
     }
+    const bool per_problem_c = mode == 1 || mode == 3;
     // output through TMA tile stores when the destination allows it: 1 = no addend to read, 2 = addend by TMA too
     const int osz = ksplit > 1 ? 4 : (int)sizeof(TO);
     const bool has_d = D != nullptr && beta != 0.f && ksplit == 1;
     int tma_out = 0;
     bool c_ok = ax_gemm_tma_out() != 0;
-    for (int g = 0; g < (mode == 1 ? count : 1); g++)
-        c_ok = c_ok && ((uintptr_t)C[g] & 15) == 0 && ((long long)nv[mode == 1 ? g : 0] * osz) % 16 == 0;
+    for (int g = 0; g < (per_problem_c ? count : 1); g++)
+        c_ok = c_ok && ((uintptr_t)C[g] & 15) == 0 && ((long long)nv[per_problem_c ? g : 0] * osz) % 16 == 0;
     if (c_ok && (!has_d || ((uintptr_t)D & 15) == 0)) tma_out = has_d ? 2 : 1;
     if (mode != 0 && (tma_out != 1 || ksplit != 1)) return -1;          // grouped launches need the plain TMA-store epilogue
     if (tma_out) {
         size_t wsb0 = 0;
-        if (mode == 1) {
-            for (int g = 0; g < count; g++) if (map_c(&tmC[g], C[g], m, nv[g], 1, osz)) return 2;
+        if (per_problem_c) {
+            for (int g = 0; g < count; g++) if (map_c(&tmC[g], C[g], mode == 3 ? mv[g] : m, nv[g], 1, osz)) return 2;
         } else {
             void* base = ksplit > 1 ? (void*)ax_splitk_ws(&wsb0) : C[0];
             if (map_c(&tmC[0], base, m, n, ksplit > 1 ? ksplit : 1, osz)) return 2;
@@ -505,11 +532,12 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
         tmC[0] = tmA[0]; tmD = tmA[0];
     }
     for (int g = 1; g < 3; g++) {           // unused slots carry valid (ignored) maps
-        if (mode != 2 || g >= count) tmA[g] = tmA[0];
+        if ((mode != 2 && mode != 3) || g >= count) tmA[g] = tmA[0];
         if (mode == 0 || g >= count) tmB[g] = tmB[0];
-        if (mode != 1 || g >= count || !tma_out) tmC[g] = tmC[0];
+        if (!per_problem_c || g >= count || !tma_out) tmC[g] = tmC[0];
     }
-    const int units = ((m + 255) / 256) * tiles_n * ksplit;
+    int units = ((m + 255) / 256) * tiles_n * ksplit;
+    if (mode == 3) { units = 0; for (int g = 0; g < count; g++) units += ((mv[g] + 255) / 256) * ((nv[g] + 255) / 256); }
     const int pairs = units < maxp ? units : maxp;
     size_t wsb = 0;
     float* ws = ax_splitk_ws(&wsb);
@@ -556,27 +584,27 @@ int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, con
                 int m, int n, int k, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
     const void* Av[1] = {A}; const void* Bv[1] = {B}; void* Cv[1] = {C};
 #define G2(AM, BMj, SL)                                                                                                        \
-    (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, 0, 1, Av, Bv, Cv, D, m, &n, &k, alpha, beta, status, ksplit, st)              \
-              : gemm2_launch<AM, BMj, float>(SL, 0, 1, Av, Bv, Cv, D, m, &n, &k, alpha, beta, status, ksplit, st))
+    (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, 0, 1, Av, Bv, Cv, D, &m, &n, &k, alpha, beta, status, ksplit, st)             \
+              : gemm2_launch<AM, BMj, float>(SL, 0, 1, Av, Bv, Cv, D, &m, &n, &k, alpha, beta, status, ksplit, st))
     if (tb == 0) return G2(0, 1, 0);
     if (tb == 1) return G2(0, 0, 1);
     return G2(1, 1, 2);
 #undef G2
 }
 
-// Grouped launch (see GemmGroup).  mode 1: A[0] shared, B[g] / C[g] / n[g] per problem, k[0].  mode 2: A[s] / B[s] / k[s]
-// per segment, C[0], n[0].  Returns -1 when this kernel cannot serve the request (the caller then runs the
-// problems one by one).
+// Grouped launch (see GemmGroup).  mode 1: A[0] shared, B[g] / C[g] / n[g] per problem, m[0], k[0].  mode 2: A[s] / B[s] /
+// k[s] per segment, C[0], m[0], n[0].  mode 3: A[g] / B[g] / C[g] / m[g] / n[g] per problem, k[0].  Returns -1 when this
+// kernel cannot serve the request (the caller then runs the problems one by one).
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
-                      int m, const int* n, const int* k, float alpha, int* status, cudaStream_t st) {
-    if (count < 2 || count > 3 || (mode != 1 && mode != 2) || m < 256) return -1;
+                      const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st) {
+    if (count < 2 || count > 3 || mode < 1 || mode > 3) return -1;
     for (int g = 0; g < count; g++) {
-        if (!aligned16(A[mode == 2 ? g : 0]) || !aligned16(B[g])) return -1;
-        const int ng = n[mode == 1 ? g : 0], kg = k[mode == 2 ? g : 0];
-        if (ng < 8 || kg < 8) return -1;
+        if (!aligned16(A[(mode == 2 || mode == 3) ? g : 0]) || !aligned16(B[g])) return -1;
+        const int mg = m[mode == 3 ? g : 0], ng = n[(mode == 1 || mode == 3) ? g : 0], kg = k[mode == 2 ? g : 0];
+        if (mg < 256 || ng < 8 || kg < 8) return -1;
         if (tb == 0) { if (kg % 8 || ng % 8) return -1; }
         else if (tb == 1) { if (kg % 8) return -1; }
-        else { if (m % 8 || ng % 8) return -1; }
+        else { if (mg % 8 || ng % 8) return -1; }
     }
 #define G2(AM, BMj, SL)                                                                                                        \
     (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, mode, count, A, B, C, nullptr, m, n, k, alpha, 0.f, status, 1, st)            \

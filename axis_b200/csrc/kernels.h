@@ -91,9 +91,9 @@ int ax_attn_bwd_simt(int dt, int out_dt, const void* q, const void* k, const voi
                      const AttnShape& s, cudaStream_t st);
 
 // gemm_tc2.cu — grouped launch of the paired-CTA GEMM (mode 1: shared A, per-problem B/C/n; mode 2: one C summed
-// over per-segment A/B/k).  -1 when not served.
+// over per-segment A/B/k; mode 3: independent problems A/B/C/m/n of one depth k).  -1 when not served.
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
-                      int m, const int* n, const int* k, float alpha, int* status, cudaStream_t st);
+                      const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st);
 
 // attn_tc.cu — tcgen05 flash attention (bf16, DH 64/128). -1 when not served.
 int ax_attn_tc_init(void);

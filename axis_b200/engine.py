@@ -100,6 +100,8 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                oc=1 (one input, several outputs): a=A; b,sa,sb = B_g; c,d,sc = C_g; n,oa,ob = n_g; k
                oc=2 (one output summed over K-segments): c=C; a,sa,sb = A_s; b,d,sc = B_s;
                k,oa,ob = k_s; n
+               oc=3 (two independent problems of one depth k): a,sa = A_g; b,sb = B_g; c,d = C_g;
+               m,oa = m_g; n,ob = n_g
     """
     return (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc,
             alpha, beta, gamma)

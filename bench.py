@@ -377,8 +377,11 @@ def kernel_table(ct, c, batch):
             gemm_flops += 2.0 * o[5] * o[6] * o[7] * max(o[8], 1)
         elif o[0] == E.GEMM_GROUP:
             # o = (kind, a, b, c, d, m, n, k, batch=count, tb, sa, sb, sc, dt, oa, ob, oc=mode, ...)
-            extra = sum((o[14], o[15])[:o[8] - 1])
-            gemm_flops += 2.0 * o[5] * ((o[6] + extra) * o[7] if o[16] == 1 else o[6] * (o[7] + extra))
+            if o[16] == 3:      # two independent problems: m = o[5], o[14]; n = o[6], o[15]; k = o[7]
+                gemm_flops += 2.0 * o[7] * (o[5] * o[6] + o[14] * o[15])
+            else:
+                extra = sum((o[14], o[15])[:o[8] - 1])
+                gemm_flops += 2.0 * o[5] * ((o[6] + extra) * o[7] if o[16] == 1 else o[6] * (o[7] + extra))
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     # DRAM bytes per GEMM launch inside this step (dram__bytes_read.sum + dram__bytes_write.sum averaged over
     # 972 launches of one ncu capture of this command line; summary: profiles/step_1b_launch_list.md).

@@ -145,7 +145,10 @@ class InterpEngine:
             ia, ic, dims = (a, sa, sb), (c, d, sc), (n if oc == 1 else k, oa, ob)
             ib = (b, sa, sb) if oc == 1 else (b, d, sc)
             for g_ in range(batch):
-                if oc == 1:
+                if oc == 3:
+                    sub = E.op(E.GEMM_SB, a=(a, sa)[g_], b=(b, sb)[g_], c=(c, d)[g_], m=(m, oa)[g_], n=(n, ob)[g_], k=k,
+                               batch=1, tb=tb, dt=dt, alpha=alpha)
+                elif oc == 1:
                     sub = E.op(E.GEMM_SB, a=a, b=ib[g_], c=ic[g_], m=m, n=dims[g_], k=k, batch=1, tb=tb, dt=dt, alpha=alpha)
                 else:
                     sub = E.op(E.GEMM_SB, a=ia[g_], b=ib[g_], c=c, m=m, n=n, k=dims[g_], batch=1, tb=tb, dt=dt, alpha=alpha,

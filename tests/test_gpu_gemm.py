@@ -193,3 +193,26 @@ def test_grouped_gemm_summed_segments(eng, dt, tb, count):
     got = eng.download_bf16(ic, (m, n)) if out_bf else eng.download(ic, (m, n))
     check(got, ref.astype(np.float32), out_bf, sum(ks))
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [0, 1, 2])
+@pytest.mark.parametrize("tb", [0, 1, 2])
+def test_grouped_gemm_independent_problems(eng, dt, tb):
+    """GEMM_GROUP mode 3: two problems with their own operands, heights and widths, one depth."""
+    rng = np.random.default_rng(300 + 10 * tb + dt)
+    k, ms, ns = 328, (776, 264), (392, 520)
+    in_bf, out_bf = dt >= 1, dt == 1
+    As = [rng.standard_normal((k, m) if tb == 2 else (m, k)).astype(np.float32) for m in ms]
+    Bs = [rng.standard_normal((n, k) if tb == 1 else (k, n)).astype(np.float32) for n in ns]
+    if in_bf:
+        As, Bs = [bf(a) for a in As], [bf(b) for b in Bs]
+    ia = [put(eng, a, in_bf) for a in As]
+    ib = [put(eng, b, in_bf) for b in Bs]
+    ic = [eng.alloc(m * n, 2 if out_bf else 4) for m, n in zip(ms, ns)]
+    eng.run([op(E.GEMM_GROUP, a=ia[0], sa=ia[1], b=ib[0], sb=ib[1], c=ic[0], d=ic[1], m=ms[0], oa=ms[1],
+                n=ns[0], ob=ns[1], k=k, batch=2, oc=3, tb=tb, dt=dt)])
+    for g in range(2):
+        got = eng.download_bf16(ic[g], (ms[g], ns[g])) if out_bf else eng.download(ic[g], (ms[g], ns[g]))
+        ref = (As[g].T if tb == 2 else As[g]).astype(np.float64) @ (Bs[g].T if tb == 1 else Bs[g]).astype(np.float64)
+        check(got, ref.astype(np.float32), out_bf, k)
+    assert eng.device_status() == 0
