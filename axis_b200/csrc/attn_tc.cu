@@ -88,6 +88,9 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int j = 0; j < nkt && ok; j++) {
                 const int s = j & 1;
                 if (!mbar_wait(b_kvf + 8 * s, (j >> 1) & 1)) { ok = false; break; }
+                // S(j) overwrites the columns that P V(j-1) reads P from: MMAs on different accumulators are not
+                // ordered against each other, so wait for that MMA's completion instead of relying on issue order
+                if (j >= 1 && !mbar_wait(b_o, (j - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < ADH / 16; kk++)
@@ -365,6 +368,9 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tc_commit(b_qe + 8 * sl);                  // the ring slot is free once these have run
                 if (u + 2 < n_sub) {
                     if (!mbar_wait(b_qf + 8 * ((u + 2) & 3), ((u + 2) >> 2) & 1)) { ok = false; break; }
+                    // S^T/dP^T(u+2) overwrite the buffer whose P^T/dS^T the dV/dK MMAs above read as their A operands:
+                    // MMAs on different accumulators are not ordered against each other, so wait for their completion
+                    if (!mbar_wait(b_qe + 8 * sl, (u >> 2) & 1)) { ok = false; break; }
                     tc_fence_after();
                     issue_sdp(u + 2);
                 }

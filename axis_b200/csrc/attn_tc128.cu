@@ -334,6 +334,9 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     load_q(it + 1);
                 }
                 if (!mbar_wait(b_qf + 8 * s, (it >> 1) & 1)) { ok = false; break; }
+                // S^T/dP^T(it) overwrite the columns whose P^T/dS^T the dV/dK MMAs of it-1 read as A operands: MMAs on
+                // different accumulators are not ordered against each other, so wait for their completion
+                if (it >= 1 && !mbar_wait(b_qe + 8 * (s ^ 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
                 tc_fence_after();
                 // S^T (128 keys x 64 queries) = K Q^T and dP^T = V dO^T over the 128-wide head: 8 k-steps each
 #pragma unroll
@@ -352,10 +355,10 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
                 for (int kk = 0; kk < QS / 16; kk++)       // dK += dS^T Q
                     tc_mma_ts(t_dK, t_dP + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loQ_n + so + kk * 128), id_acc, (it | kk) != 0);
+                tc_commit(b_qe + 8 * s);                   // Q/dO stage and the P^T/dS^T columns are free once these have run
 #pragma unroll
                 for (int kk = 0; kk < AT / 16; kk++)       // dQ^T = K^T dS^T   (k = keys), double-buffered
                     tc_mma_ss(t_dQ + (it & 1) * 64, desc_of(loK_m + kk * 128), desc_of(loDS + kk * 128), id_dq, kk != 0);
-                tc_commit(b_qe + 8 * s);
                 tc_commit(b_dq + 8 * (it & 1));
             }
             if (!ok) { *abort_flag = 1; atomicExch(status, STAT_BWD128 | 1); }
@@ -410,6 +413,8 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             float nxt = 0.f;
             if (it + 1 < n_it && threadIdx.x < 128) nxt = stat_of(it + 1);
             if (!mbar_wait(b_sdp, it & 1) || *abort_flag) { ok = false; break; }
+            // the dS^T tile in shared memory is rewritten below: dQ^T of the previous sub-tile must have read it
+            if (it >= 1 && !mbar_wait(b_dq + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
             const bool diag = u < 2 * j + 2;                  // sub-tiles that straddle this key tile's diagonal
             const int qoff = u * QS - j * AT;                 // query index of column 0 relative to key row 0
