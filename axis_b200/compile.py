@@ -386,8 +386,8 @@ class CompiledTransformer:
             plan += [op(RMSNORM, a=xs[i], b=P[p + "attn_norm.weight"], c=ys[i], m=N, n=D, dt=DT, alpha=eps)]
             plan += lin_f_group(ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), (q2s[i], k2s[i], vs[i]))
             plan += [
-                op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT),
-                op(ROPE_BTHD, a=k2s[i], b=b_cos, d=b_sin, c=k2s[i], batch=B, m=T, k=KV, n=DH, dt=DT),
+                op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT,
+                   sa=k2s[i], sb=k2s[i], sc=KV),                     # q and k in one launch
                 op(ATTN_FWD, a=q2s[i], b=k2s[i], d=vs[i], c=at2s[i], sa=lses[i],
                    m=T, n=DH, k=KV, batch=B, tb=H, dt=DT, alpha=scale),
             ]
@@ -430,8 +430,8 @@ class CompiledTransformer:
             plan += [
                 op(ATTN_BWD, a=q2s[i], b=k2s[i], d=vs[i], c=dat2, sa=lses[i], sb=at2s[i],
                    tb=dq, sc=dk, oa=dv, ob=H, oc=bD, m=T, n=DH, k=KV, batch=B, dt=DT, alpha=scale),
-                op(ROPE_BTHD, a=dq, b=b_cos, d=b_sin, c=dq, batch=B, m=T, k=H, n=DH, tb=1, dt=DT),
-                op(ROPE_BTHD, a=dk, b=b_cos, d=b_sin, c=dk, batch=B, m=T, k=KV, n=DH, tb=1, dt=DT),
+                op(ROPE_BTHD, a=dq, b=b_cos, d=b_sin, c=dq, batch=B, m=T, k=H, n=DH, tb=1, dt=DT,
+                   sa=dk, sb=dk, sc=KV),
             ]
             plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)

@@ -418,12 +418,20 @@ static int exec_op(const EngOp* op) {
             return ax_rope(dt, BUFP(op->a), (const float*)BUFP(op->b), (const float*)BUFP(op->d), BUFP(op->c), op->m, op->n, rows, 1, op->tb != 0, st);
         }
         case ENG_ROPE_BTHD: {
-            // a=x b=cos d=sin c=out; batch=B m=T k=heads n=DH; tb=1 inverse
+            // a=x b=cos d=sin c=out; batch=B m=T k=heads n=DH; tb=1 inverse; optional second tensor in the same
+            // launch: sa=x2 sb=out2 sc=its heads (0 = none)
             const long long rows = (long long)op->batch * op->m * op->k;
             NEED(op->a, rows * op->n * es); NEED(op->c, rows * op->n * es);
             NEED(op->b, (long long)op->m * (op->n / 2) * 4); NEED(op->d, (long long)op->m * (op->n / 2) * 4);
+            const void* x2 = nullptr; void* o2 = nullptr; long long rows2 = 0;
+            if (op->sc > 0) {
+                rows2 = (long long)op->batch * op->m * op->sc;
+                NEED(op->sa, rows2 * op->n * es); NEED(op->sb, rows2 * op->n * es);
+                x2 = BUFP(op->sa); o2 = BUFP(op->sb);
+            }
             G.launches++;
-            return ax_rope(dt, BUFP(op->a), (const float*)BUFP(op->b), (const float*)BUFP(op->d), BUFP(op->c), op->m, op->n, rows, op->k, op->tb != 0, st);
+            return ax_rope2(dt, BUFP(op->a), (const float*)BUFP(op->b), (const float*)BUFP(op->d), BUFP(op->c), op->m, op->n, rows, op->k,
+                            op->tb != 0, x2, o2, rows2, op->sc, st);
         }
         case ENG_SOFTMAX_CAUSAL: {
             const long long rows = (long long)op->batch * op->m;

@@ -166,21 +166,28 @@ __global__ void k_rope(const T* x, const float* __restrict__ cs, const float* __
         stf(o, r * dh + j + half, x1 * s + x2 * c);
     }
 }
-// 16-byte version: a thread rotates 8 (bf16) or 4 (fp32) consecutive pairs.
+// 16-byte version: a thread rotates 8 (bf16) or 4 (fp32) consecutive pairs.  A second tensor with its own head count
+// (the key projection next to the query projection) rides in the same launch.
 template <typename T>
 __global__ void k_rope_vec(const T* x, const float* __restrict__ cs, const float* __restrict__ sn, T* o,
-                           int T_, int dh, long long rows, int heads_inner, int inverse) {
+                           int T_, int dh, long long rows, int heads_inner, int inverse,
+                           const T* x2, T* o2, long long rows2, int heads_inner2) {
     constexpr int N = Vec<T>::N;
     const int half = dh >> 1, hv = half / N;
-    const long long total = rows * hv;
+    const long long total1 = rows * hv, total = total1 + rows2 * hv;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int j = (int)(i % hv) * N;
-        const long long r = i / hv;
-        const int t = (int)((r / heads_inner) % T_);
-        float x1[N], x2[N], c[N], s[N], o1[N], o2[N];
-        Vec<T>::ld(x + r * dh + j, x1);
-        Vec<T>::ld(x + r * dh + j + half, x2);
+        const bool second = i >= total1;
+        const long long ii = second ? i - total1 : i;
+        const T* xs = second ? x2 : x;
+        T* os = second ? o2 : o;
+        const int hi = second ? heads_inner2 : heads_inner;
+        const int j = (int)(ii % hv) * N;
+        const long long r = ii / hv;
+        const int t = (int)((r / hi) % T_);
+        float x1[N], x2v[N], c[N], s[N], o1[N], o2v[N];
+        Vec<T>::ld(xs + r * dh + j, x1);
+        Vec<T>::ld(xs + r * dh + j + half, x2v);
 #pragma unroll
         for (int q = 0; q < N; q += 4) {
             Vec<float>::ld(cs + t * half + j + q, c + q);
@@ -189,28 +196,43 @@ __global__ void k_rope_vec(const T* x, const float* __restrict__ cs, const float
 #pragma unroll
         for (int q = 0; q < N; q++) {
             const float sq = inverse ? -s[q] : s[q];
-            o1[q] = x1[q] * c[q] - x2[q] * sq;
-            o2[q] = x1[q] * sq + x2[q] * c[q];
+            o1[q] = x1[q] * c[q] - x2v[q] * sq;
+            o2v[q] = x1[q] * sq + x2v[q] * c[q];
         }
-        Vec<T>::st(o + r * dh + j, o1);
-        Vec<T>::st(o + r * dh + j + half, o2);
+        Vec<T>::st(os + r * dh + j, o1);
+        Vec<T>::st(os + r * dh + j + half, o2v);
     }
 }
 int ax_rope(int dt, const void* x, const float* cs, const float* sn, void* o, int T_, int dh,
             long long rows, int heads_inner, int inverse, cudaStream_t st) {
+    return ax_rope2(dt, x, cs, sn, o, T_, dh, rows, heads_inner, inverse, nullptr, nullptr, 0, 1, st);
+}
+// x2/o2 (optional): a second tensor of rows2 rows with heads_inner2 heads per token, rotated in the same launch
+int ax_rope2(int dt, const void* x, const float* cs, const float* sn, void* o, int T_, int dh,
+             long long rows, int heads_inner, int inverse, const void* x2, void* o2, long long rows2, int heads_inner2,
+             cudaStream_t st) {
     if (rows <= 0 || dh < 2) return 0;
     if (heads_inner < 1) heads_inner = 1;
+    if (heads_inner2 < 1) heads_inner2 = 1;
+    if (!x2) rows2 = 0;
     const int half = dh / 2;
     const int N = dt == 1 ? 8 : 4;
-    const bool vec = (half % N == 0) && aligned16(x) && aligned16(o) && aligned16(cs) && aligned16(sn);
+    const bool vec = (half % N == 0) && aligned16(x) && aligned16(o) && aligned16(cs) && aligned16(sn) &&
+                     (!x2 || (aligned16(x2) && aligned16(o2)));
     if (vec) {
-        const long long items = rows * (half / N);
-        if (dt == 1) k_rope_vec<bf16><<<ew_grid(items, T256), T256, 0, st>>>((const bf16*)x, cs, sn, (bf16*)o, T_, dh, rows, heads_inner, inverse);
-        else k_rope_vec<float><<<ew_grid(items, T256), T256, 0, st>>>((const float*)x, cs, sn, (float*)o, T_, dh, rows, heads_inner, inverse);
+        const long long items = (rows + rows2) * (half / N);
+        if (dt == 1) k_rope_vec<bf16><<<ew_grid(items, T256), T256, 0, st>>>((const bf16*)x, cs, sn, (bf16*)o, T_, dh, rows, heads_inner, inverse,
+                                                                              (const bf16*)x2, (bf16*)o2, rows2, heads_inner2);
+        else k_rope_vec<float><<<ew_grid(items, T256), T256, 0, st>>>((const float*)x, cs, sn, (float*)o, T_, dh, rows, heads_inner, inverse,
+                                                                        (const float*)x2, (float*)o2, rows2, heads_inner2);
     } else {
-        const long long items = rows * half;
-        if (dt == 1) k_rope<bf16><<<ew_grid(items, T256), T256, 0, st>>>((const bf16*)x, cs, sn, (bf16*)o, T_, dh, rows, heads_inner, inverse);
-        else k_rope<float><<<ew_grid(items, T256), T256, 0, st>>>((const float*)x, cs, sn, (float*)o, T_, dh, rows, heads_inner, inverse);
+        for (int which = 0; which < (x2 ? 2 : 1); which++) {
+            const void* xs = which ? x2 : x; void* os = which ? o2 : o;
+            const long long rr = which ? rows2 : rows; const int hi = which ? heads_inner2 : heads_inner;
+            const long long items = rr * half;
+            if (dt == 1) k_rope<bf16><<<ew_grid(items, T256), T256, 0, st>>>((const bf16*)xs, cs, sn, (bf16*)os, T_, dh, rr, hi, inverse);
+            else k_rope<float><<<ew_grid(items, T256), T256, 0, st>>>((const float*)xs, cs, sn, (float*)os, T_, dh, rr, hi, inverse);
+        }
     }
     return 0;
 }

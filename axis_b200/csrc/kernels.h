@@ -14,6 +14,8 @@ int ax_cast(int to_f32, const void* a, void* c, long long n, cudaStream_t st);
 int ax_perm0213(int dt, const void* a, void* c, int d0, int d1, int d2, int d3, cudaStream_t st);
 int ax_rope(int dt, const void* x, const float* cs, const float* sn, void* o, int T, int dh,
             long long rows, int heads_inner, int inverse, cudaStream_t st);
+int ax_rope2(int dt, const void* x, const float* cs, const float* sn, void* o, int T, int dh, long long rows, int heads_inner,
+             int inverse, const void* x2, void* o2, long long rows2, int heads_inner2, cudaStream_t st);
 int ax_repeat_kv(int dt, const void* x, void* o, int B, int KV, int H, int T, int dh, cudaStream_t st);
 int ax_repeat_kv_bwd(int dt, const void* g, void* o, int B, int KV, int H, int T, int dh, cudaStream_t st);
 int ax_softmax_causal(int dt, const void* x, void* o, int rpb, int width, int qoff, long long rows, cudaStream_t st);

@@ -75,7 +75,8 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
     convention — slot 0 is always the rotary cos table):
 
     GEMM_EX:   as GEMM_SB, plus d = addend with c's shape: c = alpha*a@b + beta*d
-    ROPE_BTHD: a=x b=cos d=sin c=out on [batch=B, m=T, k=heads, n=DH]; tb=1 inverse
+    ROPE_BTHD: a=x b=cos d=sin c=out on [batch=B, m=T, k=heads, n=DH]; tb=1 inverse; optional second
+               tensor in the same launch: sa=x2 sb=out2 sc=its heads (0 = none)
     ATTN_FWD:  a=q [B,T,H,DH] b=k d=v [B,T,KV,DH] c=o; sa=lse [B,H,T];
                m=T n=DH k=KV batch=B tb=H; alpha=scale
     ATTN_BWD:  a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=scratch (B*H*T

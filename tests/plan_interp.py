@@ -168,9 +168,11 @@ class InterpEngine:
             B_, T, H, DH = batch, m, k, n
             cos = self._f32(b, T * (DH // 2)).reshape(T, DH // 2)
             sin = self._f32(d, T * (DH // 2)).reshape(T, DH // 2)
-            x = self._get(a, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)
-            y = O.rope_bwd(x, cos, sin) if tb else O.rope_fwd(x, cos, sin)
-            return self._put(c, y.transpose(0, 2, 1, 3), dt)
+            for (src, dst, heads) in ((a, c, H),) + (((sa, sb, sc),) if sc > 0 else ()):
+                x = self._get(src, B_ * T * heads * DH, dt).reshape(B_, T, heads, DH).transpose(0, 2, 1, 3)
+                y = O.rope_bwd(x, cos, sin) if tb else O.rope_fwd(x, cos, sin)
+                self._put(dst, y.transpose(0, 2, 1, 3), dt)
+            return None
         if kind == E.ATTN_FWD:
             B_, T, DH, KV, H = batch, m, n, k, tb
             q = self._get(a, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)

@@ -125,6 +125,15 @@ def test_perm_rope_repeat(eng, dt):
     close(get(eng, ix, x.shape, dt), O.rope_fwd(xb, cos, sin).transpose(0, 2, 1, 3), dt)
     eng.run([op(E.ROPE_BTHD, a=ix, b=ic, d=isn, c=ix, batch=B, m=T, k=H, n=DH, tb=1, dt=dt)])
     close(get(eng, ix, x.shape, dt), x, dt)
+    # a second tensor with its own head count in the same launch (query and key projections)
+    xk = rnd(rng, (B, T, KV, DH), dt)
+    ik = put(eng, xk, dt)
+    eng.run([op(E.ROPE_BTHD, a=ix, b=ic, d=isn, c=ix, batch=B, m=T, k=H, n=DH, dt=dt, sa=ik, sb=ik, sc=KV)])
+    close(get(eng, ix, x.shape, dt), O.rope_fwd(xb, cos, sin).transpose(0, 2, 1, 3), dt)
+    close(get(eng, ik, xk.shape, dt), O.rope_fwd(xk.transpose(0, 2, 1, 3), cos, sin).transpose(0, 2, 1, 3), dt)
+    eng.run([op(E.ROPE_BTHD, a=ix, b=ic, d=isn, c=ix, batch=B, m=T, k=H, n=DH, tb=1, dt=dt, sa=ik, sb=ik, sc=KV)])
+    close(get(eng, ix, x.shape, dt), x, dt)
+    close(get(eng, ik, xk.shape, dt), xk, dt)
     # head_dim 6: scalar rotary path
     x6 = rnd(rng, (B, 2, T, 6), dt)
     c6, s6 = O.rope_tables(T, 6)
