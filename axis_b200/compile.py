@@ -393,8 +393,12 @@ class CompiledTransformer:
             ]
             plan += lin_f(at2s[i], i, "attn.o_proj", r1s[i], res=xs[i])
             plan += [op(RMSNORM, a=r1s[i], b=P[p + "mlp_norm.weight"], c=zs[i], m=N, n=D, dt=DT, alpha=eps)]
-            plan += lin_f_group(zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), (gs[i], us[i]))
-            plan += [op(SILU_MUL, a=gs[i], b=us[i], c=hs[i], n=N * MLP, dt=DT)]
+            if lora:
+                plan += lin_f_group(zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), (gs[i], us[i]))
+                plan += [op(SILU_MUL, a=gs[i], b=us[i], c=hs[i], n=N * MLP, dt=DT)]
+            else:   # gate and up projections with the activation in the epilogue: g, u and h = silu(g)*u in one launch
+                plan += [op(GEMM_GROUP, a=zs[i], b=P[p + "mlp.gate_proj.weight"], sa=P[p + "mlp.up_proj.weight"],
+                            c=gs[i], d=us[i], sc=hs[i], m=N, n=MLP, k=D, batch=2, oc=4, dt=DT)]
             plan += lin_f(hs[i], i, "mlp.down_proj", xs[i + 1], res=r1s[i])
 
         # ── head + loss ──

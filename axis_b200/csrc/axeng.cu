@@ -302,11 +302,36 @@ static int do_gemm(const EngOp* op, bool ex) {
 //   mode 1 (shared input): A = a; B_g = b, sa, sb; C_g = c, d, sc; n_g = n, oa, ob; k = k.
 //   mode 2 (summed over K-segments): C = c; A_s = a, sa, sb; B_s = b, d, sc; k_s = k, oa, ob; n = n.
 //   mode 3 (two independent problems of one depth k): A = a, sa; B = b, sb; C = c, d; m = m, oa; n = n, ob.
+//   mode 4 (SwiGLU pair, batch = 2): A = a; gate weights b, up weights sa (both n wide); outputs g = c, u = d,
+//           h = silu(g) * u = sc.
 // When the grouped tensor-core kernel cannot serve the request (fp32 plan, shapes, alignment) the problems run
 // one after another through the ordinary GEMM path: mode 2 as one GEMM plus accumulating ones.
 static int do_gemm_group(const EngOp* op) {
     const int count = op->batch, mode = op->oc;
-    if (count < 2 || count > 3 || mode < 1 || mode > 3 || (mode == 3 && count != 2)) { set_err("gemm_group: bad count/mode"); return 112; }
+    if (count < 2 || count > 3 || mode < 1 || mode > 4 || ((mode == 3 || mode == 4) && count != 2)) { set_err("gemm_group: bad count/mode"); return 112; }
+    if (mode == 4) {
+        const int dt4 = op->dt;
+        const long long e4 = dt4 == 1 ? 2 : 4;
+        const long long mn = (long long)op->m * op->n;
+        NEED(op->a, (long long)op->m * op->k * e4); NEED(op->b, (long long)op->k * op->n * e4); NEED(op->sa, (long long)op->k * op->n * e4);
+        NEED(op->c, mn * e4); NEED(op->d, mn * e4); NEED(op->sc, mn * e4);
+        if (dt4 == 1 && op->tb == 0 && !(G.fallback & 1) && !(G.fallback & 4)) {
+            const void* A[1] = {BUFP(op->a)}; const void* B[2] = {BUFP(op->b), BUFP(op->sa)};
+            void* C[3] = {BUFP(op->c), BUFP(op->d), BUFP(op->sc)};
+            const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
+            const int rc = ax_gemm_tc2_group(1, 0, 4, 2, A, B, C, &op->m, &op->n, &op->k, alpha, G.d_status, G.cur);
+            if (rc == 0) { G.launches++; return 0; }
+            if (rc > 0) { set_err("fused SwiGLU gemm failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+        }
+        // unfused: two GEMMs and the activation kernel
+        EngOp g1 = *op; g1.kind = ENG_GEMM_SB; g1.batch = 1; g1.sa = g1.sb = g1.sc = 0; g1.oa = g1.ob = g1.oc = 0; g1.d = -1; g1.beta = 0.f;
+        EngOp g2 = g1; g2.b = op->sa; g2.c = op->d;
+        int rc = do_gemm(&g1, false);
+        if (!rc) rc = do_gemm(&g2, false);
+        if (rc) return rc;
+        G.launches++;
+        return ax_binary(2, dt4, BUFP(op->c), BUFP(op->d), BUFP(op->sc), mn, G.cur);
+    }
     const int ia[3] = {op->a, op->sa, op->sb}, ib[3] = {op->b, mode == 1 ? op->sa : op->d, mode == 1 ? op->sb : op->sc};
     const int ic[3] = {op->c, op->d, op->sc}, dims[3] = {mode == 1 ? op->n : op->k, op->oa, op->ob};
     EngOp sub[3];

@@ -103,6 +103,9 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar) {
 //   mode 3: `count` independent problems of the same depth k, each with its own A, B, C, m[g] and n[g] (weight
 //           gradients of different projections of a layer): their tiles form one tile space, so the second
 //           problem fills the wave the first one leaves half empty.
+//   mode 4: SwiGLU pair — gate and up projections of one input with the activation fused: a 256-wide pair tile holds
+//           128 gate columns (B from problem 0, loaded by CTA 0) and the same 128 up columns (problem 1, CTA 1), so an
+//           epilogue thread has g and u of its row side by side and writes g, u and h = silu(g) * u (three outputs).
 // Grouped launches write through TMA stores, take no addend and do not split K.
 struct GemmGroup {
     int mode, count;
@@ -140,7 +143,9 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t smem_base = smem_u32(smem);
-    const int nst = tma_out == 2 ? STAGES2 - 1 : STAGES2;          // operand stages in use
+    const bool swiglu = grp.mode == 4;
+    const bool wide_stg = tma_out == 2 || swiglu;                  // four staging buffers per epilogue warp, five stages
+    const int nst = wide_stg ? STAGES2 - 1 : STAGES2;              // operand stages in use
     const uint32_t bar_d = smem_u32(bars + 20);                    // [4 warps][4 buffers] addend-arrival barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -150,6 +155,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     int tiles_n = (n + BN2 - 1) / BN2, kblocks_all = (k + BK2 - 1) / BK2;
     if (grp.mode == 1) { tiles_n = 0; for (int q = 0; q < grp.count; q++) tiles_n += (grp.n[q] + BN2 - 1) / BN2; }
     if (grp.mode == 2) { kblocks_all = 0; for (int q = 0; q < grp.count; q++) kblocks_all += grp.kb[q]; }
+    if (swiglu) tiles_n = (n + 127) / 128;
     int num_tiles = tiles_m * tiles_n;
     if (grp.mode == 3) {
         num_tiles = 0;
@@ -216,10 +222,12 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const int kb0 = split * kb_per, kb1 = min(kblocks_all, kb0 + kb_per);
             int tm, tl;
             const int g = locate(tile, tm, tl);
-            const int row0 = tm * 2 * BM2 + rank * BM2, col0 = tl * BN2 + rank * 128;
-            // operand maps: modes 1 and 3 pick B by problem (mode 3 also A), mode 2 walks A and B through the K-segments
+            const int row0 = tm * 2 * BM2 + rank * BM2, col0 = swiglu ? tl * 128 : tl * BN2 + rank * 128;
+            // operand maps: modes 1 and 3 pick B by problem (mode 3 also A), mode 2 walks A and B through the K-segments,
+            // mode 4 gives CTA 0 the gate weights and CTA 1 the up weights (same 128 columns)
             const CUtensorMap* pA = grp.mode == 3 ? (g == 0 ? &tmA : (g == 1 ? &tmA1 : &tmA2)) : &tmA;
-            const CUtensorMap* pB = (grp.mode == 1 || grp.mode == 3) ? (g == 0 ? &tmB : (g == 1 ? &tmB1 : &tmB2)) : &tmB;
+            const CUtensorMap* pB = (grp.mode == 1 || grp.mode == 3) ? (g == 0 ? &tmB : (g == 1 ? &tmB1 : &tmB2))
+                                    : (swiglu && rank == 1 ? &tmB1 : &tmB);
             int seg = 0, kl = kb0;                       // segment and k-block inside it
             if (grp.mode == 2) while (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl -= grp.kb[seg]; seg++; }
             for (int kb = kb0; kb < kb1; kb++, kl++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
@@ -290,8 +298,8 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         const float a_eff = ksplit > 1 ? 1.f : alpha;
         // staging: two 4 KB buffers per warp behind the operand ring; four when the addend is fetched by TMA
         // (the ring's last stage is then unused and adjoins the staging area)
-        const int nbuf = tma_out == 2 ? 4 : 2;
-        const uint32_t stg_off = tma_out == 2 ? (STAGES2 - 1) * STAGE_BYTES2 + quad * 16384 : STAGES2 * STAGE_BYTES2 + quad * 8192;
+        const int nbuf = wide_stg ? 4 : 2;
+        const uint32_t stg_off = wide_stg ? (STAGES2 - 1) * STAGE_BYTES2 + quad * 16384 : STAGES2 * STAGE_BYTES2 + quad * 8192;
         uint8_t* stg = smem + stg_off;
         const uint32_t stg_u32 = smem_base + stg_off;
         const uint32_t my_bar_d = bar_d + 32 * quad;
@@ -309,7 +317,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const CUtensorMap* pC = g == 0 ? &tmC : (g == 1 ? &tmC1 : &tmC2);
             const int ncols = min(BN2, ((grp.mode == 1 || grp.mode == 3) ? grp.n[g] : n) - tl * BN2);
             const int m_g = grp.mode == 3 ? grp.m[g] : m;
-            const int npc = (tma_out && row0 < m_g) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
+            const int npc = (tma_out && !swiglu && row0 < m_g) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
             const uint32_t pbase = pieces;
             auto fetch_d = [&](int j) {                          // lane 0: addend piece j of this tile -> its buffer
                 const uint32_t bi = (pbase + j) & 3;
@@ -325,7 +333,54 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             tc_fence_after();
             if (timing && threadIdx.x == 64) prof[5] = clock64();
             const uint32_t taddr = tmem_base + acc * BN2 + ((uint32_t)(quad * 32) << 16);
-            if (tma_out) {
+            if (swiglu) {
+                // accumulator columns 0..127: gate, 128..255: up (same output columns tl*128 ..); per 64-column piece
+                // three staged outputs g, u, h, each stored by its own bulk group so that the buffers rotate freely
+                const int vcols = min(128, n - tl * 128);
+                const int np2 = row0 < m ? (vcols + 63) / 64 : 0;
+#pragma unroll 1
+                for (int j = 0; j < np2; j++) {
+                    if (lane == 0) bulk_wait_read_le1();        // only the latest store may still be reading its buffer
+                    __syncwarp();
+                    uint8_t* bg = stg + ((pieces) & 3) * 4096 + lane * 128;
+                    uint8_t* bu = stg + ((pieces + 1) & 3) * 4096 + lane * 128;
+                    uint8_t* bh = stg + ((pieces + 2) & 3) * 4096 + lane * 128;
+#pragma unroll 1
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t rg[32], ru[32];
+                        tmem_ld32(taddr + j * 64 + half * 32, rg);
+                        tmem_ld32(taddr + 128 + j * 64 + half * 32, ru);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            float g8[8], u8[8], h8[8];
+#pragma unroll
+                            for (int e2 = 0; e2 < 8; e2++) {
+                                g8[e2] = alpha * __uint_as_float(rg[q * 8 + e2]);
+                                u8[e2] = alpha * __uint_as_float(ru[q * 8 + e2]);
+                                h8[e2] = g8[e2] / (1.f + __expf(-g8[e2])) * u8[e2];
+                            }
+                            const int sw = ((half * 4 + q) ^ (lane & 7)) << 4;
+                            uint4 pk;
+                            pk.x = pack2_bf16(g8[0], g8[1]); pk.y = pack2_bf16(g8[2], g8[3]); pk.z = pack2_bf16(g8[4], g8[5]); pk.w = pack2_bf16(g8[6], g8[7]);
+                            *reinterpret_cast<uint4*>(bg + sw) = pk;
+                            pk.x = pack2_bf16(u8[0], u8[1]); pk.y = pack2_bf16(u8[2], u8[3]); pk.z = pack2_bf16(u8[4], u8[5]); pk.w = pack2_bf16(u8[6], u8[7]);
+                            *reinterpret_cast<uint4*>(bu + sw) = pk;
+                            pk.x = pack2_bf16(h8[0], h8[1]); pk.y = pack2_bf16(h8[2], h8[3]); pk.z = pack2_bf16(h8[4], h8[5]); pk.w = pack2_bf16(h8[6], h8[7]);
+                            *reinterpret_cast<uint4*>(bh + sw) = pk;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int cx = tl * 128 + j * 64;
+                        tma_store_3d(&tmC, stg_u32 + ((pieces) & 3) * 4096, cx, row0, 0); bulk_commit2();
+                        tma_store_3d(&tmC1, stg_u32 + ((pieces + 1) & 3) * 4096, cx, row0, 0); bulk_commit2();
+                        tma_store_3d(&tmC2, stg_u32 + ((pieces + 2) & 3) * 4096, cx, row0, 0); bulk_commit2();
+                    }
+                    pieces += 3;
+                }
+            } else if (tma_out) {
 #pragma unroll 1
                 for (int j = 0; j < npc && ok; j++) {
                     const int c = j * cw;
@@ -502,11 +557,14 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
             grp.kb[g] = (kv[g] + BK2 - 1) / BK2;
         }
         tiles_n = (n + 255) / 256;
-    } else {
+    } else if (mode == 3) {
         for (int g = 0; g < count; g++) {
             if (map_a<A_MN>(&tmA[g], A[g], mv[g], k) || map_b<B_MN>(&tmB[g], B[g], nv[g], k)) return 2;
             grp.m[g] = mv[g]; grp.n[g] = nv[g];
         }
+    } else {        // mode 4: gate and up weights of the same width n; outputs g, u, h
+        if (sizeof(TO) != 2 || count != 2) return -1;
+        if (map_a<A_MN>(&tmA[0], A[0], m, k) || map_b<B_MN>(&tmB[0], B[0], n, k) || map_b<B_MN>(&tmB[1], B[1], n, k)) return 2;
     }
     const bool per_problem_c = mode == 1 || mode == 3;
     // output through TMA tile stores when the destination allows it: 1 = no addend to read, 2 = addend by TMA too
@@ -514,7 +572,7 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     const bool has_d = D != nullptr && beta != 0.f && ksplit == 1;
     int tma_out = 0;
     bool c_ok = ax_gemm_tma_out() != 0;
-    for (int g = 0; g < (per_problem_c ? count : 1); g++)
+    for (int g = 0; g < (per_problem_c ? count : (mode == 4 ? 3 : 1)); g++)
         c_ok = c_ok && ((uintptr_t)C[g] & 15) == 0 && ((long long)nv[per_problem_c ? g : 0] * osz) % 16 == 0;
     if (c_ok && (!has_d || ((uintptr_t)D & 15) == 0)) tma_out = has_d ? 2 : 1;
     if (mode != 0 && (tma_out != 1 || ksplit != 1)) return -1;          // grouped launches need the plain TMA-store epilogue
@@ -522,6 +580,8 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
         size_t wsb0 = 0;
         if (per_problem_c) {
             for (int g = 0; g < count; g++) if (map_c(&tmC[g], C[g], mode == 3 ? mv[g] : m, nv[g], 1, osz)) return 2;
+        } else if (mode == 4) {
+            for (int g = 0; g < 3; g++) if (map_c(&tmC[g], C[g], m, n, 1, osz)) return 2;
         } else {
             void* base = ksplit > 1 ? (void*)ax_splitk_ws(&wsb0) : C[0];
             if (map_c(&tmC[0], base, m, n, ksplit > 1 ? ksplit : 1, osz)) return 2;
@@ -534,10 +594,11 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     for (int g = 1; g < 3; g++) {           // unused slots carry valid (ignored) maps
         if ((mode != 2 && mode != 3) || g >= count) tmA[g] = tmA[0];
         if (mode == 0 || g >= count) tmB[g] = tmB[0];
-        if (!per_problem_c || g >= count || !tma_out) tmC[g] = tmC[0];
+        if (mode != 4 && (!per_problem_c || g >= count || !tma_out)) tmC[g] = tmC[0];
     }
     int units = ((m + 255) / 256) * tiles_n * ksplit;
     if (mode == 3) { units = 0; for (int g = 0; g < count; g++) units += ((mv[g] + 255) / 256) * ((nv[g] + 255) / 256); }
+    if (mode == 4) units = ((m + 255) / 256) * ((n + 127) / 128);
     const int pairs = units < maxp ? units : maxp;
     size_t wsb = 0;
     float* ws = ax_splitk_ws(&wsb);
@@ -594,10 +655,12 @@ int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, con
 
 // Grouped launch (see GemmGroup).  mode 1: A[0] shared, B[g] / C[g] / n[g] per problem, m[0], k[0].  mode 2: A[s] / B[s] /
 // k[s] per segment, C[0], m[0], n[0].  mode 3: A[g] / B[g] / C[g] / m[g] / n[g] per problem, k[0].  Returns -1 when this
-// kernel cannot serve the request (the caller then runs the problems one by one).
+// kernel cannot serve the request (the caller then runs the problems one by one).  mode 4: A[0], B[0] = gate weights,
+// B[1] = up weights (both n[0] wide), C[0] = g, C[1] = u, C[2] = silu(g) * u; bf16 output only.
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
                       const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st) {
-    if (count < 2 || count > 3 || mode < 1 || mode > 3) return -1;
+    if (count < 2 || count > 3 || mode < 1 || mode > 4) return -1;
+    if (mode == 4 && (!out_bf16 || count != 2 || !aligned16(C[2]))) return -1;
     for (int g = 0; g < count; g++) {
         if (!aligned16(A[(mode == 2 || mode == 3) ? g : 0]) || !aligned16(B[g])) return -1;
         const int mg = m[mode == 3 ? g : 0], ng = n[(mode == 1 || mode == 3) ? g : 0], kg = k[mode == 2 ? g : 0];

@@ -103,6 +103,8 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                k,oa,ob = k_s; n
                oc=3 (two independent problems of one depth k): a,sa = A_g; b,sb = B_g; c,d = C_g;
                m,oa = m_g; n,ob = n_g
+               oc=4 (SwiGLU pair, batch=2): a=A; b=gate weights, sa=up weights (n wide each);
+               c=g, d=u, sc=h=silu(g)*u
     """
     return (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc,
             alpha, beta, gamma)

@@ -379,6 +379,8 @@ def kernel_table(ct, c, batch):
             # o = (kind, a, b, c, d, m, n, k, batch=count, tb, sa, sb, sc, dt, oa, ob, oc=mode, ...)
             if o[16] == 3:      # two independent problems: m = o[5], o[14]; n = o[6], o[15]; k = o[7]
                 gemm_flops += 2.0 * o[7] * (o[5] * o[6] + o[14] * o[15])
+            elif o[16] == 4:    # gate and up projections of width n each
+                gemm_flops += 2.0 * o[5] * 2 * o[6] * o[7]
             else:
                 extra = sum((o[14], o[15])[:o[8] - 1])
                 gemm_flops += 2.0 * o[5] * ((o[6] + extra) * o[7] if o[16] == 1 else o[6] * (o[7] + extra))

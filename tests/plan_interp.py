@@ -144,6 +144,13 @@ class InterpEngine:
             self.launches -= 1
             ia, ic, dims = (a, sa, sb), (c, d, sc), (n if oc == 1 else k, oa, ob)
             ib = (b, sa, sb) if oc == 1 else (b, d, sc)
+            if oc == 4:
+                for (w_, out_) in ((b, c), (sa, d)):
+                    self.launches += 1
+                    self._gemm(E.op(E.GEMM_SB, a=a, b=w_, c=out_, m=m, n=n, k=k, batch=1, tb=tb, dt=dt, alpha=alpha), False)
+                self.launches += 1
+                g_, u_ = self._get(c, m * n, dt), self._get(d, m * n, dt)
+                return self._put(sc, O.silu_mul_fwd(g_, u_)[0], dt)
             for g_ in range(batch):
                 if oc == 3:
                     sub = E.op(E.GEMM_SB, a=(a, sa)[g_], b=(b, sb)[g_], c=(c, d)[g_], m=(m, oa)[g_], n=(n, ob)[g_], k=k,

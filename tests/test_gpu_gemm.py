@@ -216,3 +216,27 @@ def test_grouped_gemm_independent_problems(eng, dt, tb):
         ref = (As[g].T if tb == 2 else As[g]).astype(np.float64) @ (Bs[g].T if tb == 1 else Bs[g]).astype(np.float64)
         check(got, ref.astype(np.float32), out_bf, k)
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(520, 392, 320), (256, 128, 64), (1032, 1000, 136)])
+def test_grouped_gemm_swiglu_pair(eng, dt, m, n, k):
+    """GEMM_GROUP mode 4: gate and up projections with h = silu(g) * u written by the same launch (bf16);
+    the fp32 plan runs the unfused sequence behind the same op."""
+    rng = np.random.default_rng(m + n + k + dt)
+    A = rng.standard_normal((m, k)).astype(np.float32) * 0.5
+    Wg = rng.standard_normal((k, n)).astype(np.float32) * 0.2
+    Wu = rng.standard_normal((k, n)).astype(np.float32) * 0.2
+    if dt:
+        A, Wg, Wu = bf(A), bf(Wg), bf(Wu)
+    ia, ig, iu = put(eng, A, dt), put(eng, Wg, dt), put(eng, Wu, dt)
+    og, ou, oh = (eng.alloc(m * n, 2 if dt else 4) for _ in range(3))
+    eng.run([op(E.GEMM_GROUP, a=ia, b=ig, sa=iu, c=og, d=ou, sc=oh, m=m, n=n, k=k, batch=2, oc=4, dt=dt)])
+    g = A.astype(np.float64) @ Wg.astype(np.float64)
+    u = A.astype(np.float64) @ Wu.astype(np.float64)
+    h = g / (1.0 + np.exp(-g)) * u
+    get_ = (lambda i: eng.download_bf16(i, (m, n))) if dt else (lambda i: eng.download(i, (m, n)))
+    check(get_(og), g.astype(np.float32), dt == 1, k)
+    check(get_(ou), u.astype(np.float32), dt == 1, k)
+    check(get_(oh), h.astype(np.float32), dt == 1, k)
+    assert eng.device_status() == 0
