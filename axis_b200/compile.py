@@ -28,7 +28,7 @@ from typing import Dict, List, Sequence
 import numpy as np
 
 from axis_b200.engine import (
-    ADAMW_FLAT, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, EMBED_BWD_DET,
+    ADAMW_FLAT, ADD, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, COPY, EMBED_BWD_DET,
     EMBED_I32, FORK, GEMM_EX, GEMM_GROUP, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
     ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, Engine, f32_to_bf16_bits, op)
 
@@ -539,6 +539,48 @@ class CompiledTransformer:
         self._feed(tokens, targets)
         self.eng.replay(1, sync=False)
         return float(self.eng.download(self.b_loss, (1,))[0])
+
+    def step_accumulate(self, batches) -> float:
+        """One optimizer step over several micro-batches of the compiled shape (gradient accumulation).
+
+        The gradient applied is the mean of the micro-batch gradients, each normalised by its own count of
+        valid targets — with micro-batches of equal valid counts this is the gradient of the concatenated
+        batch (the equivalence the reference checks in tests/test_generate_accum.py:51); the returned loss is
+        the mean of the micro-batch losses.  Under data parallelism the averaged gradient is reduced once, after
+        the last micro-batch.  Costs one extra fp32 arena of the gradients' size."""
+        batches = list(batches)
+        n = len(batches)
+        if n < 1:
+            raise ValueError("no micro-batches")
+        if not hasattr(self, "_acc_plans"):
+            self.a_gacc = self.eng.alloc_zero(self._P_total * 4)
+            lim = 1 << 30                     # element counts of flat ops stay inside int32
+
+            def flat(kind, **kw):
+                out = []
+                for o in range(0, self._P_total, lim):
+                    ln = min(lim, self._P_total - o)
+                    v = {k_: (self.eng.view(b_, o * 4, ln * 4) if o or ln < self._P_total else b_) for k_, b_ in kw["bufs"].items()}
+                    out.append(op(kind, n=ln, dt=0, alpha=kw.get("alpha", 0.0), **v))
+                return out
+            self._acc_flat = flat
+            self._acc_plans = {}
+        if n not in self._acc_plans:
+            inv = 1.0 / n
+            first = self.plan_fb + self._acc_flat(SCALE, bufs=dict(a=self.a_grad, c=self.a_gacc), alpha=inv)
+            nxt = self.plan_fb + self._acc_flat(SCALE, bufs=dict(a=self.a_grad, c=self.a_grad), alpha=inv) \
+                + self._acc_flat(ADD, bufs=dict(a=self.a_gacc, b=self.a_grad, c=self.a_gacc))
+            last = self._acc_flat(COPY, bufs=dict(a=self.a_gacc, c=self.a_grad)) + self.plan_ar \
+                + self._opt_ops(self.max_grad_norm)
+            self._acc_plans[n] = (first, nxt, last)
+        first, nxt, last = self._acc_plans[n]
+        total = 0.0
+        for i, (x, y) in enumerate(batches):
+            self._feed(x, y)
+            self.eng.run(first if i == 0 else nxt, sync=False)
+            total += float(self.eng.download(self.b_loss, (1,))[0])
+        self.eng.run(last, sync=False)
+        return total / n
 
     def forward_backward(self, tokens: np.ndarray, targets: np.ndarray) -> float:
         """Forward + backward only (no reduction, no update); for gradient checks."""

@@ -238,6 +238,10 @@ class InterpEngine:
             tab = self._f32(c).reshape(-1, n)
             np.add.at(tab, ids, g)
             return
+        if kind == E.ADD:
+            return self._put(c, self._get(a, n, dt) + self._get(b, n, dt), dt)
+        if kind == E.COPY:
+            return self._put(c, self._get(a, n, dt), dt)
         if kind == E.SCALE:
             if alpha == 0.0:
                 return self._put(c, np.zeros(n, np.float32), dt)

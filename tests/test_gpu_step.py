@@ -216,3 +216,27 @@ def test_lora_bf16_and_prompt_masking():
         ct.step(x, y)
         after = ct.get_weights()
         assert set(after) == set(ct.pnames) and any(not np.array_equal(before[n], after[n]) for n in after)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_gradient_accumulation_equals_the_concatenated_batch(dtype):
+    """step_accumulate over two micro-batches with equal valid counts == one step on the concatenated batch
+    (oracle), the reference's accumulation equivalence (tests/test_generate_accum.py:51)."""
+    cfg = dict(vocab_size=96, dim=64, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=96, tie_embeddings=True)
+    B, T = 2, 32
+    w0 = O.init_weights(cfg, seed=4)
+    rng = np.random.default_rng(4)
+    xs = [rng.integers(0, cfg["vocab_size"], (B, T)) for _ in range(2)]
+    ys = [np.roll(x, -1, axis=1) for x in xs]
+    ct = build(cfg, w0, B, T, dtype=dtype, max_grad_norm=1.0)
+    loss = ct.step_accumulate(list(zip(xs, ys)))
+    model = O.OracleTransformer(cfg, w0)
+    opt = O.OracleAdamW(model)
+    l_ref = O.train_step(model, opt, np.concatenate(xs), np.concatenate(ys), max_grad_norm=1.0)[0]
+    assert abs(loss - l_ref) <= (2e-6 if dtype == "fp32" else 1e-3) * abs(l_ref)
+    w = ct.get_weights()
+    tol = 0.05 * 3e-4 if dtype == "fp32" else 2.5 * 3e-4
+    for nm in w:
+        assert np.abs(w[nm] - model.w[nm]).max() <= tol, nm
+    assert ct.eng.device_status() == 0
+    ct.eng.shutdown()

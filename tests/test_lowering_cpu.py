@@ -152,3 +152,27 @@ def test_invalid_inputs_are_rejected():
         ct.step(x, z["y/0"])
     with pytest.raises(ValueError):
         ct.step(z["x/0"][:, :-1], z["y/0"])
+
+
+def test_gradient_accumulation_equals_the_concatenated_batch():
+    """Two micro-batches with the same number of valid targets, accumulated, give the step of the
+    concatenated batch (the reference's accumulation equivalence, tests/test_generate_accum.py:51)."""
+    cfg = dict(vocab_size=61, dim=32, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=48, tie_embeddings=True)
+    B, T = 2, 12
+    w0 = O.init_weights(cfg, seed=4)
+    rng = np.random.default_rng(4)
+    xs = [rng.integers(0, cfg["vocab_size"], (B, T)) for _ in range(2)]
+    ys = [np.roll(x, -1, axis=1) for x in xs]              # no ignored targets: equal counts
+    ct = CompiledTransformer(InterpEngine(), cfg, w0, B, T, dtype="fp32", max_grad_norm=1.0)
+    loss = ct.step_accumulate(list(zip(xs, ys)))
+    model = O.OracleTransformer(cfg, w0)
+    opt = O.OracleAdamW(model)
+    l_ref = O.train_step(model, opt, np.concatenate(xs), np.concatenate(ys), max_grad_norm=1.0)[0]
+    assert abs(loss - l_ref) <= 2e-6 * abs(l_ref)
+    w = ct.get_weights()
+    for nm in w:
+        assert np.abs(w[nm] - model.w[nm]).max() <= 0.02 * 3e-4, nm
+    # a second accumulated step reuses the cached plans and keeps tracking the oracle
+    loss2 = ct.step_accumulate(list(zip(xs[::-1], ys[::-1])))
+    l2 = O.train_step(model, opt, np.concatenate(xs[::-1]), np.concatenate(ys[::-1]), max_grad_norm=1.0)[0]
+    assert abs(loss2 - l2) <= 5e-6 * abs(l2)
