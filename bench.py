@@ -388,7 +388,7 @@ def kernel_table(ct, c, batch):
     # DRAM bytes per GEMM launch inside this step (dram__bytes_read.sum + dram__bytes_write.sum averaged over
     # the 577 GEMM launches of one step in an ncu capture of this command line; summary:
     # profiles/step_1b_launch_list.md).  It belongs to the 1B-class workload only.
-    traffic = 142.7e6 if c.get("name", "").startswith("1B-class") and "LoRA" not in c.get("name", "") else None
+    traffic = 148.2e6 if c.get("name", "").startswith("1B-class") and "LoRA" not in c.get("name", "") else None
     out = {"roofline": {"bound": "tensor", "kernel": "k_gemm_tc2 / k_gemm_tc (tcgen05 bf16 GEMM, all GEMM ops of the step)",
                         "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s", "frac": achieved / tf_sus,
                         "peak_source": f"{src} (sustained cuBLAS bf16)", "launches": gemm_calls,
