@@ -177,7 +177,9 @@ def ownership_case():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python make_golden.py <path to a checkout of the reference repository>")
+    ref = sys.argv[1]
     sys.path.insert(0, ref)
     sys.dont_write_bytecode = True
     step_case("step_tied_gqa", V=96, D=64, L=2, H=4, KV=2, MLP=80, B=2, T=12, tied=True,
