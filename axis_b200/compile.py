@@ -67,7 +67,7 @@ class CompiledTransformer:
                                "gate_proj", "up_proj", "down_proj"),
                  grad_sync: bool = False, max_grad_norm: float = 0.0,
                  zero_stage: int = 0, rank: int = 0, world: int = 1,
-                 bucket_layers: int = 4, adam_eps: float = 1e-8):
+                 bucket_layers: int = 4, adam_eps: float = 1e-8, recompute_blocks: bool = False):
         assert dtype in ("fp32", "bf16")
         assert attn_impl in ("auto", "flash", "tiled")
         self.cfg = cfg
@@ -205,6 +205,19 @@ class CompiledTransformer:
         self.master, self.gbuf, self._mb, self._vb = {}, {}, {}, {}
         P: Dict[str, int] = {}               # compute view of every weight the plan reads
         src = dict(weights)
+        # A weight is an fp32 array, or a checkpoint tensor still in its file layout (an object with
+        # `shape` in this engine's layout and `load_into`, see pretrained.HfTensor) that is converted on the
+        # device through one staging buffer.
+        lazy = [w for w in src.values() if hasattr(w, "load_into")]
+        stage = A(max(_numel(w.shape) for w in lazy), 2) if lazy else -1
+
+        def put(dst: int, w, fp32_out: bool) -> None:
+            if hasattr(w, "load_into"):
+                w.load_into(eng, dst, fp32_out, stage)
+            elif fp32_out:
+                eng.upload(dst, np.ascontiguousarray(w, dtype=np.float32).reshape(-1))
+            else:
+                eng.upload_raw(dst, f32_to_bf16_bits(np.ascontiguousarray(w, dtype=np.float32)))
         if lora:
             rng_l = np.random.default_rng(0)
             for i in range(L):
@@ -220,15 +233,15 @@ class CompiledTransformer:
             self.a_base = eng.alloc_zero(tot * isz)
             o = 0
             for nm in base_names:
-                w = np.ascontiguousarray(weights[nm], dtype=np.float32)
-                P[nm] = eng.view(self.a_base, o * isz, w.size * isz)
-                eng.upload_raw(P[nm], f32_to_bf16_bits(w) if hf else w)
-                o += _pad(w.size)
+                n_el = _numel(weights[nm].shape)
+                P[nm] = eng.view(self.a_base, o * isz, n_el * isz)
+                put(P[nm], weights[nm], not hf)
+                o += _pad(n_el)
         for nm in self.pnames:
             n_el = _numel(self.shapes[nm])
             o = self._off[nm]
             self.gbuf[nm] = eng.view(self.a_grad, o * 4, n_el * 4)
-            w = np.ascontiguousarray(src[nm], dtype=np.float32)
+            w = src[nm]
             if tuple(w.shape) != tuple(self.shapes[nm]):
                 raise ValueError(f"{nm}: shape {w.shape} != {self.shapes[nm]}")
             if hf:
@@ -238,11 +251,11 @@ class CompiledTransformer:
                 self.master[nm] = eng.view(self.a_master, lo * 4, n_el * 4)
                 self._mb[nm] = eng.view(self.a_m, lo * 4, n_el * 4)
                 self._vb[nm] = eng.view(self.a_v, lo * 4, n_el * 4)
-                eng.upload(self.master[nm], w.reshape(-1))
+                put(self.master[nm], w, True)
                 if not hf:
                     P[nm] = self.master[nm]
             if hf and zero and self._cown[nm] != rank:
-                eng.upload_raw(P[nm], f32_to_bf16_bits(w))
+                put(P[nm], w, False)
         if hf and my_seg[1] > 0:
             # one cast of the whole owned segment (padding is zero on both sides)
             eng.run([op(CAST, a=self.a_master,
@@ -265,18 +278,30 @@ class CompiledTransformer:
         self.b_rb_scratch = A(RB_BLOCKS * D)
 
         # ── saved activations ──
+        # With recompute_blocks only the input of every block is kept (N*D per layer); the other
+        # activations live in ONE set of buffers that every block overwrites, and the backward re-runs a
+        # block's forward from its saved input before it differentiates it (the eager engine's
+        # ops.checkpoint, axis/ops.py:440-475, per transformer block).  Every forward kernel is
+        # deterministic, so the recomputed activations are the bits of the first pass: the backward sees
+        # the same inputs as without recompute.
+        self.recompute_blocks = rc = bool(recompute_blocks)
+
+        def per_layer(n_el, esz=isz):
+            if rc:
+                return [A(n_el, esz)] * L
+            return [A(n_el, esz) for _ in range(L)]
         xs = [A(N * D, isz) for _ in range(L + 1)]
-        ys = [A(N * D, isz) for _ in range(L)]
-        q2s = [A(N * H * DH, isz) for _ in range(L)]
-        k2s = [A(N * KV * DH, isz) for _ in range(L)]
-        vs = [A(N * KV * DH, isz) for _ in range(L)]
-        at2s = [A(N * H * DH, isz) for _ in range(L)]
-        r1s = [A(N * D, isz) for _ in range(L)]
-        zs = [A(N * D, isz) for _ in range(L)]
-        gs = [A(N * MLP, isz) for _ in range(L)]
-        us = [A(N * MLP, isz) for _ in range(L)]
-        hs = [A(N * MLP, isz) for _ in range(L)]
-        lses = [A(B * H * T) for _ in range(L)]
+        ys = per_layer(N * D)
+        q2s = per_layer(N * H * DH)
+        k2s = per_layer(N * KV * DH)
+        vs = per_layer(N * KV * DH)
+        at2s = per_layer(N * H * DH)
+        r1s = per_layer(N * D)
+        zs = per_layer(N * D)
+        gs = per_layer(N * MLP)
+        us = per_layer(N * MLP)
+        hs = per_layer(N * MLP)
+        lses = per_layer(B * H * T, 4)
         # ── scratch ──
         xf = A(N * D, isz)
         logits = A(N * V, isz)               # dlogits overwrite the logits
@@ -380,8 +405,10 @@ class CompiledTransformer:
                        sa=(0 if lora else G[wname]), sb=self.b_rb_scratch, m=N, n=D, dt=DT, alpha=eps)]
 
         # ── forward ──
-        plan = [op(EMBED_I32, a=P["embed.weight"], b=self.b_ids, c=xs[0], m=N, n=D, dt=DT)]
-        for i in range(L):
+        def block_f(i, down=True):
+            """forward of block i from xs[i]; down=False stops before the down projection (all that the
+            backward of the block reads is then in place)"""
+            plan = []
             p = f"blocks.{i}."
             plan += [op(RMSNORM, a=xs[i], b=P[p + "attn_norm.weight"], c=ys[i], m=N, n=D, dt=DT, alpha=eps)]
             plan += lin_f_group(ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), (q2s[i], k2s[i], vs[i]))
@@ -399,7 +426,13 @@ class CompiledTransformer:
             else:   # gate and up projections with the activation in the epilogue: g, u and h = silu(g)*u in one launch
                 plan += [op(GEMM_GROUP, a=zs[i], b=P[p + "mlp.gate_proj.weight"], sa=P[p + "mlp.up_proj.weight"],
                             c=gs[i], d=us[i], sc=hs[i], m=N, n=MLP, k=D, batch=2, oc=4, dt=DT)]
-            plan += lin_f(hs[i], i, "mlp.down_proj", xs[i + 1], res=r1s[i])
+            if down:
+                plan += lin_f(hs[i], i, "mlp.down_proj", xs[i + 1], res=r1s[i])
+            return plan
+
+        plan = [op(EMBED_I32, a=P["embed.weight"], b=self.b_ids, c=xs[0], m=N, n=D, dt=DT)]
+        for i in range(L):
+            plan += block_f(i)
 
         # ── head + loss ──
         lm_w = P["embed.weight"] if tied else P["lm_head.weight"]
@@ -426,6 +459,8 @@ class CompiledTransformer:
         marks = {0: len(plan)}
         for i in reversed(range(L)):
             p = f"blocks.{i}."
+            if rc and i < L - 1:      # the last block's activations are still in place after the forward
+                plan += block_f(i, down=False)
             plan += lin_b(dcur, hs[i], i, "mlp.down_proj", dh_)
             plan += [op(SILU_BWD, a=gs[i], b=us[i], d=dh_, c=dg_, tb=du_, n=N * MLP, dt=DT)]
             plan += lin_b_group((dg_, du_), zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), dz)
@@ -631,7 +666,8 @@ def compile_model(model, batch: int, seq: int, lib_path: str = None,
                   recompute_attn: bool = True, dtype: str = "fp32",
                   attn_tile: int = 256, attn_impl: str = "auto",
                   grad_sync: bool = False, max_grad_norm: float = 0.0,
-                  zero_stage: int = 0, rank: int = 0, world: int = 1) -> CompiledTransformer:
+                  zero_stage: int = 0, rank: int = 0, world: int = 1,
+                  recompute_blocks: bool = False) -> CompiledTransformer:
     """Compile a Transformer into a native training step (axis/compile.py:618-664).
 
     `model` is anything shaped like the reference's `axis.nn.Transformer`:
@@ -640,6 +676,9 @@ def compile_model(model, batch: int, seq: int, lib_path: str = None,
     are detected from parameter names (`...lora_a` / `...lora_b`,
     `...base.weight`), the rank from the adapter shape and alpha from the
     wrapper's `scaling` attribute; base weights are then frozen.
+
+    `recompute_blocks` (not in the reference's compiled engine, whose signature ends at `world`) trades a
+    second forward of every block for activation memory: see CompiledTransformer.
     """
     weights = {n.replace(".base.weight", ".weight"): np.asarray(p.data)
                for n, p in model.named_parameters()}
@@ -662,7 +701,8 @@ def compile_model(model, batch: int, seq: int, lib_path: str = None,
                                attn_impl=attn_impl, lora_r=lora_r, lora_alpha=lora_alpha,
                                lora_targets=targets or ("q_proj", "k_proj", "v_proj", "o_proj"),
                                grad_sync=grad_sync, max_grad_norm=max_grad_norm,
-                               zero_stage=zero_stage, rank=rank, world=world)
+                               zero_stage=zero_stage, rank=rank, world=world,
+                               recompute_blocks=recompute_blocks)
 
 
 def _find_lora_scaling(model) -> float:

@@ -564,6 +564,14 @@ static int exec_op(const EngOp* op) {
             G.launches++;
             return ax_cast(op->tb != 0, BUFP(op->a), BUFP(op->c), n, st);
         }
+        case ENG_TRANSPOSE_BF16: {
+            // a = bf16 [m,n]; c = [n,m] bf16 (dt=1) or fp32 (dt=0)
+            const long long el = (long long)op->m * op->n;
+            if (op->a == op->c) { set_err("transpose: in place is not supported"); return 112; }
+            NEED(op->a, el * 2); NEED(op->c, el * (dt == 1 ? 2 : 4));
+            G.launches++;
+            return ax_transpose_bf16(dt != 1, BUFP(op->a), BUFP(op->c), op->m, op->n, st);
+        }
         case ENG_ROWDOT: {
             const long long el = (long long)op->m * op->n;
             NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->b, el * (dt >= 1 ? 2 : 4)); NEED(op->c, (long long)op->m * 4);

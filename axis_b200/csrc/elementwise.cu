@@ -115,6 +115,34 @@ int ax_cast(int to_f32, const void* a, void* c, long long n, cudaStream_t st) {
     return 0;
 }
 
+// ── c[cols,rows] = a[rows,cols]^T, bf16 in, bf16 or fp32 out ───────────────
+// Load-time layout change of checkpoint weights (stored [out,in]) to the [in,out] layout the GEMMs read:
+// a 32 x 32 tile goes through shared memory so that both the reads and the writes are row-contiguous.
+template <typename TO>
+__global__ void __launch_bounds__(256) k_transpose_bf16(const bf16* __restrict__ a, TO* __restrict__ c, int rows, int cols) {
+    __shared__ unsigned short tile[32][33];
+    const unsigned short* ab = reinterpret_cast<const unsigned short*>(a);
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += 8)
+        if (r0 + r < rows && c0 + threadIdx.x < cols) tile[r][threadIdx.x] = ab[(long long)(r0 + r) * cols + c0 + threadIdx.x];
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8)
+        if (c0 + j < cols && r0 + threadIdx.x < rows) {
+            const unsigned short v = tile[threadIdx.x][j];
+            const long long o = (long long)(c0 + j) * rows + r0 + threadIdx.x;
+            if constexpr (sizeof(TO) == 4) c[o] = __uint_as_float((unsigned)v << 16);
+            else reinterpret_cast<unsigned short*>(c)[o] = v;
+        }
+}
+int ax_transpose_bf16(int out_f32, const void* a, void* c, int rows, int cols, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0) return 0;
+    const dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+    if (grid.y > 65535) return 121;
+    if (out_f32) k_transpose_bf16<float><<<grid, block, 0, st>>>((const bf16*)a, (float*)c, rows, cols);
+    else k_transpose_bf16<bf16><<<grid, block, 0, st>>>((const bf16*)a, (bf16*)c, rows, cols);
+    return 0;
+}
+
 // ── [d0,d1,d2,d3] -> [d0,d2,d1,d3] ─────────────────────────────────────────
 // One thread moves one 16-byte piece of a d3-row when d3 allows, else one element.
 template <typename T, int W>

@@ -11,6 +11,7 @@ int ax_binary(int which, int dt, const void* a, const void* b, void* c, long lon
 int ax_scale(int dt, const void* a, void* c, float alpha, long long n, cudaStream_t st);
 int ax_copy(int dt, const void* a, void* c, long long n, cudaStream_t st);
 int ax_cast(int to_f32, const void* a, void* c, long long n, cudaStream_t st);
+int ax_transpose_bf16(int out_f32, const void* a, void* c, int rows, int cols, cudaStream_t st);
 int ax_perm0213(int dt, const void* a, void* c, int d0, int d1, int d2, int d3, cudaStream_t st);
 int ax_rope(int dt, const void* x, const float* cs, const float* sn, void* o, int T, int dh,
             long long rows, int heads_inner, int inverse, cudaStream_t st);

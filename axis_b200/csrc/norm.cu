@@ -75,6 +75,51 @@ k_rmsnorm_warp(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
     }
 }
 
+// ── wide rows: WPR warps share a row ───────────────────────────────────────
+// Rows too wide for one warp's registers (the 7B-class width 4096 is 16 vectors per lane in bf16) are cut
+// into WPR column spans, one warp each; the WPR warps of a row exchange their partial sums through shared
+// memory around a named barrier of their own (two slots used alternately, so one barrier per row suffices).
+// Blocks have 8 warps = 8 / WPR rows in flight.
+__device__ __forceinline__ void row_bar(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+template <typename T, int VPL, int WPR>
+__global__ void __launch_bounds__(256)
+k_rmsnorm_wide(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ o, int rows, float eps) {
+    constexpr int N = Vec<T>::N, SPAN = 32 * VPL * N, DIM = SPAN * WPR, G = 8 / WPR;
+    __shared__ float red[2][G][WPR];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, grp = wib / WPR, part = wib % WPR;
+    int it = 0;
+    for (int r = blockIdx.x * G + grp; r < rows; r += gridDim.x * G, it ^= 1) {
+        const T* xr = x + (long long)r * DIM + part * SPAN;
+        float xv[VPL][N];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            Vec<T>::ld(xr + (lane + 32 * i) * N, xv[i]);
+#pragma unroll
+            for (int q = 0; q < N; q++) ss += xv[i][q] * xv[i][q];
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[it][grp][part] = ss;
+        row_bar(1 + grp, WPR * 32);
+        float tot = 0.f;
+#pragma unroll
+        for (int q = 0; q < WPR; q++) tot += red[it][grp][q];
+        const float inv = rsqrtf(tot / DIM + eps);
+        T* orow = o + (long long)r * DIM + part * SPAN;
+        const T* wr = w + part * SPAN;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            float wv[N];
+            Vec<T>::ld(wr + (lane + 32 * i) * N, wv);
+#pragma unroll
+            for (int q = 0; q < N; q++) xv[i][q] = xv[i][q] * inv * wv[q];
+            Vec<T>::st(orow + (lane + 32 * i) * N, xv[i]);
+        }
+    }
+}
+
 #define RBW_WARPS 8
 template <typename T, int VPL>
 __global__ void __launch_bounds__(RBW_WARPS * 32)
@@ -215,6 +260,86 @@ k_rmsnorm_bwd_packed(const bf16* __restrict__ x, const bf16* __restrict__ w, con
     }
 }
 
+// The packed backward for wide rows: WPR warps per row (see k_rmsnorm_wide); every warp keeps the dw partial of
+// its own column span in its own shared-memory row, and the block partial adds the rows' groups in fixed order.
+template <int VPL, int WPR>
+__global__ void __launch_bounds__(RBP_WARPS * 32, 2)
+k_rmsnorm_bwd_packed_wide(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ g,
+                          const bf16* res, bf16* dx, float* __restrict__ partial, int rows, float eps) {
+    constexpr int SPAN = 32 * VPL * 8, DIM = SPAN * WPR, G = RBP_WARPS / WPR;
+    extern __shared__ float sdw_all[];                     // [RBP_WARPS][SPAN]
+    __shared__ float red[2][G][WPR][2];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, grp = wib / WPR, part = wib % WPR;
+    float* sdw = sdw_all + wib * SPAN;
+#pragma unroll
+    for (int i = 0; i < VPL; i++) {
+        float4* p = reinterpret_cast<float4*>(sdw + (lane + 32 * i) * 8);
+        p[0] = make_float4(0.f, 0.f, 0.f, 0.f); p[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const bf16* wr = w + part * SPAN;
+    int it = 0;
+    for (int r = blockIdx.x * G + grp; r < rows; r += gridDim.x * G, it ^= 1) {
+        const long long base = (long long)r * DIM + part * SPAN;
+        uint4 xp[VPL], gp[VPL], rp[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            const int c = (lane + 32 * i) * 8;
+            xp[i] = *reinterpret_cast<const uint4*>(x + base + c);
+            gp[i] = *reinterpret_cast<const uint4*>(g + base + c);
+            if (res) rp[i] = *reinterpret_cast<const uint4*>(res + base + c);
+        }
+        float ss = 0.f, gwx = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            float xv[8], gv[8], wv[8];
+            unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(__ldg(reinterpret_cast<const uint4*>(wr + (lane + 32 * i) * 8)), wv);
+#pragma unroll
+            for (int q = 0; q < 8; q++) { ss += xv[q] * xv[q]; gwx += gv[q] * wv[q] * xv[q]; }
+        }
+        ss = warp_sum(ss);
+        gwx = warp_sum(gwx);
+        if (lane == 0) { red[it][grp][part][0] = ss; red[it][grp][part][1] = gwx; }
+        row_bar(1 + grp, WPR * 32);
+        ss = 0.f; gwx = 0.f;
+#pragma unroll
+        for (int q = 0; q < WPR; q++) { ss += red[it][grp][q][0]; gwx += red[it][grp][q][1]; }
+        const float inv = rsqrtf(ss / DIM + eps);
+        const float coef = inv * inv * inv * (gwx / DIM);
+#pragma unroll
+        for (int i = 0; i < VPL; i++) {
+            float xv[8], gv[8], wv[8], ov[8];
+            unpack8(xp[i], xv); unpack8(gp[i], gv); unpack8(__ldg(reinterpret_cast<const uint4*>(wr + (lane + 32 * i) * 8)), wv);
+            if (res) unpack8(rp[i], ov);
+            float4* p = reinterpret_cast<float4*>(sdw + (lane + 32 * i) * 8);
+            float4 a0 = p[0], a1 = p[1];
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float d = gv[q] * wv[q] * inv - xv[q] * coef;
+                ov[q] = res ? ov[q] + d : d;
+            }
+            a0.x += gv[0] * xv[0] * inv; a0.y += gv[1] * xv[1] * inv; a0.z += gv[2] * xv[2] * inv; a0.w += gv[3] * xv[3] * inv;
+            a1.x += gv[4] * xv[4] * inv; a1.y += gv[5] * xv[5] * inv; a1.z += gv[6] * xv[6] * inv; a1.w += gv[7] * xv[7] * inv;
+            p[0] = a0; p[1] = a1;
+            Vec<bf16>::st(dx + base + (lane + 32 * i) * 8, ov);
+        }
+    }
+    if (!partial) return;
+    __syncthreads();
+    for (int j = threadIdx.x; j < DIM; j += blockDim.x) {   // fixed order over the row groups
+        const int pj = j / SPAN, cj = j - pj * SPAN;
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < G; q++) t += sdw_all[(q * WPR + pj) * SPAN + cj];
+        partial[(long long)blockIdx.x * DIM + j] = t;
+    }
+}
+// warps per row (2 or 4, 0 = no wide form) such that a lane holds at most `maxv` 16-byte vectors of its span
+static int wide_wpr(int dim, int per, int maxv) {
+    for (int wpr = 2; wpr <= 4; wpr *= 2)
+        if (dim % (32 * per * wpr) == 0 && dim / (32 * per * wpr) <= maxv) return wpr;
+    return 0;
+}
+
 static int norm_threads(int dim, int per) {
     int t = (dim / per + 31) / 32 * 32;
     if (t < 32) t = 32;
@@ -232,6 +357,16 @@ int ax_rmsnorm(int dt, const void* x, const void* w, void* o, int rows, int dim,
         if (dt == 1) { switch (vpl) { NW(bf16, 1) NW(bf16, 2) NW(bf16, 3) NW(bf16, 4) NW(bf16, 5) NW(bf16, 6) NW(bf16, 7) NW(bf16, 8) } }
         else { switch (vpl) { NW(float, 1) NW(float, 2) NW(float, 3) NW(float, 4) NW(float, 5) NW(float, 6) NW(float, 7) NW(float, 8) } }
 #undef NW
+    }
+    if (const int wpr = vec ? wide_wpr(dim, per, 8) : 0) {
+        const int vpl = dim / (32 * per * wpr), gr = 8 / wpr;
+        const int g = (rows + gr - 1) / gr < AX_SMS * 8 ? (rows + gr - 1) / gr : AX_SMS * 8;
+#define NWW(TT, V, W) case V: k_rmsnorm_wide<TT, V, W><<<g, 256, 0, st>>>((const TT*)x, (const TT*)w, (TT*)o, rows, eps); return 0;
+#define NWS(TT, W) switch (vpl) { NWW(TT, 1, W) NWW(TT, 2, W) NWW(TT, 3, W) NWW(TT, 4, W) NWW(TT, 5, W) NWW(TT, 6, W) NWW(TT, 7, W) NWW(TT, 8, W) }
+        if (dt == 1) { if (wpr == 2) NWS(bf16, 2) else NWS(bf16, 4) }
+        else { if (wpr == 2) NWS(float, 2) else NWS(float, 4) }
+#undef NWS
+#undef NWW
     }
     const int thr = norm_threads(dim, vec ? per : 1);
     const int grid = rows < AX_SMS * 32 ? rows : AX_SMS * 32;
@@ -414,6 +549,21 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
         else { switch (vpl) { BW(float, 1) BW(float, 2) BW(float, 3) BW(float, 4) BW(float, 5) BW(float, 6) } }
 #undef BW
         if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbw, dim);
+        return 0;
+    }
+    // at most 5 vectors per lane: 8 warps x 5 KB of dw rows plus the exchange slots stay inside the 48 KB
+    // that need no opt-in
+    if (const int wpr = (vec && dt == 1) ? wide_wpr(dim, per, 5) : 0) {
+        const int vpl = dim / (32 * per * wpr), gr = RBP_WARPS / wpr;
+        int nbp = (rows + gr - 1) / gr;
+        if (nbp > RB_BLOCKS) nbp = RB_BLOCKS;
+        const size_t sm = (size_t)RBP_WARPS * (dim / wpr) * 4;
+#define BPW(V, W) case V: k_rmsnorm_bwd_packed_wide<V, W><<<nbp, RBP_WARPS * 32, sm, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
+#define BPS(W) switch (vpl) { BPW(1, W) BPW(2, W) BPW(3, W) BPW(4, W) BPW(5, W) }
+        if (wpr == 2) BPS(2) else BPS(4)
+#undef BPS
+#undef BPW
+        if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
         return 0;
     }
     const int thr = norm_threads(dim, vec ? per : 1);

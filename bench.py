@@ -233,10 +233,16 @@ def main():
     ap.add_argument("--impl", default="axis_b200")
     ap.add_argument("--config", default="c3")
     ap.add_argument("--zero", type=int, default=1)
+    ap.add_argument("--recompute", action="store_true",
+                    help="keep one set of activations and re-run each block's forward inside the backward")
+    ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-table", action="store_true")
     args = ap.parse_args()
-    c = CONFIGS[args.config]
+    c = dict(CONFIGS[args.config])
+    if args.batch:
+        c["name"] = c["name"].replace(f"B{c['B']}", f"B{args.batch}")
+        c["B"] = args.batch
     W = max(args.warmup, 3)
     K = max(args.steps, 1)
 
@@ -264,7 +270,8 @@ def main():
         model.apply_lora(rank=c["lora"], alpha=2.0 * c["lora"])
     zero = args.zero if WORLD > 1 else 0
     ct = compile_model(model, batch=c["B"], seq=c["T"], dtype=c["dtype"], lr=c["lr"], max_grad_norm=1.0,
-                       grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD)
+                       grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD,
+                       recompute_blocks=args.recompute)
     del model
     eng = ct.eng
     if WORLD > 1:
@@ -311,7 +318,8 @@ def main():
             "dtype": c["dtype"], "data": "synthetic",
             "config": {"workload": c["name"], "parallelism": f"dp{WORLD}" + ("+zero1" if zero else ""),
                        "l2": "working set per step far exceeds the 126 MB L2 (no flush needed)",
-                       "global_batch": c["B"] * WORLD, "seq_len": c["T"]},
+                       "global_batch": c["B"] * WORLD, "seq_len": c["T"],
+                       "recompute_blocks": bool(args.recompute)},
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 2 * 4 * c["B"] * c["T"],
                     "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches), "clocks": clk, "loss_first": losses[0], "loss_last": losses[-1],

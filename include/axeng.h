@@ -62,6 +62,8 @@ enum EngOpKind {
     ENG_STREAM = 46,          /* tb=1: following ops go to the comm stream, tb=0: main      */
     ENG_SILU_MUL_BWD_RC = 47, /* SwiGLU backward that also rewrites h for recompute-free dW */
     ENG_GEMM_GROUP = 48,      /* 2-3 GEMMs of a layer as one launch: shared input, or one output summed over K-segments */
+    ENG_TRANSPOSE_BF16 = 49,  /* c[n,m] = a[m,n]^T, a bf16; c bf16 (dt=1) or widened to fp32 (dt=0): checkpoint weights
+                                 stored [out,in] in bf16 go to the [in,out] compute / master layout on the device */
     ENG_KIND_COUNT
 };
 

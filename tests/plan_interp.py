@@ -41,6 +41,10 @@ class InterpEngine:
         self.bufs.append(self.bufs[parent][byte_offset:byte_offset + nbytes])
         return len(self.bufs) - 1
 
+    def bytes_allocated(self):
+        """bytes of the allocations (views of an allocation are not counted)"""
+        return sum(b.size for b in self.bufs if b.base is None)
+
     def new_tensor(self, arr):
         i = self.alloc(arr.size)
         self.upload(i, arr)
@@ -251,6 +255,13 @@ class InterpEngine:
             if tb == 0:
                 return self._put(c, self._get(a, cnt, 0), 1)
             return self._put(c, self._get(a, cnt, 1), 0)
+        if kind == E.TRANSPOSE_BF16:
+            src = self.bufs[a].view(np.uint16)[:m * n].reshape(m, n).T
+            if dt == 1:
+                self.bufs[c].view(np.uint16)[:m * n] = src.reshape(-1)
+            else:
+                self.bufs[c].view(np.float32)[:m * n] = E.bf16_bits_to_f32(np.ascontiguousarray(src).reshape(-1))
+            return
         if kind == E.GNORM_FLAT:
             g = self._f32(a, m * E.CHUNK, oa * E.CHUNK)
             if tb > 0:

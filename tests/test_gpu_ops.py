@@ -76,7 +76,10 @@ def test_binary_scale_copy_cast(eng, dt, n):
 
 
 @pytest.mark.parametrize("dt", [0, 1])
-@pytest.mark.parametrize("rows,dim", [(5, 48), (33, 256), (8, 1536), (3, 100)])
+@pytest.mark.parametrize("rows,dim", [(5, 48), (33, 256), (8, 1536), (3, 100),
+                                      # wide rows (several warps per row); row counts that leave ragged last
+                                      # groups and make blocks loop (more rows than one wave holds)
+                                      (37, 2048), (9, 3072), (700, 4096), (2500, 4096), (11, 5120)])
 def test_rmsnorm_fwd_bwd(eng, dt, rows, dim):
     rng = np.random.default_rng(rows * dim)
     x, w, g, res = rnd(rng, (rows, dim), dt), rnd(rng, dim, dt), rnd(rng, (rows, dim), dt), rnd(rng, (rows, dim), dt)

@@ -240,3 +240,57 @@ def test_gradient_accumulation_equals_the_concatenated_batch(dtype):
         assert np.abs(w[nm] - model.w[nm]).max() <= tol, nm
     assert ct.eng.device_status() == 0
     ct.eng.shutdown()
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("lora", [0, 8])
+def test_block_recompute_equals_the_plain_step(dtype, lora):
+    """recompute_blocks keeps one set of activations and re-runs each block's forward inside the backward
+    (the eager engine's ops.checkpoint, axis/ops.py:440-475).  The recomputed activations are bit-identical,
+    so in fp32 (ordered reductions everywhere) losses, gradients and weights are equal bit for bit under
+    graph replay; in bf16 the tensor-core attention adds its dQ pieces in no fixed order, so the two plans
+    differ like two runs of the same plan and both stay inside the bf16 bar against the oracle."""
+    cfg = dict(vocab_size=512, dim=256, n_layers=3, n_heads=4, n_kv_heads=2, mlp_hidden=384, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=2)
+    rng = np.random.default_rng(2)
+    kw = dict(lora_r=lora, lora_alpha=16.0) if lora else {}
+    batches = [O.make_batch(rng, 512, 2, 256, 0.05) for _ in range(4)]
+    lora_b = {}
+
+    def run(recompute):         # one engine per process: the two plans run one after the other
+        ct = build(cfg, w0, 2, 256, dtype=dtype, max_grad_norm=1.0, recompute_blocks=recompute, **kw)
+        assert ct.recompute_blocks == recompute
+        if lora:    # adapters start at zero on the B side: give them values so every gradient is live
+            st = ct.state_dict()
+            for k in st:
+                if k.startswith("w/") and k.endswith("lora_b"):
+                    lora_b.setdefault(k, (0.02 * rng.standard_normal(st[k].shape)).astype(np.float32))
+                    st[k] = lora_b[k]
+            ct.load_state_dict(st)
+        l0 = ct.forward_backward(*batches[0])
+        g = ct.grads()
+        ct.capture()
+        ls = [ct.replay_step(*b) for b in batches[1:]]
+        assert ct.eng.device_status() == 0
+        return l0, g, ls, ct.get_weights()
+
+    la, ga, lsa, wa = run(False)
+    lb, gb, lsb, wb = run(True)
+    assert la == lb                         # the forward is the same plan
+    for nm in ga:
+        if dtype == "fp32":
+            assert np.array_equal(ga[nm], gb[nm]), nm
+        else:
+            assert rel(gb[nm], ga[nm]) <= 5e-3, nm
+    if not lora:
+        l_ref, g_ref = O.OracleTransformer(cfg, w0).loss_and_grads(*batches[0])
+        tol = 1e-5 if dtype == "fp32" else 2e-2
+        worst = max((rel(gb[nm], g_ref[nm]), nm) for nm in g_ref)
+        assert worst[0] <= tol, worst
+    for s, (x1, x2) in enumerate(zip(lsa, lsb)):
+        assert abs(x1 - x2) <= (0 if dtype == "fp32" else 2e-4 * abs(x1)), (s, x1, x2)
+    for nm in wa:
+        if dtype == "fp32":
+            assert np.array_equal(wa[nm], wb[nm]), nm
+        else:
+            assert np.abs(wa[nm] - wb[nm]).max() <= 4.5 * 3e-4, nm

@@ -176,3 +176,43 @@ def test_gradient_accumulation_equals_the_concatenated_batch():
     loss2 = ct.step_accumulate(list(zip(xs[::-1], ys[::-1])))
     l2 = O.train_step(model, opt, np.concatenate(xs[::-1]), np.concatenate(ys[::-1]), max_grad_norm=1.0)[0]
     assert abs(loss2 - l2) <= 5e-6 * abs(l2)
+
+
+@pytest.mark.parametrize("name,dtype", [("step_tied_gqa", "fp32"), ("step_lora", "fp32"), ("step_untied_mha", "bf16")])
+def test_block_recompute_reproduces_the_plain_plan_bit_for_bit(name, dtype):
+    """Keeping only each block's input and re-running the block's forward inside the backward (the eager
+    engine's ops.checkpoint, axis/ops.py:440-475) gives the same losses, gradients and weights, bit for
+    bit, and still matches the reference's golden step."""
+    z, cfg, w0 = load(name)
+    a = build(cfg, w0, dtype=dtype)
+    b = build(cfg, w0, dtype=dtype, recompute_blocks=True)
+    assert b.recompute_blocks and not a.recompute_blocks
+    L = cfg["n_layers"]
+    from axis_b200.engine import ATTN_FWD, ATTN_BWD
+    kinds = lambda ct: [int(o[0]) for o in ct.plan_fb]
+    assert kinds(a).count(ATTN_FWD) == L and kinds(b).count(ATTN_FWD) == 2 * L - 1
+    assert kinds(a).count(ATTN_BWD) == kinds(b).count(ATTN_BWD) == L
+    for s in range(2):
+        la = a.step(z[f"x/{s}"], z[f"y/{s}"])
+        lb = b.step(z[f"x/{s}"], z[f"y/{s}"])
+        assert la == lb
+        if dtype == "fp32":
+            assert abs(lb - z["losses"][s]) <= 2e-6 * max(1, abs(z["losses"][s]))
+        ga, gb = a.grads(), b.grads()
+        for nm in ga:
+            assert np.array_equal(ga[nm], gb[nm]), nm
+    wa, wb = a.get_weights(), b.get_weights()
+    for nm in wa:
+        assert np.array_equal(wa[nm], wb[nm]), nm
+
+
+def test_block_recompute_keeps_one_set_of_activations():
+    """Device bytes of the activations: L sets without recompute, one set (plus a block input per layer) with."""
+    cfg = dict(vocab_size=61, dim=32, n_layers=6, n_heads=4, n_kv_heads=2, mlp_hidden=48, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=1)
+    e0, e1 = InterpEngine(), InterpEngine()
+    CompiledTransformer(e0, cfg, w0, 2, 16, dtype="bf16")
+    CompiledTransformer(e1, cfg, w0, 2, 16, dtype="bf16", recompute_blocks=True)
+    N, D, MLP, H, KV, DH, L = 32, 32, 48, 4, 2, 8, 6
+    per_block = 2 * (N * D * 5 + N * KV * DH * 2 + N * MLP * 3) + 4 * 2 * H * 16      # all but the block input
+    assert e0.bytes_allocated() - e1.bytes_allocated() == (L - 1) * per_block
