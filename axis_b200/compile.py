@@ -575,6 +575,22 @@ class CompiledTransformer:
         self.eng.replay(1, sync=False)
         return float(self.eng.download(self.b_loss, (1,))[0])
 
+    def replay_step_async(self, tokens: np.ndarray, targets: np.ndarray):
+        """Launch one captured step and return the loss of the step launched BEFORE it (None on the first
+        call): the host never waits for the step it has just queued, so batch preparation for step i+1
+        overlaps step i on the GPU.  Token conversion goes through the engine's pinned ring and the loss
+        comes back through a pinned read-back ring.  `flush()` collects the last loss."""
+        self._feed(tokens, targets)
+        self.eng.replay(1, sync=False)
+        tk = self.eng.download_async(self.b_loss, 1)
+        prev, self._pending_loss = getattr(self, "_pending_loss", None), tk
+        return None if prev is None else float(self.eng.download_wait(prev, 1)[0])
+
+    def flush(self):
+        """Loss of the last step queued with replay_step_async (None if there is none); waits for it."""
+        prev, self._pending_loss = getattr(self, "_pending_loss", None), None
+        return None if prev is None else float(self.eng.download_wait(prev, 1)[0])
+
     def step_accumulate(self, batches) -> float:
         """One optimizer step over several micro-batches of the compiled shape (gradient accumulation).
 

@@ -19,6 +19,8 @@
 #define API extern "C" __attribute__((visibility("default")))
 #define MAX_BUFS 65536
 #define STAGE_SLOTS 4
+#define RING_SLOTS 8
+#define RING_FLOATS 64
 
 struct Buf { void* p; long long bytes; bool owned; };
 
@@ -45,6 +47,10 @@ struct Engine {
     long long stage_cap[STAGE_SLOTS] = {0};
     cudaEvent_t stage_ev[STAGE_SLOTS] = {nullptr};
     int stage_next = 0;
+    float* ring = nullptr;                      // pinned read-back ring: RING_SLOTS x RING_FLOATS
+    cudaEvent_t ring_ev[RING_SLOTS] = {nullptr};
+    int ring_ticket[RING_SLOTS];
+    int ring_next = 0;
     char err[512] = {0};
     int last_op_rc = 0;
 };
@@ -71,6 +77,12 @@ static void release_all() {
         if (G.stage_ev[i]) cudaEventDestroy(G.stage_ev[i]);
         G.stage[i] = nullptr; G.stage_cap[i] = 0; G.stage_ev[i] = nullptr;
     }
+    if (G.ring) { cudaFreeHost(G.ring); G.ring = nullptr; }
+    for (int i = 0; i < RING_SLOTS; i++) {
+        if (G.ring_ev[i]) cudaEventDestroy(G.ring_ev[i]);
+        G.ring_ev[i] = nullptr; G.ring_ticket[i] = -1;
+    }
+    G.ring_next = 0;
     if (G.d_status) { cudaFree(G.d_status); G.d_status = nullptr; }
     if (G.l2_flush) { cudaFree(G.l2_flush); G.l2_flush = nullptr; }
     if (G.comm) { ncclCommDestroy(G.comm); G.comm = nullptr; }
@@ -193,6 +205,33 @@ API int eng_upload_tokens(int idx, const long long* host, long long n, long long
     int rc = (int)cudaMemcpyAsync(G.bufs[idx].p, dst, (size_t)n * 4, cudaMemcpyHostToDevice, G.stream);
     cudaEventRecord(G.stage_ev[s], G.stream);
     return rc;
+}
+API int eng_download_async(int idx, long long nfloats) {
+    if (nfloats < 1 || nfloats > RING_FLOATS || !have(idx, nfloats * 4)) { set_err("download_async: buffer %d missing or count %lld outside 1..%d", idx, nfloats, RING_FLOATS); return -110; }
+    if (!G.ring) {
+        if (cudaMallocHost(&G.ring, sizeof(float) * RING_SLOTS * RING_FLOATS)) { G.ring = nullptr; set_err("pinned alloc failed"); return -2; }
+        for (int i = 0; i < RING_SLOTS; i++) G.ring_ticket[i] = -1;
+    }
+    const int ticket = G.ring_next;
+    const int s = ticket % RING_SLOTS;
+    G.ring_next = ticket == 0x3fffffff ? 0 : ticket + 1;
+    if (!G.ring_ev[s]) {
+        if (cudaEventCreateWithFlags(&G.ring_ev[s], cudaEventDisableTiming)) { G.ring_ev[s] = nullptr; set_err("event create failed"); return -5; }
+    } else if (G.ring_ticket[s] >= 0) {
+        cudaEventSynchronize(G.ring_ev[s]);       // an uncollected copy into this slot: let it land before the slot is rewritten
+    }
+    if (cudaMemcpyAsync(G.ring + s * RING_FLOATS, G.bufs[idx].p, nfloats * 4, cudaMemcpyDeviceToHost, G.stream)) { set_err("download_async: copy failed"); return -1; }
+    cudaEventRecord(G.ring_ev[s], G.stream);
+    G.ring_ticket[s] = ticket;
+    return ticket;
+}
+API int eng_download_wait(int ticket, float* host, long long nfloats) {
+    const int s = ticket >= 0 ? ticket % RING_SLOTS : 0;
+    if (ticket < 0 || !G.ring || G.ring_ticket[s] != ticket || nfloats < 1 || nfloats > RING_FLOATS) { set_err("download_wait: ticket %d is not pending", ticket); return 4; }
+    if (cudaEventSynchronize(G.ring_ev[s])) { set_err("download_wait: %s", cudaGetErrorString(cudaGetLastError())); return 1; }
+    memcpy(host, G.ring + s * RING_FLOATS, nfloats * 4);
+    G.ring_ticket[s] = -1;
+    return 0;
 }
 API int eng_device_status(int clear) {
     int v[16];

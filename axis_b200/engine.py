@@ -150,6 +150,8 @@ class Engine:
         L.eng_upload_raw.argtypes = [c_i, c_ll, c_p, c_ll]
         L.eng_download_raw.argtypes = [c_i, c_ll, c_p, c_ll]
         L.eng_upload_tokens.argtypes = [c_i, c_p, c_ll, c_ll]
+        L.eng_download_async.argtypes = [c_i, c_ll]
+        L.eng_download_wait.argtypes = [c_i, c_p, c_ll]
         L.eng_last_error.restype = ctypes.c_char_p
         L.eng_time_plan.argtypes = [ctypes.POINTER(_EngOp), c_i, c_i, c_i, ctypes.POINTER(ctypes.c_float)]
         L.eng_profile_read.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(c_i), c_i]
@@ -207,6 +209,18 @@ class Engine:
     def download_raw(self, idx: int, shape, dtype, byte_offset: int = 0) -> np.ndarray:
         out = np.empty(shape, dtype=dtype)
         self._check(self.lib.eng_download_raw(idx, int(byte_offset), out.ctypes.data, out.nbytes), "download_raw")
+        return out
+
+    def download_async(self, idx: int, nfloats: int = 1) -> int:
+        """Queue a read-back of `nfloats` floats behind the queued work; returns a ticket for download_wait."""
+        tk = self.lib.eng_download_async(idx, int(nfloats))
+        if tk < 0:
+            raise RuntimeError(f"download_async failed rc={tk}: {self.last_error()}")
+        return tk
+
+    def download_wait(self, ticket: int, nfloats: int = 1) -> np.ndarray:
+        out = np.empty(int(nfloats), dtype=np.float32)
+        self._check(self.lib.eng_download_wait(int(ticket), out.ctypes.data, int(nfloats)), "download_wait")
         return out
 
     def upload_bf16(self, idx: int, arr: np.ndarray) -> None:

@@ -7,7 +7,8 @@ One JSON line on stdout (rank 0).  `value` is tokens/s of the whole job with the
 batch already on the device (CUDA-graph replays between two CUDA events, max
 over ranks); `e2e` is the same metric through the public API with host arrays
 (`ct.replay_step(x, y)`: pinned H2D of ids/targets and the D2H loss read every
-step).  N > 1 (launched by torchrun): data parallel + ZeRO-1, one process per
+step; `e2e.pipelined_value` is the same loop with `ct.replay_step_async`, which
+reads step i's loss after step i+1 is queued).  N > 1 (launched by torchrun): data parallel + ZeRO-1, one process per
 GPU, weak scaling (fixed per-GPU batch).  `--impl reference` times the numpy
 restatement of the reference's step on the host cores (the only place besides
 `cpu_baseline` where this file runs anything from oracle/).
@@ -307,6 +308,13 @@ def main():
         losses.append(ct.replay_step(*batches[i % 4]))
     eng.sync()
     e2e_s = reduce_max(time.perf_counter() - t0)
+    # the same with the loss of step i read after step i+1 is queued (pinned read-back ring)
+    eng.sync(); barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        ct.replay_step_async(*batches[i % 4])
+    losses.append(ct.flush())
+    e2e_async_s = reduce_max(time.perf_counter() - t0)
     clk = clocks.stop()
 
     tokens = c["B"] * c["T"] * WORLD
@@ -321,7 +329,7 @@ def main():
                        "global_batch": c["B"] * WORLD, "seq_len": c["T"],
                        "recompute_blocks": bool(args.recompute)},
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 2 * 4 * c["B"] * c["T"],
-                    "d2h_bytes_per_step": 4},
+                    "d2h_bytes_per_step": 4, "pipelined_value": tokens * K / e2e_async_s},
             "gpu_launches": int(launches), "clocks": clk, "loss_first": losses[0], "loss_last": losses[-1],
             "step_tflops": step_flops(c) * K / (ms_dev / 1e3) / 1e12 / 1.0,
             "device_status": eng.device_status()}

@@ -121,6 +121,13 @@ int eng_download_raw(int idx, long long byte_offset, void* host, long long nbyte
 /* int64 tokens -> device int32 (values are range-checked against `limit`:
  * a token >= limit or < -1 returns 3).  */
 int eng_upload_tokens(int idx, const long long* host, long long n, long long limit);
+/* Read-back that does not stall the host: eng_download_async queues a copy of nfloats (<= 64) floats of buffer
+ * idx into a pinned slot behind the work queued so far and returns a ticket (>= 0; negative = failure);
+ * eng_download_wait blocks until that copy has landed and hands it out (4 = the ticket is unknown or older
+ * than the 8 slots of the ring).  A host loop that reads step i's loss after launching step i+1 keeps the GPU
+ * queue non-empty while it prepares the next batch. */
+int eng_download_async(int idx, long long nfloats);
+int eng_download_wait(int ticket, float* host, long long nfloats);
 /* Release every buffer, graph, communicator and stream. */
 int eng_shutdown(void);
 /* Text of the last failure (static storage). */

@@ -83,6 +83,20 @@ class InterpEngine:
         n = int(np.prod(shape)) * np.dtype(dtype).itemsize
         return self.bufs[i][byte_offset:byte_offset + n].view(dtype).reshape(shape).copy()
 
+    def download_async(self, i, nfloats=1):
+        if not hasattr(self, "_tickets"):
+            self._tickets, self._tk = {}, 0
+        self._tk += 1
+        self._tickets[self._tk] = self.bufs[i].view(np.float32)[:nfloats].copy()
+        for old in [t for t in self._tickets if t <= self._tk - 8]:
+            del self._tickets[old]
+        return self._tk
+
+    def download_wait(self, ticket, nfloats=1):
+        if ticket not in getattr(self, "_tickets", {}):
+            raise RuntimeError("download_wait failed rc=4")
+        return self._tickets.pop(ticket)[:nfloats]
+
     def upload_tokens(self, i, tokens, limit):
         t = np.asarray(tokens, dtype=np.int64).reshape(-1)
         if (t >= limit).any() or (t < -1).any():

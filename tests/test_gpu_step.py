@@ -294,3 +294,33 @@ def test_block_recompute_equals_the_plain_step(dtype, lora):
             assert np.array_equal(wa[nm], wb[nm]), nm
         else:
             assert np.abs(wa[nm] - wb[nm]).max() <= 4.5 * 3e-4, nm
+
+
+def test_async_replay_pipeline_matches_the_blocking_steps():
+    """replay_step_async returns step i's loss when step i+1 is queued (pinned read-back ring, no host stall on
+    the step just launched); the loss sequence and the final weights equal those of replay_step, bit for bit
+    (fp32: ordered reductions everywhere)."""
+    z, cfg, w0 = load("step_tied_gqa")
+    rng = np.random.default_rng(11)
+    xs = [O.make_batch(rng, cfg["vocab_size"], cfg["B"], cfg["T"], 0.1) for _ in range(12)]   # more steps than ring slots
+
+    def run(pipelined):
+        ct = build(cfg, w0, cfg["B"], cfg["T"], max_grad_norm=1.0)
+        ct.capture()
+        if pipelined:
+            out = [ct.replay_step_async(x, y) for x, y in xs]
+            assert out[0] is None
+            out = out[1:] + [ct.flush()]
+            assert ct.flush() is None
+            with pytest.raises(RuntimeError):
+                ct.eng.download_wait(3)                 # collected long ago
+        else:
+            out = [ct.replay_step(x, y) for x, y in xs]
+        assert ct.eng.device_status() == 0
+        return out, ct.get_weights()
+
+    la, wa = run(False)
+    lb, wb = run(True)
+    assert la == lb
+    for nm in wa:
+        assert np.array_equal(wa[nm], wb[nm]), nm

@@ -216,3 +216,18 @@ def test_block_recompute_keeps_one_set_of_activations():
     N, D, MLP, H, KV, DH, L = 32, 32, 48, 4, 2, 8, 6
     per_block = 2 * (N * D * 5 + N * KV * DH * 2 + N * MLP * 3) + 4 * 2 * H * 16      # all but the block input
     assert e0.bytes_allocated() - e1.bytes_allocated() == (L - 1) * per_block
+
+
+def test_async_replay_returns_the_previous_loss():
+    """replay_step_async hands out step i's loss when step i+1 is queued; the sequence equals replay_step's."""
+    z, cfg, w0 = load("step_tied_gqa")
+    a, b = build(cfg, w0), build(cfg, w0)
+    a.capture(); b.capture()
+    xs = [(z[f"x/{s % cfg['steps']}"], z[f"y/{s % cfg['steps']}"]) for s in range(4)]
+    want = [a.replay_step(x, y) for x, y in xs]
+    got = [b.replay_step_async(x, y) for x, y in xs]
+    assert got[0] is None and got[1:] == want[:-1]
+    assert b.flush() == want[-1] and b.flush() is None
+    assert b.replay_step_async(*xs[0]) is None          # after a flush the pipeline starts empty again
+    with pytest.raises(RuntimeError):
+        b.eng.download_wait(12345)
