@@ -20,6 +20,10 @@ state_dict / load_state_dict`).  What differs is the plan it emits:
   side stream while backward continues (axis/compile.py:490-496 all-reduces
   per tensor after backward); ZeRO-1 keeps the reference's per-tensor greedy
   owner map (axis/compile.py:128-139) bit for bit.
+
+Additions to the reference's surface: `recompute_blocks` (per-block activation recompute),
+`step_accumulate` (gradient accumulation), `replay_step_async` / `flush` (the host reads step i's loss after
+step i+1 is queued), and weights given as checkpoint tensors still in their file layout (see pretrained.py).
 """
 from __future__ import annotations
 
@@ -534,6 +538,7 @@ class CompiledTransformer:
         self.plan_step = self._plan_fb_sync + opt_ops(max_grad_norm)
         self._plan_noclip = None
         self._captured = False
+        self._pending_loss = None            # read-back ticket of the last replay_step_async
 
     # ── API (axis/compile.py:547-615) ──
     def set_lr(self, lr: float) -> None:
@@ -583,12 +588,12 @@ class CompiledTransformer:
         self._feed(tokens, targets)
         self.eng.replay(1, sync=False)
         tk = self.eng.download_async(self.b_loss, 1)
-        prev, self._pending_loss = getattr(self, "_pending_loss", None), tk
+        prev, self._pending_loss = self._pending_loss, tk
         return None if prev is None else float(self.eng.download_wait(prev, 1)[0])
 
     def flush(self):
         """Loss of the last step queued with replay_step_async (None if there is none); waits for it."""
-        prev, self._pending_loss = getattr(self, "_pending_loss", None), None
+        prev, self._pending_loss = self._pending_loss, None
         return None if prev is None else float(self.eng.download_wait(prev, 1)[0])
 
     def step_accumulate(self, batches) -> float:
