@@ -24,7 +24,7 @@ def _data(rank, step):
     return x, np.roll(x, -1, axis=1)
 
 
-def _worker(rank, world, port, zero, dtype, out):
+def _worker(rank, world, port, zero, dtype, recompute, out):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     from axis_b200.compile import CompiledTransformer
@@ -34,7 +34,7 @@ def _worker(rank, world, port, zero, dtype, out):
     w0 = O.init_weights(CFG, seed=3)
     ct = CompiledTransformer(InterpEngine(dist), CFG, w0, B, T, dtype=dtype, grad_sync=True,
                              zero_stage=1 if zero else 0, rank=rank, world=world, max_grad_norm=1.0,
-                             bucket_layers=2)
+                             bucket_layers=2, recompute_blocks=recompute)
     losses = []
     for s in range(STEPS):
         losses.append(ct.step(*_data(rank, s)))
@@ -47,18 +47,19 @@ def _worker(rank, world, port, zero, dtype, out):
     dist.destroy_process_group()
 
 
-def _run(world, zero, dtype):
+def _run(world, zero, dtype, recompute=False):
     import torch.multiprocessing as mp
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, port, zero, dtype, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, zero, dtype, recompute, out), nprocs=world, join=True)
     return [out[r] for r in range(world)]
 
 
 @pytest.fixture(scope="module")
 def runs():
-    return {"dp32": _run(2, False, "fp32"), "dp16": _run(2, False, "bf16"), "z16": _run(2, True, "bf16")}
+    return {"dp32": _run(2, False, "fp32"), "dp16": _run(2, False, "bf16"), "z16": _run(2, True, "bf16"),
+            "z16rc": _run(2, True, "bf16", recompute=True)}
 
 
 def test_dp_matches_single_process_on_concatenated_batch(runs):
@@ -119,3 +120,18 @@ def test_reduction_is_bucketed_inside_backward(runs):
     gemm_after_first_reduce = [i for i, k in enumerate(first) if k == E.GEMM_SB and i > red[0]]
     assert len(red) >= 3 and gemm_after_first_reduce, "reductions must be interleaved with backward GEMMs"
     assert first.count(E.FORK) == first.count(E.STREAM) // 2 and first[-1] == E.JOIN
+
+
+def test_zero1_with_block_recompute_equals_zero1_bit_for_bit(runs):
+    """Per-block recompute re-runs forward ops inside the backward; the bucket boundaries of the overlapped
+    reduction move with them and the result does not change."""
+    from axis_b200 import engine as E
+    z, rc = runs["z16"], runs["z16rc"]
+    for r in range(2):
+        assert rc[r]["losses"] == z[r]["losses"] and rc[r]["owned"] == z[r]["owned"]
+        for nm, w in z[r]["w"].items():
+            assert np.array_equal(w, rc[r]["w"][nm]), nm
+        assert np.array_equal(z[r]["mirror"], rc[r]["mirror"])
+        step0 = lambda tr: tr[:tr.index(E.GNORM_FLAT)]
+        assert step0(rc[r]["trace"]).count(E.REDUCE) == step0(z[r]["trace"]).count(E.REDUCE)
+        assert step0(rc[r]["trace"]).count(E.ATTN_FWD) == 2 * CFG["n_layers"] - 1
