@@ -32,7 +32,7 @@ from typing import Dict, List, Sequence
 import numpy as np
 
 from axis_b200.engine import (
-    ADAMW_FLAT, ADD, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, COPY, EMBED_BWD_DET,
+    ADAMW_FLAT, ADD, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, COLSUM_BATCH, COPY, EMBED_BWD_DET,
     EMBED_I32, FORK, GEMM_EX, GEMM_GROUP, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
     ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, Engine, f32_to_bf16_bits, op)
 
@@ -279,7 +279,13 @@ class CompiledTransformer:
         npart = max(1, (max(s[1] for s in self._seg) + 8191) // 8192)
         self.b_partials = A(npart)
         self.b_ce_scratch = A(N + 8)
-        self.b_rb_scratch = A(RB_BLOCKS * D)
+        # RMSNorm backward leaves its per-block dw partials in one zeroed scratch area per norm; a batched column
+        # sum per reduction bucket turns them into the weight gradients (one launch instead of one per norm)
+        n_norms = 0 if lora else 2 * L + 1
+        self.b_rb_scratch = eng.alloc_zero(max(n_norms, 1) * RB_BLOCKS * D * 4)
+        self.b_rb_table = A(max(n_norms, 1))
+        rb_names: List[str] = []             # norm weights in the order of their backward launches
+        rb_pending: List[int] = []
 
         # ── saved activations ──
         # With recompute_blocks only the input of every block is kept (N*D per layer); the other
@@ -405,8 +411,22 @@ class CompiledTransformer:
 
         def norm_b(x, wname, g, res, out):
             """out = res + rmsnorm_bwd(x, w, g); dw -> G[wname] unless frozen"""
+            if lora:
+                return [op(RMSNORM_BWD_ACC, a=x, b=P[wname], d=g, c=out, tb=(res if res >= 0 else 0), sa=0,
+                           sb=self.b_rb_scratch, m=N, n=D, dt=DT, alpha=eps)]
+            rb_pending.append(len(rb_names))
+            rb_names.append(wname)
             return [op(RMSNORM_BWD_ACC, a=x, b=P[wname], d=g, c=out, tb=(res if res >= 0 else 0),
-                       sa=(0 if lora else G[wname]), sb=self.b_rb_scratch, m=N, n=D, dt=DT, alpha=eps)]
+                       sa=G[wname], sb=self.b_rb_scratch, oa=len(rb_names), m=N, n=D, dt=DT, alpha=eps)]
+
+        def flush_dw():
+            """weight gradients of the norms whose backward ran since the last flush"""
+            if not rb_pending:
+                return []
+            o_ = [op(COLSUM_BATCH, a=self.b_rb_scratch, b=self.b_rb_table, c=self.a_grad, m=len(rb_pending), n=D,
+                     oa=rb_pending[0], k=CHUNK)]
+            rb_pending.clear()
+            return o_
 
         # ── forward ──
         def block_f(i, down=True):
@@ -460,6 +480,7 @@ class CompiledTransformer:
             if not lora:
                 plan += [op(GEMM_SB, a=xf, b=dlogits, c=G["lm_head.weight"], m=D, n=V, k=N, batch=1, tb=2, dt=DTW)]
         plan += norm_b(xs[L], "norm.weight", dxf, -1, dcur)
+        plan += flush_dw()
         marks = {0: len(plan)}
         for i in reversed(range(L)):
             p = f"blocks.{i}."
@@ -479,13 +500,17 @@ class CompiledTransformer:
             plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
             if (L - 1 - i) % bucket_layers == bucket_layers - 1 and i > 0:
+                plan += flush_dw()
                 marks[1 + (L - 1 - i) // bucket_layers] = len(plan)
         if not lora:
             if not tied:
                 plan += [op(SCALE, a=G["embed.weight"], c=G["embed.weight"], n=V * D, alpha=0.0)]
             plan += [op(EMBED_BWD_DET, a=dcur, b=self.b_ids, c=G["embed.weight"], m=N, n=D, dt=DT)]
+        plan += flush_dw()
         marks[nb - 1] = len(plan)
         self.plan_fb = plan
+        if rb_names:
+            eng.upload_raw(self.b_rb_table, np.array([self._off[nm] // CHUNK for nm in rb_names], dtype=np.int32))
 
         # ── gradient reduction: bucketed, on the side stream, overlapped with backward ──
         def comm_ops(b):

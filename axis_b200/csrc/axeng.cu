@@ -537,16 +537,30 @@ static int exec_op(const EngOp* op) {
         }
         case ENG_RMSNORM_BWD_ACC: {
             // a=x b=w d=g c=dx; tb=residual (<=0 none); sa=dw fp32 (<=0 none); sb=scratch; m=N n=D; alpha=eps
+            // oa=j>0: deferred dw -- the partials stay in area j-1 of the scratch for a later COLSUM_BATCH
             const long long el = (long long)op->m * op->n;
             NEED(op->a, el * es); NEED(op->b, op->n * es); NEED(op->d, el * es); NEED(op->c, el * es);
             const void* res = nullptr; float* dw = nullptr; float* scr = nullptr;
             if (op->tb > 0) { NEED(op->tb, el * es); res = BUFP(op->tb); }
+            const int defer = op->oa > 0;
             if (op->sa > 0) {
+                const long long area = ax_rmsnorm_bwd_acc_scratch(op->n);
                 NEED(op->sa, (long long)op->n * 4); dw = (float*)BUFP(op->sa);
-                NEED(op->sb, ax_rmsnorm_bwd_acc_scratch(op->n)); scr = (float*)BUFP(op->sb);
+                NEED(op->sb, area * (defer ? op->oa : 1)); scr = (float*)((char*)BUFP(op->sb) + (defer ? area * (op->oa - 1) : 0));
             }
-            G.launches += dw ? 2 : 1;
-            return ax_rmsnorm_bwd_acc(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), res, BUFP(op->c), dw, scr, op->m, op->n, op->alpha, st);
+            G.launches += (dw && !defer) ? 2 : 1;
+            return ax_rmsnorm_bwd_acc(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), res, BUFP(op->c), dw, scr, op->m, op->n, op->alpha, st,
+                                      dw ? defer : 0);
+        }
+        case ENG_COLSUM_BATCH: {
+            // a=scratch areas, b=int32 table of destination offsets (in units of k elements), c=fp32 arena;
+            // m=count, n=D, oa=first area, k=unit
+            if (op->m <= 0 || op->n <= 0 || op->oa < 0 || op->k <= 0) { set_err("colsum_batch: bad shape"); return 112; }
+            NEED(op->a, ax_rmsnorm_bwd_acc_scratch(op->n) * (op->oa + op->m)); NEED(op->b, (long long)(op->oa + op->m) * 4);
+            NEED(op->c, 4);
+            G.launches++;
+            return ax_colsum_batch((const float*)BUFP(op->a), (float*)BUFP(op->c), (const int*)BUFP(op->b), op->oa, op->m, op->n, op->k,
+                                   (long long)(G.bufs[op->c].bytes / 4), G.d_status, st);
         }
         case ENG_SILU_BWD: {
             const long long n = op->n;

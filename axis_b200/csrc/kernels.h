@@ -32,7 +32,10 @@ int ax_colsum(int dt, const void* a, float* c, int rows, int n, cudaStream_t st)
 // scratch: >= ax_rmsnorm_bwd_acc_scratch(dim) bytes.
 long long ax_rmsnorm_bwd_acc_scratch(int dim);
 int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, const void* res, void* dx,
-                       float* dw, float* scratch, int rows, int dim, float eps, cudaStream_t st);
+                       float* dw, float* scratch, int rows, int dim, float eps, cudaStream_t st, int defer = 0);
+// Sums the partials that `count` deferred launches left in consecutive scratch areas (see norm.cu).
+int ax_colsum_batch(const float* scratch, float* arena, const int* table, int first, int count, int dim, int chunk,
+                    long long arena_elems, int* status, cudaStream_t st);
 
 // loss.cu
 int ax_embed(int dt, const void* table, const void* ids, int ids_i32, void* o, int N, int D, cudaStream_t st);

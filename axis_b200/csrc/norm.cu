@@ -524,13 +524,15 @@ __global__ void k_colsum_partials(const float* __restrict__ partial, float* __re
 }
 long long ax_rmsnorm_bwd_acc_scratch(int dim) { return (long long)RB_BLOCKS * dim * sizeof(float); }
 int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, const void* res, void* dx,
-                       float* dw, float* scratch, int rows, int dim, float eps, cudaStream_t st) {
+                       float* dw, float* scratch, int rows, int dim, float eps, cudaStream_t st, int defer) {
+    // defer: leave the per-block partials in `scratch` (rows the launch does not use keep what they hold) and
+    // do not sum them; ax_colsum_batch sums all RB_BLOCKS rows of several such scratch areas later
     if (rows <= 0 || dim <= 0) return 0;
     if ((size_t)dim * 4 > 200 * 1024) return 120;
     const int per = dt == 1 ? 8 : 4;
     const bool vec = dim % per == 0 && aligned16(x) && aligned16(w) && aligned16(g) && aligned16(dx) &&
                      (!res || aligned16(res));
-    float* part = dw ? scratch : nullptr;
+    float* part = (dw || defer) ? scratch : nullptr;
     if (vec && dim % (32 * per) == 0 && dim / (32 * per) <= 6) {      // more vectors per lane would spill
         const int vpl = dim / (32 * per);
         if (dt == 1) {
@@ -539,7 +541,7 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
 #define BP(V) case V: k_rmsnorm_bwd_packed<V><<<nbp, RBP_WARPS * 32, (size_t)RBP_WARPS * dim * 4, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
             switch (vpl) { BP(1) BP(2) BP(3) BP(4) BP(5) BP(6) }
 #undef BP
-            if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
+            if (dw && !defer) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
             return 0;
         }
         int nbw = (rows + RBW_WARPS - 1) / RBW_WARPS;
@@ -548,7 +550,7 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
         if (dt == 1) { switch (vpl) { BW(bf16, 1) BW(bf16, 2) BW(bf16, 3) BW(bf16, 4) BW(bf16, 5) BW(bf16, 6) } }
         else { switch (vpl) { BW(float, 1) BW(float, 2) BW(float, 3) BW(float, 4) BW(float, 5) BW(float, 6) } }
 #undef BW
-        if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbw, dim);
+        if (dw && !defer) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbw, dim);
         return 0;
     }
     // at most 5 vectors per lane: 8 warps x 5 KB of dw rows plus the exchange slots stay inside the 48 KB
@@ -563,7 +565,7 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
         if (wpr == 2) BPS(2) else BPS(4)
 #undef BPS
 #undef BPW
-        if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
+        if (dw && !defer) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
         return 0;
     }
     const int thr = norm_threads(dim, vec ? per : 1);
@@ -579,7 +581,40 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
     if (dt == 1) { if (vec) RB_LAUNCH(bf16, true); else RB_LAUNCH(bf16, false); }
     else { if (vec) RB_LAUNCH(float, true); else RB_LAUNCH(float, false); }
 #undef RB_LAUNCH
-    if (dw) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nb, dim);
+    if (dw && !defer) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nb, dim);
+    return 0;
+}
+
+// dw of `count` deferred RMSNorm backward launches in one launch: instance y has its RB_BLOCKS x dim partials at
+// scratch + (first + y) * RB_BLOCKS * dim and its result goes to arena + table[first + y] * chunk.  Rows beyond those
+// a launch wrote are zero (the scratch is allocated zeroed and row counts do not change between steps), so the sum
+// always runs over all RB_BLOCKS rows in block order: no atomics, run-to-run identical.  A destination outside the
+// arena is skipped and reported through the status word.
+__global__ void k_colsum_batch(const float* __restrict__ scratch, float* __restrict__ arena, const int* __restrict__ table,
+                               int first, int dim, int chunk, long long arena_elems, int* status) {
+    __shared__ float sh[8][33];
+    const int inst = first + blockIdx.y;
+    const float* partial = scratch + (long long)inst * RB_BLOCKS * dim;
+    const long long off = (long long)table[inst] * chunk;
+    const int j = blockIdx.x * 32 + threadIdx.x;
+    float acc = 0.f;
+    if (j < dim)
+        for (int b = threadIdx.y; b < RB_BLOCKS; b += 8) acc += partial[(long long)b * dim + j];
+    sh[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && j < dim) {
+        if (off < 0 || off + dim > arena_elems) { if (j == 0) atomicExch(status, 130); return; }
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) t += sh[q][threadIdx.x];
+        arena[off + j] = t;
+    }
+}
+int ax_colsum_batch(const float* scratch, float* arena, const int* table, int first, int count, int dim, int chunk,
+                    long long arena_elems, int* status, cudaStream_t st) {
+    if (count <= 0 || dim <= 0) return 0;
+    if (count > 65535) return 121;
+    k_colsum_batch<<<dim3((dim + 31) / 32, count), dim3(32, 8), 0, st>>>(scratch, arena, table, first, dim, chunk, arena_elems, status);
     return 0;
 }
 
@@ -619,7 +654,7 @@ int eng_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* g, const v
     }
     // Nothing in the scratch has to start at zero: the first kernel overwrites rows
     // [0, blocks) x [0, dim) of it and the second reads exactly those.
-    const int rc = ax_rmsnorm_bwd_acc(dt, x, w, g, res, dx, dw, g_noalloc_addr[dev], rows, dim, eps, (cudaStream_t)stream);
+    const int rc = ax_rmsnorm_bwd_acc(dt, x, w, g, res, dx, dw, g_noalloc_addr[dev], rows, dim, eps, (cudaStream_t)stream, 0);
     if (rc) return rc;
     return cudaPeekAtLastError() == cudaSuccess ? 0 : 204;
 }

@@ -27,8 +27,8 @@ import numpy as np
 # fused kinds of this engine (include/axeng.h)
 (GEMM_EX, ROPE_BTHD, ATTN_FWD, ATTN_BWD, RMSNORM_BWD_ACC, CE_FUSED, EMBED_BWD_DET,
  GNORM_FLAT, ADAMW_FLAT, EMBED_I32, REDUCE, ALLGATHER_F32, FORK, JOIN, STREAM,
- SILU_MUL_BWD_RC, GEMM_GROUP, TRANSPOSE_BF16) = range(32, 50)
-KIND_COUNT = 50
+ SILU_MUL_BWD_RC, GEMM_GROUP, TRANSPOSE_BF16, COLSUM_BATCH) = range(32, 51)
+KIND_COUNT = 51
 KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "COPY", "GEMM_SB",
               "PERM_0213", "ROPE", "SOFTMAX_CAUSAL", "REPEAT_KV", "RMSNORM_BWD", "COLSUM",
               "REPEAT_KV_BWD", "SOFTMAX_BWD", "SILU_BWD", "EMBED", "EMBED_BWD", "CE", "TICK", "CAST",
@@ -36,7 +36,7 @@ KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "CO
               "COUNTVALID", "BROADCAST", "GEMM_EX", "ROPE_BTHD", "ATTN_FWD", "ATTN_BWD",
               "RMSNORM_BWD_ACC", "CE_FUSED", "EMBED_BWD_DET", "GNORM_FLAT", "ADAMW_FLAT",
               "EMBED_I32", "REDUCE", "ALLGATHER_F32", "FORK", "JOIN", "STREAM", "SILU_MUL_BWD_RC",
-              "GEMM_GROUP", "TRANSPOSE_BF16"]
+              "GEMM_GROUP", "TRANSPOSE_BF16", "COLSUM_BATCH"]
 
 CHUNK = 1024          # arena granularity of the flat optimizer / collective ops
 GNORM_CHUNK = 8192    # elements per grad-norm partial
@@ -105,6 +105,10 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                m,oa = m_g; n,ob = n_g
                oc=4 (SwiGLU pair, batch=2): a=A; b=gate weights, sa=up weights (n wide each);
                c=g, d=u, sc=h=silu(g)*u
+    RMSNORM_BWD_ACC with oa=j>0: dw is deferred, the per-block partial sums stay in area j-1 of the scratch sb
+               (areas of 296*n floats, allocated zeroed)
+    COLSUM_BATCH: a=scratch areas, b=int32 table, c=fp32 arena; areas oa..oa+m-1 are summed into
+               c[table[i]*k : +n]
     TRANSPOSE_BF16: a = bf16 [m,n]; c = [n,m], bf16 (dt=1) or widened to fp32 (dt=0); not in place
     """
     return (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc,

@@ -247,8 +247,19 @@ class InterpEngine:
             if tb > 0:
                 dx = dx + self._get(tb, m * n, dt).reshape(m, n)
             self._put(c, dx, dt)
-            if sa > 0:
+            if sa > 0 and oa > 0:       # deferred: the partial sums stay in scratch area oa-1 (row 0 here)
+                area = 296 * n
+                self._f32(sb)[(oa - 1) * area:(oa - 1) * area + n] = dw
+            elif sa > 0:
                 self._put(sa, dw, 0)
+            return
+        if kind == E.COLSUM_BATCH:
+            area = 296 * n
+            tab = self.bufs[b].view(np.int32)
+            for i in range(oa, oa + m):
+                part = self._f32(a)[i * area:(i + 1) * area].reshape(296, n)
+                off = int(tab[i]) * k
+                self._f32(c)[off:off + n] = part.sum(axis=0, dtype=np.float32)
             return
         if kind == E.EMBED_BWD_DET:
             ids = self.bufs[b].view(np.int32)[:m]

@@ -312,3 +312,44 @@ def test_graph_capture_replay_counts(eng):
     before = eng.launch_count(reset=True)
     eng.replay(2)
     assert eng.launch_count() == 2 and before >= 3
+
+
+@pytest.mark.parametrize("dt", [0, 1])
+@pytest.mark.parametrize("dim", [256, 1536, 4096])
+def test_rmsnorm_deferred_dw_and_batched_column_sum(eng, dt, dim):
+    """Three RMSNorm backward launches leave their per-block partial sums in consecutive zeroed scratch areas
+    (oa = 1, 2, 3); one COLSUM_BATCH over areas 1..2 and one over area 0 give the same dw, bit for bit, as the
+    immediate form, at offsets of an fp32 arena taken from a device table."""
+    rng = np.random.default_rng(dim + dt)
+    unit = 1024
+    rows = [40, 700, 9]
+    arena = eng.alloc_zero(4 * 8 * 4096)
+    offs = np.array([4, 0, 8], dtype=np.int32)                 # in units of `unit` elements; disjoint for dim <= 4096
+    table = eng.alloc(4)
+    eng.upload_raw(table, offs)
+    scratch = eng.alloc_zero(3 * 296 * dim * 4)
+    one = eng.alloc(296 * dim)
+    want, plan = [], []
+    for j, r in enumerate(rows):
+        x, w, g = rnd(rng, (r, dim), dt), rnd(rng, dim, dt), rnd(rng, (r, dim), dt)
+        ix, iw, ig = put(eng, x, dt), put(eng, w, dt), put(eng, g, dt)
+        idx, idw = eng.alloc(r * dim), eng.alloc(dim)
+        eng.run([op(E.RMSNORM_BWD_ACC, a=ix, b=iw, d=ig, c=idx, tb=0, sa=idw, sb=one, m=r, n=dim, dt=dt, alpha=1e-5)])
+        want.append((eng.download(idw, dim), get(eng, idx, (r, dim), dt)))
+        plan.append(op(E.RMSNORM_BWD_ACC, a=ix, b=iw, d=ig, c=idx, tb=0, sa=idw, sb=scratch, oa=j + 1, m=r, n=dim,
+                       dt=dt, alpha=1e-5))
+        eng.run([op(E.SCALE, a=idw, c=idw, n=dim, alpha=0.0)])
+    plan += [op(E.COLSUM_BATCH, a=scratch, b=table, c=arena, m=2, n=dim, oa=1, k=unit),
+             op(E.COLSUM_BATCH, a=scratch, b=table, c=arena, m=1, n=dim, oa=0, k=unit)]
+    for _ in range(2):                                          # a second pass over the same areas
+        eng.run(plan)
+        got = eng.download(arena, 8 * 4096)
+        for j in range(3):
+            o = int(offs[j]) * unit
+            assert np.array_equal(got[o:o + dim], want[j][0]), j
+    assert eng.device_status() == 0
+    # a destination outside the arena is skipped and reported
+    eng.upload_raw(table, np.array([10 ** 6, 0, 0], dtype=np.int32))
+    eng.run([op(E.COLSUM_BATCH, a=scratch, b=table, c=arena, m=1, n=dim, oa=0, k=unit)])
+    assert eng.device_status(clear=True) == 130
+    assert eng.device_status() == 0
