@@ -402,9 +402,9 @@ def kernel_table(ct, c, batch):
                 gemm_flops += 2.0 * o[5] * ((o[6] + extra) * o[7] if o[16] == 1 else o[6] * (o[7] + extra))
     achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     # DRAM bytes per GEMM launch inside this step (dram__bytes_read.sum + dram__bytes_write.sum averaged over
-    # the 577 GEMM launches of one step in an ncu capture of this command line; summary:
+    # the 576 GEMM launches of a one-step window in an ncu capture of this command line; summary:
     # profiles/step_1b_launch_list.md).  It belongs to the 1B-class workload only.
-    traffic = 148.2e6 if c.get("name", "").startswith("1B-class") and "LoRA" not in c.get("name", "") else None
+    traffic = 148.4e6 if c.get("name", "").startswith("1B-class") and "LoRA" not in c.get("name", "") else None
     out = {"roofline": {"bound": "tensor", "kernel": "k_gemm_tc2 / k_gemm_tc (tcgen05 bf16 GEMM, all GEMM ops of the step)",
                         "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s", "frac": achieved / tf_sus,
                         "peak_source": f"{src} (sustained cuBLAS bf16)", "launches": gemm_calls,
