@@ -34,7 +34,7 @@ import numpy as np
 from axis_b200.engine import (
     ADAMW_FLAT, ADD, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, COLSUM_BATCH, COPY, EMBED_BWD_DET,
     EMBED_I32, FORK, GEMM_EX, GEMM_GROUP, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
-    ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, Engine, f32_to_bf16_bits, op)
+    ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, EVENT, Engine, f32_to_bf16_bits, op)
 
 LIN_ORDER = ("attn.q_proj", "attn.k_proj", "attn.v_proj", "attn.o_proj",
              "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj")
@@ -71,7 +71,8 @@ class CompiledTransformer:
                                "gate_proj", "up_proj", "down_proj"),
                  grad_sync: bool = False, max_grad_norm: float = 0.0,
                  zero_stage: int = 0, rank: int = 0, world: int = 1,
-                 bucket_layers: int = 4, adam_eps: float = 1e-8, recompute_blocks: bool = False):
+                 bucket_layers: int = 4, adam_eps: float = 1e-8, recompute_blocks: bool = False,
+                 overlap_dw: bool = True):
         assert dtype in ("fp32", "bf16")
         assert attn_impl in ("auto", "flash", "tiled")
         self.cfg = cfg
@@ -342,6 +343,39 @@ class CompiledTransformer:
                           alpha=sc_l, beta=1.0)]
             return o_
 
+        # ── weight-gradient GEMMs on a side stream ──
+        # The dW GEMMs of a block feed nothing until the optimizer (or the bucket's reduction), so they are
+        # queued on a side stream and fill the SMs that the main chain's kernels leave idle (partial last
+        # waves of the dX GEMMs and of the attention backward).  Dependencies are explicit events: the side
+        # stream waits for the main chain before each group (its inputs were just produced there), and the main
+        # chain waits for the side stream's last reader of a gradient buffer before it overwrites that buffer.
+        # Not used with adapters (their gradients chain through shared scratch) nor with per-block recompute
+        # (the shared activation set is rewritten while a side GEMM could still read it).
+        side_dw = bool(overlap_dw) and not lora and not rc
+        self.overlap_dw = side_dw
+        ev = [0]                              # last event id handed out
+        side_reads: Dict[int, int] = {}       # gradient buffer -> event after its last side-stream reader
+
+        def on_side(ops_, reads):
+            if not side_dw or not ops_:
+                return ops_
+            e_in, e_out = ev[0] + 1, ev[0] + 2
+            ev[0] = e_out
+            for b_ in reads:
+                side_reads[b_] = e_out
+            return [op(EVENT, tb=1, sa=0, oa=e_in), op(EVENT, tb=2, sa=2, oa=e_in), op(STREAM, tb=2)] + ops_ + \
+                   [op(EVENT, tb=1, sa=2, oa=e_out), op(STREAM, tb=0)]
+
+        def before_write(*bufs):
+            """main chain: wait until the side stream has finished reading the buffers about to be rewritten"""
+            es = [side_reads.pop(b_) for b_ in bufs if b_ in side_reads]
+            if not es:
+                return []
+            e = max(es)                        # the side stream runs in order: later events imply earlier ones
+            for b_ in [b_ for b_, v in side_reads.items() if v <= e]:
+                del side_reads[b_]
+            return [op(EVENT, tb=2, sa=0, oa=e)]
+
         def lin_b(g, x, i, pref, dx, acc=False, dw=True):
             """dx (+)= g@W_eff^T ; weight grads: dW (full; dw=False leaves it to a later grouped launch) or dA/dB (LoRA)"""
             fin, fout = lin_geom[pref]
@@ -350,7 +384,7 @@ class CompiledTransformer:
                      beta=1.0 if acc else 0.0)]
             if not lora:
                 if dw:
-                    o_ += [op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)]
+                    o_ += on_side([op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)], [g])
             elif pref.split(".")[-1] in lset:
                 u = u_l[(i, pref)]
                 o_ += [op(GEMM_SB, a=g, b=P[key + ".lora_b"], c=t1, m=N, k=fout, n=lora_r, batch=1, tb=1, dt=DT),
@@ -394,8 +428,8 @@ class CompiledTransformer:
                      k=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=2, tb=1, dt=DT)]
             if not lora:
                 gw = [G[k_ + ".weight"] for k_ in keys] + [0]
-                o_ += [op(GEMM_GROUP, a=x, b=gg[0], sa=gg[1], sb=gg[2], c=gw[0], d=gw[1], sc=gw[2], m=fin, k=N,
-                          n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, tb=2, dt=DTW)]
+                o_ += on_side([op(GEMM_GROUP, a=x, b=gg[0], sa=gg[1], sb=gg[2], c=gw[0], d=gw[1], sc=gw[2], m=fin, k=N,
+                                  n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, tb=2, dt=DTW)], list(gs_))
             else:
                 for p_, g_, k_ in zip(prefs, gs_, keys):
                     if p_.split(".")[-1] not in lset:
@@ -482,15 +516,19 @@ class CompiledTransformer:
         plan += norm_b(xs[L], "norm.weight", dxf, -1, dcur)
         plan += flush_dw()
         marks = {0: len(plan)}
+        mark_ev = {0: 0}                      # last side-stream event a bucket's gradients depend on
         for i in reversed(range(L)):
             p = f"blocks.{i}."
             if rc and i < L - 1:      # the last block's activations are still in place after the forward
                 plan += block_f(i, down=False)
             plan += lin_b(dcur, hs[i], i, "mlp.down_proj", dh_)
+            plan += before_write(dg_, du_)
             plan += [op(SILU_BWD, a=gs[i], b=us[i], d=dh_, c=dg_, tb=du_, n=N * MLP, dt=DT)]
             plan += lin_b_group((dg_, du_), zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), dz)
+            plan += before_write(dr1)
             plan += norm_b(r1s[i], p + "mlp_norm.weight", dz, dcur, dr1)
             plan += lin_b(dr1, at2s[i], i, "attn.o_proj", dat2)
+            plan += before_write(dq, dk, dv)
             plan += [
                 op(ATTN_BWD, a=q2s[i], b=k2s[i], d=vs[i], c=dat2, sa=lses[i], sb=at2s[i],
                    tb=dq, sc=dk, oa=dv, ob=H, oc=bD, m=T, n=DH, k=KV, batch=B, dt=DT, alpha=scale),
@@ -498,16 +536,21 @@ class CompiledTransformer:
                    sa=dk, sb=dk, sc=KV),
             ]
             plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
+            plan += before_write(dcur)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
             if (L - 1 - i) % bucket_layers == bucket_layers - 1 and i > 0:
                 plan += flush_dw()
                 marks[1 + (L - 1 - i) // bucket_layers] = len(plan)
+                mark_ev[1 + (L - 1 - i) // bucket_layers] = ev[0]
         if not lora:
             if not tied:
                 plan += [op(SCALE, a=G["embed.weight"], c=G["embed.weight"], n=V * D, alpha=0.0)]
             plan += [op(EMBED_BWD_DET, a=dcur, b=self.b_ids, c=G["embed.weight"], m=N, n=D, dt=DT)]
         plan += flush_dw()
         marks[nb - 1] = len(plan)
+        mark_ev[nb - 1] = ev[0]
+        if ev[0]:                             # the main chain ends after the last side-stream GEMM
+            plan += [op(EVENT, tb=2, sa=0, oa=ev[0])]
         self.plan_fb = plan
         if rb_names:
             eng.upload_raw(self.b_rb_table, np.array([self._off[nm] // CHUNK for nm in rb_names], dtype=np.int32))
@@ -518,7 +561,9 @@ class CompiledTransformer:
                    for r in range(cw) for (st, ln) in [self._groups[r][b]] if ln > 0]
             if not red:
                 return []
-            out = [op(FORK), op(STREAM, tb=1), op(GROUP, tb=0)] + red + [op(GROUP, tb=1)]
+            dep = mark_ev.get(b, 0)          # the bucket's weight gradients come from the side stream
+            out = [op(FORK)] + ([op(EVENT, tb=2, sa=1, oa=dep)] if dep else []) + \
+                  [op(STREAM, tb=1), op(GROUP, tb=0)] + red + [op(GROUP, tb=1)]
             if not zero:     # replicated: everyone gets the reduced gradients back
                 out += [op(GROUP, tb=0)] + [op(BROADCAST, a=self.a_grad, m=o[5], oa=o[14], tb=o[9]) for o in red] \
                     + [op(GROUP, tb=1)]
@@ -713,7 +758,7 @@ def compile_model(model, batch: int, seq: int, lib_path: str = None,
                   attn_tile: int = 256, attn_impl: str = "auto",
                   grad_sync: bool = False, max_grad_norm: float = 0.0,
                   zero_stage: int = 0, rank: int = 0, world: int = 1,
-                  recompute_blocks: bool = False) -> CompiledTransformer:
+                  recompute_blocks: bool = False, overlap_dw: bool = True) -> CompiledTransformer:
     """Compile a Transformer into a native training step (axis/compile.py:618-664).
 
     `model` is anything shaped like the reference's `axis.nn.Transformer`:
@@ -724,7 +769,8 @@ def compile_model(model, batch: int, seq: int, lib_path: str = None,
     wrapper's `scaling` attribute; base weights are then frozen.
 
     `recompute_blocks` (not in the reference's compiled engine, whose signature ends at `world`) trades a
-    second forward of every block for activation memory: see CompiledTransformer.
+    second forward of every block for activation memory: see CompiledTransformer.  `overlap_dw=False` keeps the
+    weight-gradient GEMMs on the main stream.
     """
     weights = {n.replace(".base.weight", ".weight"): np.asarray(p.data)
                for n, p in model.named_parameters()}
@@ -748,7 +794,7 @@ def compile_model(model, batch: int, seq: int, lib_path: str = None,
                                lora_targets=targets or ("q_proj", "k_proj", "v_proj", "o_proj"),
                                grad_sync=grad_sync, max_grad_norm=max_grad_norm,
                                zero_stage=zero_stage, rank=rank, world=world,
-                               recompute_blocks=recompute_blocks)
+                               recompute_blocks=recompute_blocks, overlap_dw=overlap_dw)
 
 
 def _find_lora_scaling(model) -> float:

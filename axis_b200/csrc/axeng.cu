@@ -26,7 +26,8 @@ struct Buf { void* p; long long bytes; bool owned; };
 
 struct Engine {
     bool inited = false;
-    cudaStream_t stream = nullptr, comm_stream = nullptr;
+    cudaStream_t stream = nullptr, comm_stream = nullptr, side_stream = nullptr;    // main chain, collectives, overlapped weight-gradient GEMMs
+    std::vector<cudaEvent_t> named_events;      // EVENT ops: cross-stream dependencies by id
     cudaStream_t cur = nullptr;                 // stream the next op goes to
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     std::vector<cudaEvent_t> fork_events;       // one per FORK/JOIN inside a plan
@@ -65,6 +66,7 @@ static void set_err(const char* fmt, ...) {
 static void release_all() {
     if (G.stream) cudaStreamSynchronize(G.stream);
     if (G.comm_stream) cudaStreamSynchronize(G.comm_stream);
+    if (G.side_stream) cudaStreamSynchronize(G.side_stream);
     if (G.graph) { cudaGraphExecDestroy(G.graph); G.graph = nullptr; }
     for (int i = 0; i < MAX_BUFS; i++) {
         if (G.bufs[i].p && G.bufs[i].owned) cudaFree(G.bufs[i].p);
@@ -88,6 +90,9 @@ static void release_all() {
     if (G.comm) { ncclCommDestroy(G.comm); G.comm = nullptr; }
     if (G.stream) { cudaStreamDestroy(G.stream); G.stream = nullptr; }
     if (G.comm_stream) { cudaStreamDestroy(G.comm_stream); G.comm_stream = nullptr; }
+    if (G.side_stream) { cudaStreamDestroy(G.side_stream); G.side_stream = nullptr; }
+    for (auto e : G.named_events) if (e) cudaEventDestroy(e);
+    G.named_events.clear();
     G.bytes = 0; G.launches = 0; G.graph_launches = 0; G.inited = false;
 }
 
@@ -97,6 +102,7 @@ API int eng_init(void) {
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev < 1) { set_err("no CUDA device"); return 1; }
     if (cudaStreamCreateWithFlags(&G.stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
     if (cudaStreamCreateWithFlags(&G.comm_stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
+    if (cudaStreamCreateWithFlags(&G.side_stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
     G.cur = G.stream;
     if (cudaMalloc(&G.d_status, 64)) { set_err("status alloc failed"); return 3; }
     cudaMemset(G.d_status, 0, 64);
@@ -124,6 +130,7 @@ API long long eng_bytes_allocated(void) { return G.bytes; }
 API int eng_sync(void) {
     int rc = (int)cudaStreamSynchronize(G.stream);
     if (!rc) rc = (int)cudaStreamSynchronize(G.comm_stream);
+    if (!rc) rc = (int)cudaStreamSynchronize(G.side_stream);
     return rc;
 }
 API long long eng_launch_count(int reset) {
@@ -780,8 +787,19 @@ static int exec_op(const EngOp* op) {
             return 0;
         }
         case ENG_STREAM:
-            G.cur = op->tb ? G.comm_stream : G.stream;
+            G.cur = op->tb == 2 ? G.side_stream : (op->tb ? G.comm_stream : G.stream);
+            ax_gemm_side(G.cur != G.stream);
             return 0;
+        case ENG_EVENT: {
+            // tb=1: record event oa on stream sa; tb=2: stream sa waits for event oa (sa: 0 main, 1 collectives, 2 side)
+            if (op->oa < 0 || op->oa >= 65536 || op->sa < 0 || op->sa > 2 || (op->tb != 1 && op->tb != 2)) { set_err("event: bad arguments"); return 112; }
+            if ((size_t)op->oa >= G.named_events.size()) G.named_events.resize(op->oa + 1, nullptr);
+            cudaEvent_t& e = G.named_events[op->oa];
+            if (!e && cudaEventCreateWithFlags(&e, cudaEventDisableTiming)) { e = nullptr; return 113; }
+            cudaStream_t s = op->sa == 2 ? G.side_stream : (op->sa ? G.comm_stream : G.stream);
+            if (op->tb == 1) return cudaEventRecord(e, s) ? 113 : 0;
+            return cudaStreamWaitEvent(s, e, 0) ? 113 : 0;
+        }
         default:
             set_err("unknown op kind %d", op->kind);
             return 100;
@@ -791,10 +809,12 @@ static int exec_op(const EngOp* op) {
 static int run_ops(const EngOp* ops, int n_ops) {
     G.fork_used = 0;
     G.cur = G.stream;
+    ax_gemm_side(0);
     for (int i = 0; i < n_ops; i++) {
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         const bool prof = G.profile && ops[i].kind >= 0 && ops[i].kind < ENG_KIND_COUNT &&
-                          ops[i].kind != ENG_GROUP && ops[i].kind != ENG_STREAM && ops[i].kind != ENG_FORK && ops[i].kind != ENG_JOIN;
+                          ops[i].kind != ENG_GROUP && ops[i].kind != ENG_STREAM && ops[i].kind != ENG_FORK && ops[i].kind != ENG_JOIN &&
+                          ops[i].kind != ENG_EVENT;
         if (prof) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, G.cur); }
         int rc = exec_op(&ops[i]);
         if (!rc) {

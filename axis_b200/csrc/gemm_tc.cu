@@ -232,9 +232,14 @@ static const size_t SPLITK_WS_BYTES = 160u << 20;
 static int g_pair_mode = 0;        // 0 auto, 1 never use the paired-CTA kernel, 2 use it whenever the shape allows
 static int g_pairs_avail = 0;      // co-resident CTA pairs of the paired kernel (0 = unavailable)
 // programmatic dependent launch of the GEMM kernels (AXENG_NO_PDL=1 turns it off)
+// GEMMs queued on a side stream (weight gradients that overlap the main chain): no programmatic dependent
+// launch (their predecessor in the stream is an event wait, not a kernel of the chain) and no split-K (the
+// split-K workspace is one buffer, owned by the main stream's launches)
+static int g_side = 0;
+void ax_gemm_side(int on) { g_side = on; }
 int ax_gemm_pdl(void) {
     static const int on = getenv("AXENG_NO_PDL") ? 0 : 1;
-    return on;
+    return on && !g_side;
 }
 // output tiles written by TMA stores from a shared-memory staging area (AXENG_NO_TMA_OUT=1: per-thread stores)
 int ax_gemm_tma_out(void) {
@@ -326,7 +331,7 @@ int ax_gemm_tc(int out_bf16, int tb, const void* A, const void* B, void* C, cons
         if (bn == 256 && n < 256) break;
         const long long tiles = tm_ * ((n + bn - 1) / bn);
         for (int sk = 1; sk <= 4; sk++) {
-            if (sk > 1 && (kblocks < 16 * sk || (n & 3) || !g_splitk_ws ||
+            if (sk > 1 && (g_side || kblocks < 16 * sk || (n & 3) || !g_splitk_ws ||
                            (size_t)sk * m * n * 4 > SPLITK_WS_BYTES)) break;
             const double per_kb = bn == 256 ? 1.0 : 0.72;
             double cost = (double)waves(tiles * sk) * ((kblocks + sk - 1) / sk) * per_kb;
@@ -342,7 +347,7 @@ int ax_gemm_tc(int out_bf16, int tb, const void* A, const void* B, void* C, cons
         int best2_s = 1;
         double best2 = 1e30;
         for (int sk = 1; sk <= 4; sk++) {
-            if (sk > 1 && (kblocks < 16 * sk || (n & 3) || !g_splitk_ws || (size_t)sk * m * n * 4 > SPLITK_WS_BYTES)) break;
+            if (sk > 1 && (g_side || kblocks < 16 * sk || (n & 3) || !g_splitk_ws || (size_t)sk * m * n * 4 > SPLITK_WS_BYTES)) break;
             double cost = (double)((tiles2 * sk + g_pairs_avail - 1) / g_pairs_avail) * ((kblocks + sk - 1) / sk) * 0.70;
             if (sk > 1) cost += (2.0 * sk + 1.0) * m * n * 4.0 / 4.0e12 / 0.45e-6 + 4.0;
             if (cost < best2 - 1e-9) { best2 = cost; best2_s = sk; }

@@ -98,6 +98,7 @@ int ax_attn_bwd_simt(int dt, int out_dt, const void* q, const void* k, const voi
 
 // gemm_tc2.cu — grouped launch of the paired-CTA GEMM (mode 1: shared A, per-problem B/C/n; mode 2: one C summed
 // over per-segment A/B/k; mode 3: independent problems A/B/C/m/n of one depth k).  -1 when not served.
+void ax_gemm_side(int on);
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
                       const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st);
 

@@ -27,8 +27,8 @@ import numpy as np
 # fused kinds of this engine (include/axeng.h)
 (GEMM_EX, ROPE_BTHD, ATTN_FWD, ATTN_BWD, RMSNORM_BWD_ACC, CE_FUSED, EMBED_BWD_DET,
  GNORM_FLAT, ADAMW_FLAT, EMBED_I32, REDUCE, ALLGATHER_F32, FORK, JOIN, STREAM,
- SILU_MUL_BWD_RC, GEMM_GROUP, TRANSPOSE_BF16, COLSUM_BATCH) = range(32, 51)
-KIND_COUNT = 51
+ SILU_MUL_BWD_RC, GEMM_GROUP, TRANSPOSE_BF16, COLSUM_BATCH, EVENT) = range(32, 52)
+KIND_COUNT = 52
 KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "COPY", "GEMM_SB",
               "PERM_0213", "ROPE", "SOFTMAX_CAUSAL", "REPEAT_KV", "RMSNORM_BWD", "COLSUM",
               "REPEAT_KV_BWD", "SOFTMAX_BWD", "SILU_BWD", "EMBED", "EMBED_BWD", "CE", "TICK", "CAST",
@@ -36,7 +36,7 @@ KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "CO
               "COUNTVALID", "BROADCAST", "GEMM_EX", "ROPE_BTHD", "ATTN_FWD", "ATTN_BWD",
               "RMSNORM_BWD_ACC", "CE_FUSED", "EMBED_BWD_DET", "GNORM_FLAT", "ADAMW_FLAT",
               "EMBED_I32", "REDUCE", "ALLGATHER_F32", "FORK", "JOIN", "STREAM", "SILU_MUL_BWD_RC",
-              "GEMM_GROUP", "TRANSPOSE_BF16", "COLSUM_BATCH"]
+              "GEMM_GROUP", "TRANSPOSE_BF16", "COLSUM_BATCH", "EVENT"]
 
 CHUNK = 1024          # arena granularity of the flat optimizer / collective ops
 GNORM_CHUNK = 8192    # elements per grad-norm partial
@@ -96,7 +96,9 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                alpha=max_norm beta=wd gamma=eps
     REDUCE / BROADCAST / ALLREDUCE with m>0: m chunks at chunk offset oa of a
     ALLGATHER_F32: a=send (offset oa) c=recv; n=count per rank
-    FORK / JOIN / STREAM(tb): side-stream control for overlapped collectives
+    FORK / JOIN / STREAM(tb): side-stream control for overlapped collectives (tb: 0 main, 1 collectives,
+               2 side stream of the overlapped weight-gradient GEMMs)
+    EVENT: tb=1 record event oa on stream sa / tb=2 stream sa waits for event oa (sa as STREAM's tb)
     GEMM_GROUP: batch = 2 or 3 GEMMs of one layer as one launch; m, tb, dt, alpha as GEMM_SB.
                oc=1 (one input, several outputs): a=A; b,sa,sb = B_g; c,d,sc = C_g; n,oa,ob = n_g; k
                oc=2 (one output summed over K-segments): c=C; a,sa,sb = A_s; b,d,sc = B_s;

@@ -236,6 +236,8 @@ def main():
     ap.add_argument("--zero", type=int, default=1)
     ap.add_argument("--recompute", action="store_true",
                     help="keep one set of activations and re-run each block's forward inside the backward")
+    ap.add_argument("--no-overlap-dw", action="store_true",
+                    help="run the weight-gradient GEMMs inline instead of on the side stream")
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-table", action="store_true")
@@ -272,7 +274,7 @@ def main():
     zero = args.zero if WORLD > 1 else 0
     ct = compile_model(model, batch=c["B"], seq=c["T"], dtype=c["dtype"], lr=c["lr"], max_grad_norm=1.0,
                        grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD,
-                       recompute_blocks=args.recompute)
+                       recompute_blocks=args.recompute, overlap_dw=not args.no_overlap_dw)
     del model
     eng = ct.eng
     if WORLD > 1:
@@ -327,7 +329,7 @@ def main():
             "config": {"workload": c["name"], "parallelism": f"dp{WORLD}" + ("+zero1" if zero else ""),
                        "l2": "working set per step far exceeds the 126 MB L2 (no flush needed)",
                        "global_batch": c["B"] * WORLD, "seq_len": c["T"],
-                       "recompute_blocks": bool(args.recompute)},
+                       "recompute_blocks": bool(args.recompute), "overlap_dw": bool(ct.overlap_dw)},
             "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 2 * 4 * c["B"] * c["T"],
                     "d2h_bytes_per_step": 4, "pipelined_value": tokens * K / e2e_async_s},
             "gpu_launches": int(launches), "clocks": clk, "loss_first": losses[0], "loss_last": losses[-1],

@@ -65,6 +65,7 @@ enum EngOpKind {
     ENG_TRANSPOSE_BF16 = 49,  /* c[n,m] = a[m,n]^T, a bf16; c bf16 (dt=1) or widened to fp32 (dt=0): checkpoint weights
                                  stored [out,in] in bf16 go to the [in,out] compute / master layout on the device */
     ENG_COLSUM_BATCH = 50,    /* dw of several RMSNORM_BWD_ACC launches whose partial sums were left in scratch (oa > 0 there) */
+    ENG_EVENT = 51,           /* cross-stream dependency by id: record on a stream / make a stream wait (main, collectives, side) */
     ENG_KIND_COUNT
 };
 

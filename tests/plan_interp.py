@@ -151,7 +151,7 @@ class InterpEngine:
     def _exec(self, o):
         (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc, alpha, beta, gamma) = o
         self.trace.append(kind)
-        if kind not in (E.GROUP, E.FORK, E.JOIN, E.STREAM):
+        if kind not in (E.GROUP, E.FORK, E.JOIN, E.STREAM, E.EVENT):
             self.launches += 1
         if kind in (E.GEMM, E.GEMM_SB):
             return self._gemm(o, False)
@@ -312,7 +312,7 @@ class InterpEngine:
             if sa > 0:
                 self._put(sa, p, 1, off)
             return
-        if kind in (E.GROUP, E.FORK, E.JOIN, E.STREAM):
+        if kind in (E.GROUP, E.FORK, E.JOIN, E.STREAM, E.EVENT):
             return
         if kind in (E.REDUCE, E.BROADCAST, E.ALLREDUCE):
             import torch

@@ -119,7 +119,10 @@ def test_reduction_is_bucketed_inside_backward(runs):
     red = [i for i, k in enumerate(first) if k == E.REDUCE]
     gemm_after_first_reduce = [i for i, k in enumerate(first) if k == E.GEMM_SB and i > red[0]]
     assert len(red) >= 3 and gemm_after_first_reduce, "reductions must be interleaved with backward GEMMs"
-    assert first.count(E.FORK) == first.count(E.STREAM) // 2 and first[-1] == E.JOIN
+    # every reduction group forks the collectives stream off the main chain; stream switches come in pairs
+    # (collectives and the side stream of the weight-gradient GEMMs); the main chain joins at the end
+    assert first.count(E.FORK) >= 3 and first.count(E.STREAM) % 2 == 0 and first[-1] == E.JOIN
+    assert first.count(E.EVENT) > 0
 
 
 def test_zero1_with_block_recompute_equals_zero1_bit_for_bit(runs):

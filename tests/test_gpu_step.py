@@ -324,3 +324,41 @@ def test_async_replay_pipeline_matches_the_blocking_steps():
     assert la == lb
     for nm in wa:
         assert np.array_equal(wa[nm], wb[nm]), nm
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_side_stream_weight_gradients_equal_the_inline_plan(dtype):
+    """The dW GEMMs on the side stream (ordered against the main chain by events) give the losses, gradients and
+    weights of the plan that runs them inline: bit for bit in fp32, like two runs of one plan in bf16 — eagerly
+    and under graph replay, over enough steps for a missing dependency to show as a difference."""
+    cfg = dict(vocab_size=512, dim=256, n_layers=4, n_heads=4, n_kv_heads=2, mlp_hidden=384, tie_embeddings=False)
+    w0 = O.init_weights(cfg, seed=5)
+    rng = np.random.default_rng(5)
+    batches = [O.make_batch(rng, 512, 2, 256, 0.05) for _ in range(9)]
+
+    def run(overlap):
+        ct = build(cfg, w0, 2, 256, dtype=dtype, max_grad_norm=1.0, overlap_dw=overlap)
+        assert ct.overlap_dw == overlap
+        l0 = ct.forward_backward(*batches[0])
+        g = ct.grads()
+        ls = [ct.step(*batches[0])]
+        ct.capture()
+        ls += [ct.replay_step(*b) for b in batches[1:]]
+        assert ct.eng.device_status() == 0
+        return l0, g, ls, ct.get_weights()
+
+    la, ga, lsa, wa = run(False)
+    lb, gb, lsb, wb = run(True)
+    assert la == lb
+    for nm in ga:
+        if dtype == "fp32":
+            assert np.array_equal(ga[nm], gb[nm]), nm
+        else:
+            assert rel(gb[nm], ga[nm]) <= 5e-3, nm
+    for s, (x1, x2) in enumerate(zip(lsa, lsb)):
+        assert abs(x1 - x2) <= (0 if dtype == "fp32" else 5e-4 * abs(x1)), (s, x1, x2)
+    for nm in wa:
+        if dtype == "fp32":
+            assert np.array_equal(wa[nm], wb[nm]), nm
+        else:
+            assert np.abs(wa[nm] - wb[nm]).max() <= 9 * 4.5 * 3e-4, nm

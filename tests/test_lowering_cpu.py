@@ -231,3 +231,87 @@ def test_async_replay_returns_the_previous_loss():
     assert b.replay_step_async(*xs[0]) is None          # after a flush the pipeline starts empty again
     with pytest.raises(RuntimeError):
         b.eng.download_wait(12345)
+
+
+def _side_stream_hazards(plan):
+    """Static check of a plan that queues weight-gradient GEMMs on the side stream (STREAM tb=2): every such GEMM
+    must start after an event recorded on the main chain directly before it, and until the main chain (or the
+    collectives stream, for REDUCE / BROADCAST) has waited for the event recorded after it, no op there may write
+    a buffer the GEMM reads or touch a buffer it writes.  Returns a list of violations."""
+    from axis_b200 import engine as E
+    F = dict(kind=0, a=1, b=2, c=3, d=4, m=5, n=6, k=7, batch=8, tb=9, sa=10, sb=11, sc=12, dt=13, oa=14, ob=15, oc=16)
+    writes = {E.GEMM_SB: ["c"], E.GEMM_EX: ["c"], E.GEMM_GROUP: ["c", "d", "sc"], E.SILU_BWD: ["c", "tb"],
+              E.RMSNORM_BWD_ACC: ["c", "sb"], E.RMSNORM: ["c"], E.ATTN_FWD: ["c", "sa"],
+              E.ATTN_BWD: ["tb", "sc", "oa", "oc"], E.ROPE_BTHD: ["c", "sb"], E.CE_FUSED: ["c", "d", "sa", "sb"],
+              E.EMBED_I32: ["c"], E.EMBED_BWD_DET: ["c"], E.SILU_MUL: ["c"], E.SCALE: ["c"]}
+    bad, stream = [], 0
+    side = []                                   # (index, reads, writes, e_out or None)
+    for i, o in enumerate(plan):
+        k = o[0]
+        if k == E.STREAM:
+            stream = o[F["tb"]]
+            continue
+        if k == E.EVENT:
+            if o[F["tb"]] == 1 and o[F["sa"]] == 2 and side and side[-1][3] is None:
+                side[-1][3] = o[F["oa"]]        # the event recorded after the last side GEMM
+            if o[F["tb"]] == 2 and o[F["sa"]] in (0, 1):      # main / collectives caught up with the side stream
+                for s_ in side:
+                    if s_[3] is not None and s_[3] <= o[F["oa"]]:
+                        s_[4].add(o[F["sa"]])
+            continue
+        if stream == 2:
+            if k not in (E.GEMM_SB, E.GEMM_GROUP):
+                bad.append((i, "non-GEMM op on the side stream"))
+            prev = plan[i - 1], plan[i - 2], plan[i - 3]
+            if not (prev[0][0] == E.STREAM and prev[1][0] == E.EVENT and prev[1][F["tb"]] == 2 and prev[1][F["sa"]] == 2
+                    and prev[2][0] == E.EVENT and prev[2][F["tb"]] == 1 and prev[2][F["sa"]] == 0
+                    and prev[1][F["oa"]] == prev[2][F["oa"]]):
+                bad.append((i, "side GEMM does not wait for the main chain"))
+            grp = k == E.GEMM_GROUP
+            rd = {o[F[f]] for f in (("a", "b", "sa", "sb") if grp else ("a", "b"))} - {0, -1}
+            wr = {o[F[f]] for f in (("c", "d", "sc") if grp else ("c",))} - {0, -1}
+            side.append([i, rd, wr, None, set()])
+            continue
+        if k in (E.GROUP, E.FORK, E.JOIN):
+            continue
+        who = 1 if stream == 1 else 0
+        touched = {o[F[f]] for f in ("a", "b", "c", "d", "sa", "sb", "sc", "tb", "oa", "oc") if isinstance(o[F[f]], int)}
+        written = {o[F[f]] for f in writes.get(k, [])}
+        for s_ in side:
+            if who in s_[4]:
+                continue                        # this stream has waited for that GEMM
+            if written & s_[1]:
+                bad.append((i, f"op {E.KIND_NAMES[k]} rewrites an input of the side GEMM at {s_[0]}"))
+            if k not in (E.COLSUM_BATCH, E.GNORM_FLAT, E.ADAMW_FLAT, E.REDUCE, E.BROADCAST) and touched & s_[2]:
+                bad.append((i, f"op {E.KIND_NAMES[k]} touches an output of the side GEMM at {s_[0]}"))
+            if k in (E.GNORM_FLAT, E.ADAMW_FLAT, E.REDUCE, E.BROADCAST):
+                bad.append((i, f"{E.KIND_NAMES[k]} over the gradient arena before the side GEMM at {s_[0]} is awaited"))
+    if any(0 not in s_[4] for s_ in side):
+        bad.append((len(plan), "the main chain ends before the side stream"))
+    return bad, len(side)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_side_stream_weight_gradients_are_ordered_by_events(world):
+    """The dW GEMMs run on a side stream; the plan orders them against the main chain and the collectives with
+    events only.  The checker finds no hazard in the emitted plans and does find one when a wait is removed."""
+    from axis_b200 import engine as E
+    cfg = dict(vocab_size=61, dim=32, n_layers=5, n_heads=4, n_kv_heads=2, mlp_hidden=48, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=1)
+    kw = dict(grad_sync=True, zero_stage=1, rank=0, world=2, bucket_layers=2) if world == 2 else {}
+    ct = CompiledTransformer(InterpEngine(), cfg, w0, 2, 8, dtype="bf16", max_grad_norm=1.0, **kw)
+    assert ct.overlap_dw
+    bad, n_side = _side_stream_hazards(ct.plan_step)
+    assert not bad, bad[:5]
+    assert n_side == 4 * cfg["n_layers"]
+    # drop the wait in front of one SiLU backward: the rewrite of dg/du races with the previous block's dW
+    plan = list(ct.plan_step)
+    idx = [i for i, o in enumerate(plan) if o[0] == E.SILU_BWD][2]
+    assert plan[idx - 1][0] == E.EVENT and plan[idx - 1][9] == 2
+    del plan[idx - 1]
+    bad2, _ = _side_stream_hazards(plan)
+    assert any("rewrites an input" in msg for _, msg in bad2)
+    # adapters and per-block recompute keep everything on the main chain
+    for kw2 in (dict(lora_r=4), dict(recompute_blocks=True), dict(overlap_dw=False)):
+        c2 = CompiledTransformer(InterpEngine(), cfg, w0, 2, 8, dtype="bf16", **kw2)
+        assert not c2.overlap_dw and not any(o[0] == E.EVENT for o in c2.plan_step)
