@@ -100,9 +100,14 @@ API int eng_init(void) {
     if (G.inited) release_all();
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev < 1) { set_err("no CUDA device"); return 1; }
-    if (cudaStreamCreateWithFlags(&G.stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
-    if (cudaStreamCreateWithFlags(&G.comm_stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
-    if (cudaStreamCreateWithFlags(&G.side_stream, cudaStreamNonBlocking)) { set_err("stream create failed"); return 5; }
+    // the main chain and the collectives get the highest priority, the side stream the lowest: its GEMMs take the
+    // SMs the chain leaves idle and do not delay it (AXENG_FLAT_PRIORITY=1: all streams alike)
+    int prio_lo = 0, prio_hi = 0;
+    cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+    if (getenv("AXENG_FLAT_PRIORITY")) prio_hi = prio_lo;
+    if (cudaStreamCreateWithPriority(&G.stream, cudaStreamNonBlocking, prio_hi)) { set_err("stream create failed"); return 5; }
+    if (cudaStreamCreateWithPriority(&G.comm_stream, cudaStreamNonBlocking, prio_hi)) { set_err("stream create failed"); return 5; }
+    if (cudaStreamCreateWithPriority(&G.side_stream, cudaStreamNonBlocking, prio_lo)) { set_err("stream create failed"); return 5; }
     G.cur = G.stream;
     if (cudaMalloc(&G.d_status, 64)) { set_err("status alloc failed"); return 3; }
     cudaMemset(G.d_status, 0, 64);
