@@ -23,8 +23,9 @@ LIB = os.path.join(LIBDIR, "libaxeng.so")
 SOURCES = ["axeng.cu", "elementwise.cu", "norm.cu", "loss.cu", "optim.cu", "gemm_simt.cu",
            "gemm_tc.cu", "gemm_tc2.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc128.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-              "-Xcompiler", "-fPIC", "--use_fast_math_off_placeholder"]
-NVCC_FLAGS = [f for f in NVCC_FLAGS if f != "--use_fast_math_off_placeholder"]
+              "-Xcompiler", "-fPIC"]
+if os.environ.get("AXENG_BUILD_PROF"):      # instrumented build: in-kernel cycle stamps of the GEMM / attention kernels
+    NVCC_FLAGS.append("-DAXENG_PROF")
 
 
 def _nvcc() -> str:

@@ -262,9 +262,7 @@ class CompiledTransformer:
             if hf and zero and self._cown[nm] != rank:
                 put(P[nm], w, False)
         if hf and my_seg[1] > 0:
-            # one cast of the whole owned segment (padding is zero on both sides)
-            eng.run([op(CAST, a=self.a_master,
-                        c=eng.view(self.a_mirror, my_seg[0] * 2, my_seg[1] * 2), m=my_seg[1], tb=0)])
+            eng.run(self._cast_segment())
         self.pb = P
 
         # ── io + scalars ──
@@ -600,15 +598,28 @@ class CompiledTransformer:
                         tb=self.b_t, sc=self.b_wdflag, oa=self.b_sumsq, ob=cw, oc=self.b_gnorm,
                         alpha=float(max_norm or 0.0), beta=self.wd, gamma=adam_eps)]
             if zero:
-                ops_ += [op(GROUP, tb=0)] + \
-                    [op(BROADCAST, a=self.a_mirror, m=self._seg[r][1] // CHUNK, oa=self._seg[r][0] // CHUNK,
-                        tb=r, dt=1) for r in range(cw) if self._seg[r][1] > 0] + [op(GROUP, tb=1)]
+                ops_ += self._mirror_bcast_ops()
             return ops_
         self._opt_ops = opt_ops
         self.plan_step = self._plan_fb_sync + opt_ops(max_grad_norm)
         self._plan_noclip = None
         self._captured = False
         self._pending_loss = None            # read-back ticket of the last replay_step_async
+
+    def _mirror_bcast_ops(self):
+        """ZeRO-1: every owner broadcasts its segment of the bf16 mirror (one grouped launch)."""
+        return [op(GROUP, tb=0)] + \
+            [op(BROADCAST, a=self.a_mirror, m=ln // CHUNK, oa=st // CHUNK, tb=r, dt=1)
+             for r, (st, ln) in enumerate(self._seg) if ln > 0] + [op(GROUP, tb=1)]
+
+    def _cast_segment(self):
+        """fp32 masters of this rank's segment -> its bf16 mirror segment (padding is zero on both sides).
+        The count goes in as chunks x CHUNK (CAST converts m*n elements): a 7B-class segment has more
+        elements than a 32-bit field holds.  The reference casts tensor by tensor (axis/compile.py:192-200)."""
+        s0, sl = self._my_seg
+        if not hasattr(self, "_mirror_seg"):
+            self._mirror_seg = self.eng.view(self.a_mirror, s0 * 2, sl * 2)
+        return [op(CAST, a=self.a_master, c=self._mirror_seg, m=sl // CHUNK, n=CHUNK, tb=0)]
 
     # ── API (axis/compile.py:547-615) ──
     def set_lr(self, lr: float) -> None:
@@ -746,8 +757,12 @@ class CompiledTransformer:
             self.eng.upload(self._mb[nm], np.asarray(st[f"m/{nm}"]).reshape(-1))
             self.eng.upload(self._vb[nm], np.asarray(st[f"v/{nm}"]).reshape(-1))
         if self.dtype == "bf16" and self._my_seg[1] > 0:
-            s0, sl = self._my_seg
-            self.eng.run([op(CAST, a=self.a_master, c=self.eng.view(self.a_mirror, s0 * 2, sl * 2), m=sl, tb=0)])
+            self.eng.run(self._cast_segment())
+        if self.zero:
+            # the other ranks' segments of the bf16 mirror still hold the weights this object was built with:
+            # every owner publishes its freshly cast segment, so the first step after a resume computes from the
+            # restored weights everywhere (collective: every rank calls load_state_dict)
+            self.eng.run(self._mirror_bcast_ops())
         self.eng.upload(self.b_t, np.asarray(st["_t"], dtype=np.float32).reshape(-1))
         self.set_lr(float(np.asarray(st["_lr"]).reshape(-1)[0]))
 

@@ -56,6 +56,7 @@ struct Engine {
     int last_op_rc = 0;
 };
 static Engine G;
+int ax_variant = 0;
 
 static void set_err(const char* fmt, ...) {
     va_list ap; va_start(ap, fmt);
@@ -132,6 +133,7 @@ API int eng_set_fallback(int mask) {
     return 0;
 }
 API long long eng_bytes_allocated(void) { return G.bytes; }
+API int eng_last_variant(void) { return ax_variant; }
 API int eng_sync(void) {
     int rc = (int)cudaStreamSynchronize(G.stream);
     if (!rc) rc = (int)cudaStreamSynchronize(G.comm_stream);
@@ -327,6 +329,9 @@ static int do_gemm(const EngOp* op, bool ex) {
     const int m = op->m, n = op->n, k = op->k;
     const int batch = op->batch > 0 ? op->batch : 1;
     if (m < 0 || n < 0 || k < 0 || op->tb < 0 || op->tb > 2) { set_err("gemm: bad shape"); return 112; }
+    if (op->oa < 0 || op->ob < 0 || op->oc < 0 || (batch > 1 && (op->sa < 0 || op->sb < 0 || op->sc < 0))) {
+        set_err("gemm: negative offset or batch stride"); return 112;
+    }
     const long long a_el = (long long)m * k, b_el = (long long)k * n, c_el = (long long)m * n;
     NEED(op->a, (op->oa + (long long)(batch - 1) * op->sa + a_el) * ei);
     NEED(op->b, (op->ob + (long long)(batch - 1) * op->sb + b_el) * ei);
@@ -345,6 +350,7 @@ static int do_gemm(const EngOp* op, bool ex) {
         if (rc > 0) { set_err("tensor-core gemm failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
     }
     G.launches++;
+    ax_variant = 0x20;
     return ax_gemm_simt(in_bf, out_bf, op->tb, A, B, C, beta != 0.f ? D : nullptr, m, n, k, batch,
                         op->sa, op->sb, op->sc, alpha, beta, G.cur);
 }
@@ -433,6 +439,12 @@ static AttnShape shape_bthd(int B, int H, int KV, int T, int DH, float scale) {
     s.kb = (long long)T * KV * DH; s.kh = DH; s.kt = (long long)KV * DH;
     s.db = (long long)T * H; s.dh_ = 1; s.dtk = H;
     return s;
+}
+
+// rows of an embedding table (or of its gradient) that fit the buffer: ids are checked against it on the device
+static int table_rows(int idx, int dim, long long elsize) {
+    const long long r = dim > 0 ? G.bufs[idx].bytes / ((long long)dim * elsize) : 0;
+    return r > 0x7fffffffLL ? 0x7fffffff : (int)r;
 }
 
 static int exec_op(const EngOp* op) {
@@ -584,19 +596,22 @@ static int exec_op(const EngOp* op) {
             const long long el = (long long)op->m * op->n;
             NEED(op->b, (long long)op->m * 4); NEED(op->c, el * es); NEED(op->a, (long long)op->n * es);
             G.launches++;
-            return ax_embed(dt, BUFP(op->a), BUFP(op->b), op->kind == ENG_EMBED_I32, BUFP(op->c), op->m, op->n, st);
+            return ax_embed(dt, BUFP(op->a), BUFP(op->b), op->kind == ENG_EMBED_I32, BUFP(op->c), op->m, op->n,
+                            table_rows(op->a, op->n, es), G.d_status, st);
         }
         case ENG_EMBED_BWD: {
             const long long el = (long long)op->m * op->n;
             NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->b, (long long)op->m * 4); NEED(op->c, (long long)op->n * 4);
             G.launches++;
-            return ax_embed_bwd_atomic(dt >= 1, BUFP(op->a), (const float*)BUFP(op->b), (float*)BUFP(op->c), op->m, op->n, st);
+            return ax_embed_bwd_atomic(dt >= 1, BUFP(op->a), (const float*)BUFP(op->b), (float*)BUFP(op->c), op->m, op->n,
+                                       table_rows(op->c, op->n, 4), G.d_status, st);
         }
         case ENG_EMBED_BWD_DET: {
             const long long el = (long long)op->m * op->n;
             NEED(op->a, el * (dt >= 1 ? 2 : 4)); NEED(op->b, (long long)op->m * 4); NEED(op->c, (long long)op->n * 4);
             G.launches++;
-            return ax_embed_bwd_det(dt, BUFP(op->a), (const int*)BUFP(op->b), (float*)BUFP(op->c), op->m, op->n, st);
+            return ax_embed_bwd_det(dt, BUFP(op->a), (const int*)BUFP(op->b), (float*)BUFP(op->c), op->m, op->n,
+                                    table_rows(op->c, op->n, 4), G.d_status, st);
         }
         case ENG_COUNTVALID:
             NEED(op->a, (long long)op->m * 4); NEED(op->c, 4);
@@ -608,7 +623,7 @@ static int exec_op(const EngOp* op) {
             const float* den = nullptr;
             if (op->sa > 0) { NEED(op->sa, 4); den = (const float*)BUFP(op->sa); }
             G.launches++;
-            return ax_ce(dt, BUFP(op->a), (const float*)BUFP(op->b), BUFP(op->c), (float*)BUFP(op->d), den, op->m, op->n, st);
+            return ax_ce(dt, BUFP(op->a), (const float*)BUFP(op->b), BUFP(op->c), (float*)BUFP(op->d), den, op->m, op->n, G.d_status, st);
         }
         case ENG_CE_FUSED: {
             // a=logits b=targets(int32) c=dlogits d=loss; sa=denom; sb=scratch (N+8 floats); m=N n=V
@@ -617,7 +632,7 @@ static int exec_op(const EngOp* op) {
             NEED(op->sa, 4); NEED(op->sb, ((long long)op->m + 8) * 4);
             G.launches += 2;
             return ax_ce_fused(dt, BUFP(op->a), (const int*)BUFP(op->b), BUFP(op->c), (float*)BUFP(op->d),
-                               (float*)BUFP(op->sa), (float*)BUFP(op->sb), op->m, op->n, st);
+                               (float*)BUFP(op->sa), (float*)BUFP(op->sb), op->m, op->n, G.d_status, st);
         }
         case ENG_TICK:
             NEED(op->a, 4);

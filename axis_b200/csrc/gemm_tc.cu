@@ -354,12 +354,13 @@ int ax_gemm_tc(int out_bf16, int tb, const void* A, const void* B, void* C, cons
         }
         if (g_pair_mode == 2 || best2 < best) {
             const int rc = ax_gemm_tc2(out_bf16, tb, A, B, C, D, m, n, k, alpha, beta, status, best2_s, st);
-            if (rc >= 0) return rc;
+            if (rc >= 0) { ax_variant = 0x22 + 0x100 * best2_s; return rc; }
         }
     }
 #define GL(BN_, AM, BMj)                                                                                       \
     (out_bf16 ? gemm_launch<BN_, AM, BMj, bf16>(A, B, C, D, m, n, k, alpha, beta, status, ks, st)            \
               : gemm_launch<BN_, AM, BMj, float>(A, B, C, D, m, n, k, alpha, beta, status, ks, st))
+    ax_variant = 0x21 + 0x100 * ks;
     if (tb == 0) return use256 ? GL(256, 0, 1) : GL(128, 0, 1);
     if (tb == 1) return use256 ? GL(256, 0, 0) : GL(128, 0, 0);
     return use256 ? GL(256, 1, 1) : GL(128, 1, 1);

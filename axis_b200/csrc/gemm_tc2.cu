@@ -130,10 +130,14 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     // tma_out == 2: the addend D is fetched the same way (TMA tile loads through tmD, two pieces ahead, into
     // the staging buffer where the result then replaces it); the operand ring then runs with five stages and
     // the sixth stage's memory doubles the staging area (four buffers per epilogue warp).
-    // prof (optional, normally null): clock64 stamps of pair 0's leader CTA — [0] entry, [1] set-up done,
-    // [2] predecessor grid finished, [3] first operands landed, [4] last MMA issued, [5] last accumulator
-    // complete, [6] last tile stored, [7] exit
+    // prof (only in builds with -DAXENG_PROF, otherwise null and every stamp compiles out): clock64 stamps of
+    // pair 0's leader CTA — [0] entry, [1] set-up done, [2] predecessor grid finished, [3] first operands landed,
+    // [4] last MMA issued, [5] last accumulator complete, [6] last tile stored, [7] exit
+#ifdef AXENG_PROF
     const bool timing = prof != nullptr && blockIdx.x == 0;
+#else
+    constexpr bool timing = false;
+#endif
     if (timing && threadIdx.x == 0) prof[0] = clock64();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -614,11 +618,14 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = ax_gemm_pdl() ? 2 : 1;
     TO* Cp = (TO*)C[0]; const TO* Dp = (const TO*)D;
-    static const bool want_prof = getenv("AXENG_GEMM_PROF") != nullptr;     // debugging aid, prints to stderr
     long long* prof = nullptr;
+#ifdef AXENG_PROF       // debugging aid of instrumented builds: allocates, synchronises and prints per launch
+    static const bool want_prof = getenv("AXENG_GEMM_PROF") != nullptr;
     if (want_prof && (cudaMalloc(&prof, 64) != cudaSuccess || cudaMemset(prof, 0, 64) != cudaSuccess)) prof = nullptr;
+#endif
     if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA[0], tmB[0], tmC[0], tmD, tmA[1], tmA[2], tmB[1], tmB[2], tmC[1], tmC[2],
                            grp, tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
+#ifdef AXENG_PROF
     if (prof) {
         long long h[8];
         cudaStreamSynchronize(st);
@@ -627,6 +634,7 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
         fprintf(stderr, "gemm2 %dx%dx%d mode %d split %d pairs %d (cycles from entry): setup %lld dep %lld first_full %lld last_mma %lld last_acc %lld stored %lld exit %lld\n",
                 m, n, k, mode, ksplit, pairs, h[1] - h[0], h[2] - h[0], h[3] - h[0], h[4] - h[0], h[5] - h[0], h[6] - h[0], h[7] - h[0]);
     }
+#endif
     if (ksplit > 1) ax_splitk_reduce_launch<TO>(ws, ksplit, Cp, Dp, (long long)m * n, alpha, beta, st);
     return 0;
 }

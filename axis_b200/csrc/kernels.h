@@ -6,6 +6,12 @@
 
 // dt: 0 = fp32 storage, 1 = bf16 storage (2 = bf16 in / fp32 out where stated)
 
+// Code of the kernel variant the last multi-variant launcher chose (read through eng_last_variant; the parity
+// tests assert with it that a shape really ran on the kernel they mean to check):
+//   0x10 cross-entropy streaming rows, 0x11 cross-entropy register-resident rows,
+//   0x20 general GEMM, 0x21 single-CTA tcgen05 GEMM, 0x22 paired-CTA tcgen05 GEMM (+ 0x100 * split-K factor)
+extern int ax_variant;
+
 // elementwise.cu
 int ax_binary(int which, int dt, const void* a, const void* b, void* c, long long n, cudaStream_t st); // 0 add 1 mul 2 silu_mul
 int ax_scale(int dt, const void* a, void* c, float alpha, long long n, cudaStream_t st);
@@ -38,14 +44,16 @@ int ax_colsum_batch(const float* scratch, float* arena, const int* table, int fi
                     long long arena_elems, int* status, cudaStream_t st);
 
 // loss.cu
-int ax_embed(int dt, const void* table, const void* ids, int ids_i32, void* o, int N, int D, cudaStream_t st);
-int ax_embed_bwd_atomic(int g_bf16, const void* g, const float* ids, float* dT, int N, int D, cudaStream_t st);
-int ax_embed_bwd_det(int g_dt, const void* g, const int* ids, float* dT, int N, int D, cudaStream_t st);
+// rows = rows of the table (derived from its buffer size by the caller): an id or target outside its range is
+// skipped and recorded in the status word (0x401 gather, 0x402 scatter, 0x403 cross-entropy target)
+int ax_embed(int dt, const void* table, const void* ids, int ids_i32, void* o, int N, int D, int rows, int* status, cudaStream_t st);
+int ax_embed_bwd_atomic(int g_bf16, const void* g, const float* ids, float* dT, int N, int D, int rows, int* status, cudaStream_t st);
+int ax_embed_bwd_det(int g_dt, const void* g, const int* ids, float* dT, int N, int D, int rows, int* status, cudaStream_t st);
 int ax_countvalid(const float* tgt, float* acc, int N, cudaStream_t st);
-int ax_ce(int dt, const void* logits, const float* tgt, void* dlogits, float* loss, const float* denom, int N, int V, cudaStream_t st);
+int ax_ce(int dt, const void* logits, const float* tgt, void* dlogits, float* loss, const float* denom, int N, int V, int* status, cudaStream_t st);
 // scratch: N + 8 floats. targets int32 (<0 ignored). loss[0] = mean NLL over valid, denom[0] = count.
 int ax_ce_fused(int dt, const void* logits, const int* tgt, void* dlogits, float* loss, float* denom,
-                float* scratch, int N, int V, cudaStream_t st);
+                float* scratch, int N, int V, int* status, cudaStream_t st);
 
 // optim.cu
 int ax_adamw(float* p, const float* g, float* m, float* v, const float* tbuf, void* pbf,

@@ -6,47 +6,61 @@
 #include "kernels.h"
 
 // ── embedding gather: o[r,:] = table[ids[r],:] ─────────────────────────────
+// An id outside [0, rows) never reaches the table: its output row is zero-filled and the status word is set.
+#define STAT_INDEX 0x400       // + 1 gather id, 2 scatter id, 3 cross-entropy target
 template <typename T, typename I, int W>
 __global__ void k_embed(const T* __restrict__ table, const I* __restrict__ ids, T* __restrict__ o,
-                        int N, int Dw) {
+                        int N, int Dw, int rows, int* status) {
     const long long total = (long long)N * Dw;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int r = (int)(i / Dw), j = (int)(i % Dw);
-        const long long src = (long long)((int)ids[r]) * Dw + j;
+        const int id = (int)ids[r];
+        if (id < 0 || id >= rows) {
+            if (j == 0 && status) atomicExch(status, STAT_INDEX | 1);
+            if (W == 1) o[i] = T(0.f);
+            else reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const long long src = (long long)id * Dw + j;
         if (W == 1) o[i] = table[src];
         else reinterpret_cast<uint4*>(o)[i] = reinterpret_cast<const uint4*>(table)[src];
     }
 }
 template <typename T, typename I>
-static void embed_launch(const void* table, const void* ids, void* o, int N, int D, cudaStream_t st) {
+static void embed_launch(const void* table, const void* ids, void* o, int N, int D, int rows, int* status, cudaStream_t st) {
     constexpr int per = 16 / sizeof(T);
     if (D % per == 0 && aligned16(table) && aligned16(o))
-        k_embed<T, I, per><<<ew_grid((long long)N * (D / per), 256), 256, 0, st>>>((const T*)table, (const I*)ids, (T*)o, N, D / per);
+        k_embed<T, I, per><<<ew_grid((long long)N * (D / per), 256), 256, 0, st>>>((const T*)table, (const I*)ids, (T*)o, N, D / per, rows, status);
     else
-        k_embed<T, I, 1><<<ew_grid((long long)N * D, 256), 256, 0, st>>>((const T*)table, (const I*)ids, (T*)o, N, D);
+        k_embed<T, I, 1><<<ew_grid((long long)N * D, 256), 256, 0, st>>>((const T*)table, (const I*)ids, (T*)o, N, D, rows, status);
 }
-int ax_embed(int dt, const void* table, const void* ids, int ids_i32, void* o, int N, int D, cudaStream_t st) {
+int ax_embed(int dt, const void* table, const void* ids, int ids_i32, void* o, int N, int D, int rows, int* status, cudaStream_t st) {
     if (N <= 0 || D <= 0) return 0;
-    if (dt == 1) { if (ids_i32) embed_launch<bf16, int>(table, ids, o, N, D, st); else embed_launch<bf16, float>(table, ids, o, N, D, st); }
-    else { if (ids_i32) embed_launch<float, int>(table, ids, o, N, D, st); else embed_launch<float, float>(table, ids, o, N, D, st); }
+    if (dt == 1) { if (ids_i32) embed_launch<bf16, int>(table, ids, o, N, D, rows, status, st); else embed_launch<bf16, float>(table, ids, o, N, D, rows, status, st); }
+    else { if (ids_i32) embed_launch<float, int>(table, ids, o, N, D, rows, status, st); else embed_launch<float, float>(table, ids, o, N, D, rows, status, st); }
     return 0;
 }
 
 // ── scatter-add with fp32 atomics (reference ABI; summation order varies) ──
 template <typename T>
-__global__ void k_embed_bwd_atomic(const T* g, const float* ids, float* dT, int N, int D) {
+__global__ void k_embed_bwd_atomic(const T* g, const float* ids, float* dT, int N, int D, int rows, int* status) {
     const long long total = (long long)N * D;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int r = (int)(i / D), j = (int)(i % D);
-        atomicAdd(&dT[(long long)((int)ids[r]) * D + j], ldf(g, i));
+        const int id = (int)ids[r];
+        if (id < 0 || id >= rows) {                     // the row is skipped, the table gradient untouched
+            if (j == 0 && status) atomicExch(status, STAT_INDEX | 2);
+            continue;
+        }
+        atomicAdd(&dT[(long long)id * D + j], ldf(g, i));
     }
 }
-int ax_embed_bwd_atomic(int g_bf16, const void* g, const float* ids, float* dT, int N, int D, cudaStream_t st) {
+int ax_embed_bwd_atomic(int g_bf16, const void* g, const float* ids, float* dT, int N, int D, int rows, int* status, cudaStream_t st) {
     if (N <= 0 || D <= 0) return 0;
-    if (g_bf16) k_embed_bwd_atomic<bf16><<<ew_grid((long long)N * D, 256), 256, 0, st>>>((const bf16*)g, ids, dT, N, D);
-    else k_embed_bwd_atomic<float><<<ew_grid((long long)N * D, 256), 256, 0, st>>>((const float*)g, ids, dT, N, D);
+    if (g_bf16) k_embed_bwd_atomic<bf16><<<ew_grid((long long)N * D, 256), 256, 0, st>>>((const bf16*)g, ids, dT, N, D, rows, status);
+    else k_embed_bwd_atomic<float><<<ew_grid((long long)N * D, 256), 256, 0, st>>>((const float*)g, ids, dT, N, D, rows, status);
     return 0;
 }
 
@@ -55,7 +69,7 @@ int ax_embed_bwd_atomic(int g_bf16, const void* g, const float* ids, float* dT, 
 // walks the later occurrences in row order and adds their gradient rows to
 // dT[token] — the same order as a sequential scatter-add, every run.
 template <typename T>
-__global__ void k_embed_bwd_det(const T* __restrict__ g, const int* __restrict__ ids, float* dT, int N, int D) {
+__global__ void k_embed_bwd_det(const T* __restrict__ g, const int* __restrict__ ids, float* dT, int N, int D, int rows, int* status) {
     __shared__ int s_flag;
     __shared__ int s_list[256];
     __shared__ int s_cnt;
@@ -70,7 +84,8 @@ __global__ void k_embed_bwd_det(const T* __restrict__ g, const int* __restrict__
         __syncthreads();
         const bool first = s_flag == 0;
         __syncthreads();
-        if (!first || tok < 0) continue;
+        if (tok >= rows && first && threadIdx.x == 0 && status) atomicExch(status, STAT_INDEX | 2);
+        if (!first || tok < 0 || tok >= rows) continue;      // ids outside the table are skipped, nothing is written
         // gather the occurrences >= r in order, 256 at a time
         for (int base = r; base < N; base += 256) {
             if (threadIdx.x == 0) s_cnt = 0;
@@ -98,11 +113,11 @@ __global__ void k_embed_bwd_det(const T* __restrict__ g, const int* __restrict__
         }
     }
 }
-int ax_embed_bwd_det(int g_dt, const void* g, const int* ids, float* dT, int N, int D, cudaStream_t st) {
+int ax_embed_bwd_det(int g_dt, const void* g, const int* ids, float* dT, int N, int D, int rows, int* status, cudaStream_t st) {
     if (N <= 0 || D <= 0) return 0;
     const int grid = N < AX_SMS * 16 ? N : AX_SMS * 16;
-    if (g_dt >= 1) k_embed_bwd_det<bf16><<<grid, 256, 0, st>>>((const bf16*)g, ids, dT, N, D);
-    else k_embed_bwd_det<float><<<grid, 256, 0, st>>>((const float*)g, ids, dT, N, D);
+    if (g_dt >= 1) k_embed_bwd_det<bf16><<<grid, 256, 0, st>>>((const bf16*)g, ids, dT, N, D, rows, status);
+    else k_embed_bwd_det<float><<<grid, 256, 0, st>>>((const float*)g, ids, dT, N, D, rows, status);
     return 0;
 }
 
@@ -129,13 +144,17 @@ int ax_countvalid(const float* tgt, float* acc, int N, cudaStream_t st) {
 // Reference ABI (kind CE): fp32 targets, denom buffer optional, loss via one
 // atomicAdd per row.
 template <typename T, bool VEC>
-__global__ void k_ce(const T* logits, const float* tgt, T* dlogits, float* loss, const float* denom, int Nrows, int V) {
+__global__ void k_ce(const T* logits, const float* tgt, T* dlogits, float* loss, const float* denom, int Nrows, int V, int* status) {
     __shared__ float sh[40];
     __shared__ float s_xt;
     for (int r = blockIdx.x; r < Nrows; r += gridDim.x) {
         const T* lr = logits + (long long)r * V;
         T* dr = dlogits + (long long)r * V;
-        const int t = (int)tgt[r];
+        int t = (int)tgt[r];
+        if (t >= V) {                    // a target outside the vocabulary: the row counts as ignored
+            if (threadIdx.x == 0 && status) atomicExch(status, STAT_INDEX | 3);
+            t = -1;
+        }
         if (t < 0) {
             for (int j = threadIdx.x; j < V; j += blockDim.x) stf(dr, j, 0.f);
             continue;
@@ -183,18 +202,18 @@ __global__ void k_ce(const T* logits, const float* tgt, T* dlogits, float* loss,
         __syncthreads();
     }
 }
-int ax_ce(int dt, const void* logits, const float* tgt, void* dlogits, float* loss, const float* denom, int N, int V, cudaStream_t st) {
+int ax_ce(int dt, const void* logits, const float* tgt, void* dlogits, float* loss, const float* denom, int N, int V, int* status, cudaStream_t st) {
     if (N <= 0 || V <= 0) return 0;
     const int per = dt == 1 ? 8 : 4;
     const bool vec = V % per == 0 && aligned16(logits) && aligned16(dlogits);
     const int thr = V >= 4096 ? 512 : 256;
     const int grid = N < AX_SMS * 64 ? N : AX_SMS * 64;
     if (dt == 1) {
-        if (vec) k_ce<bf16, true><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, N, V);
-        else k_ce<bf16, false><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, N, V);
+        if (vec) k_ce<bf16, true><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, N, V, status);
+        else k_ce<bf16, false><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, N, V, status);
     } else {
-        if (vec) k_ce<float, true><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, N, V);
-        else k_ce<float, false><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, N, V);
+        if (vec) k_ce<float, true><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, N, V, status);
+        else k_ce<float, false><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, N, V, status);
     }
     return 0;
 }
@@ -204,10 +223,10 @@ int ax_ce(int dt, const void* logits, const float* tgt, void* dlogits, float* lo
 // as float in denom[0], zeroes the done-counter.  k_ce_rows: as k_ce, but the
 // row keeps its loss term in rowloss[r]; the last block to finish adds the N
 // terms in a fixed order and writes loss[0].
-__global__ void k_ce_prepare(const int* tgt, float* denom, float* loss, unsigned int* counter, int N) {
+__global__ void k_ce_prepare(const int* tgt, float* denom, float* loss, unsigned int* counter, int N, int V) {
     __shared__ int sh_i[32];
     int c = 0;
-    for (int i = threadIdx.x; i < N; i += blockDim.x) c += tgt[i] >= 0;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) c += tgt[i] >= 0 && tgt[i] < V;
     for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
     if ((threadIdx.x & 31) == 0) sh_i[threadIdx.x >> 5] = c;
     __syncthreads();
@@ -221,7 +240,7 @@ __global__ void k_ce_prepare(const int* tgt, float* denom, float* loss, unsigned
 }
 template <typename T, bool VEC>
 __global__ void k_ce_rows(const T* logits, const int* tgt, T* dlogits, float* loss, const float* denom,
-                          float* rowloss, unsigned int* counter, int Nrows, int V) {
+                          float* rowloss, unsigned int* counter, int Nrows, int V, int* status) {
     __shared__ float sh[40];
     __shared__ float s_xt;
     __shared__ bool s_last;
@@ -230,7 +249,11 @@ __global__ void k_ce_rows(const T* logits, const int* tgt, T* dlogits, float* lo
     for (int r = blockIdx.x; r < Nrows; r += gridDim.x) {
         const T* lr = logits + (long long)r * V;
         T* dr = dlogits + (long long)r * V;
-        const int t = tgt[r];
+        int t = tgt[r];
+        if (t >= V) {
+            if (threadIdx.x == 0 && status) atomicExch(status, STAT_INDEX | 3);
+            t = -1;
+        }
         if (t < 0) {
             if (VEC) {
                 float z[N];
@@ -301,7 +324,7 @@ __global__ void k_ce_rows(const T* logits, const int* tgt, T* dlogits, float* lo
 #define CE_VPT 8
 __global__ void __launch_bounds__(512, 2)
 k_ce_rows_reg(const bf16* logits, const int* __restrict__ tgt, bf16* dlogits, float* loss, const float* denom,
-              float* rowloss, unsigned int* counter, int Nrows, int V) {
+              float* rowloss, unsigned int* counter, int Nrows, int V, int* status) {
     __shared__ float sh[40];
     __shared__ float s_xt;
     __shared__ bool s_last;
@@ -310,7 +333,11 @@ k_ce_rows_reg(const bf16* logits, const int* __restrict__ tgt, bf16* dlogits, fl
     for (int r = blockIdx.x; r < Nrows; r += gridDim.x) {
         const bf16* lr = logits + (long long)r * V;
         bf16* dr = dlogits + (long long)r * V;
-        const int t = tgt[r];
+        int t = tgt[r];
+        if (t >= V) {
+            if (threadIdx.x == 0 && status) atomicExch(status, STAT_INDEX | 3);
+            t = -1;
+        }
         if (t < 0) {
             const uint4 z = make_uint4(0, 0, 0, 0);
             for (int j = threadIdx.x; j < nvec; j += 512) reinterpret_cast<uint4*>(dr)[j] = z;
@@ -380,26 +407,28 @@ k_ce_rows_reg(const bf16* logits, const int* __restrict__ tgt, bf16* dlogits, fl
 }
 
 int ax_ce_fused(int dt, const void* logits, const int* tgt, void* dlogits, float* loss, float* denom,
-                float* scratch, int N, int V, cudaStream_t st) {
+                float* scratch, int N, int V, int* status, cudaStream_t st) {
     if (N <= 0 || V <= 0) return 0;
     unsigned int* counter = reinterpret_cast<unsigned int*>(scratch);
     float* rowloss = scratch + 8;
-    k_ce_prepare<<<1, 1024, 0, st>>>(tgt, denom, loss, counter, N);
+    k_ce_prepare<<<1, 1024, 0, st>>>(tgt, denom, loss, counter, N, V);
     const int per = dt == 1 ? 8 : 4;
     const bool vec = V % per == 0 && aligned16(logits) && aligned16(dlogits);
     const int thr = V >= 4096 ? 512 : 256;
     const int grid = N < AX_SMS * 16 ? N : AX_SMS * 16;
+    ax_variant = 0x10;
     if (dt == 1 && vec && V >= 2048 && V <= 512 * 8 * CE_VPT) {
         const int g2 = N < AX_SMS * 8 ? N : AX_SMS * 8;
-        k_ce_rows_reg<<<g2, 512, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V);
+        ax_variant = 0x11;
+        k_ce_rows_reg<<<g2, 512, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V, status);
         return 0;
     }
     if (dt == 1) {
-        if (vec) k_ce_rows<bf16, true><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V);
-        else k_ce_rows<bf16, false><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V);
+        if (vec) k_ce_rows<bf16, true><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V, status);
+        else k_ce_rows<bf16, false><<<grid, thr, 0, st>>>((const bf16*)logits, tgt, (bf16*)dlogits, loss, denom, rowloss, counter, N, V, status);
     } else {
-        if (vec) k_ce_rows<float, true><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, rowloss, counter, N, V);
-        else k_ce_rows<float, false><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, rowloss, counter, N, V);
+        if (vec) k_ce_rows<float, true><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, rowloss, counter, N, V, status);
+        else k_ce_rows<float, false><<<grid, thr, 0, st>>>((const float*)logits, tgt, (float*)dlogits, loss, denom, rowloss, counter, N, V, status);
     }
     return 0;
 }

@@ -652,9 +652,14 @@ int eng_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* g, const v
         if (cudaGetSymbolAddress((void**)&p, g_noalloc_partials) != cudaSuccess || !p) { cudaGetLastError(); return 203; }
         g_noalloc_addr[dev] = p;
     }
+    cudaGetLastError();       // an earlier, unrelated error of this thread must not be reported as this call's (204)
+    if (rows == 0) {          // an empty batch: dx has no rows and the column sums are zero
+        if (dw && cudaMemsetAsync(dw, 0, (size_t)dim * sizeof(float), (cudaStream_t)stream) != cudaSuccess) { cudaGetLastError(); return 204; }
+        return 0;
+    }
     // Nothing in the scratch has to start at zero: the first kernel overwrites rows
     // [0, blocks) x [0, dim) of it and the second reads exactly those.
     const int rc = ax_rmsnorm_bwd_acc(dt, x, w, g, res, dx, dw, g_noalloc_addr[dev], rows, dim, eps, (cudaStream_t)stream, 0);
     if (rc) return rc;
-    return cudaPeekAtLastError() == cudaSuccess ? 0 : 204;
+    return cudaGetLastError() == cudaSuccess ? 0 : 204;
 }

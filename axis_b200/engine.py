@@ -38,6 +38,7 @@ KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "CO
               "EMBED_I32", "REDUCE", "ALLGATHER_F32", "FORK", "JOIN", "STREAM", "SILU_MUL_BWD_RC",
               "GEMM_GROUP", "TRANSPOSE_BF16", "COLSUM_BATCH", "EVENT"]
 
+_I32_MAX = 2 ** 31 - 1
 CHUNK = 1024          # arena granularity of the flat optimizer / collective ops
 GNORM_CHUNK = 8192    # elements per grad-norm partial
 
@@ -125,7 +126,16 @@ class PackedPlan:
         if len(plan):
             cols = list(zip(*plan))
             for j, name in enumerate(_OP_DTYPE.names):
-                arr[name] = np.asarray(cols[j], dtype=np.float32 if j >= 17 else np.int64)
+                if j >= 17:
+                    arr[name] = np.asarray(cols[j], dtype=np.float32)
+                    continue
+                col = np.asarray(cols[j], dtype=np.int64)
+                bad = np.nonzero((col > _I32_MAX) | (col < -_I32_MAX - 1))[0]
+                if bad.size:        # the descriptor's integer fields are 32 bits wide: refuse, never wrap
+                    i = int(bad[0])
+                    raise OverflowError(f"op {i} (kind {plan[i][0]}): field '{name}' = {int(col[i])} does not fit "
+                                        f"the 32-bit op descriptor")
+                arr[name] = col
         self.arr = arr
         self.n = len(plan)
         self.ptr = arr.ctypes.data_as(ctypes.POINTER(_EngOp))
@@ -324,6 +334,10 @@ class Engine:
 
     def device_status(self, clear: bool = True) -> int:
         return int(self.lib.eng_device_status(1 if clear else 0))
+
+    def last_variant(self) -> int:
+        """Code of the kernel variant the last GEMM / cross-entropy op ran on (include/axeng.h)."""
+        return int(self.lib.eng_last_variant())
 
     def bytes_allocated(self) -> int:
         return int(self.lib.eng_bytes_allocated())

@@ -158,6 +158,11 @@ int eng_nccl_init_timeout(int rank, int world, const void* id128, int timeout_ms
 int eng_set_fallback(int mask);
 /* Bytes currently allocated through eng_alloc*. */
 long long eng_bytes_allocated(void);
+/* Code of the kernel variant the last GEMM / cross-entropy op ran on (no counterpart in the reference; lets a
+ * test assert that a shape was served by the kernel it means to check): 0x10 cross-entropy streaming rows,
+ * 0x11 register-resident rows; 0x20 general GEMM, 0x21 single-CTA tcgen05 GEMM, 0x22 paired-CTA tcgen05 GEMM,
+ * the GEMM codes plus 0x100 times the split-K factor. */
+int eng_last_variant(void);
 
 /* Fused RMSNorm backward that allocates nothing (no counterpart in the
  * reference).  dx = (res ? res : 0) + d(rmsnorm)/dx, dw = sum over rows of
@@ -180,6 +185,9 @@ long long eng_bytes_allocated(void);
  * capture.  Every call uses the same array and leaves its partials there;
  * nothing in it has to be cleared between calls, but two calls that overlap on
  * the GPU (different streams, no ordering) race on it — serialise them.
+ * rows == 0 is served: dw (if given) is set to zero, dx is not touched.  The
+ * call clears this thread's pending CUDA error before it launches, so 204
+ * reports only its own launch.
  * Returns 0, or 201 dim too large, 202 bad argument, 203 device/symbol lookup
  * failed, 204 launch failed. */
 int eng_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* g, const void* res, void* dx, float* dw,

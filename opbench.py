@@ -1,15 +1,15 @@
 """Per-kernel micro-benchmark through the C ABI.
 
-    python -m axis_b200.opbench gemm --m 8192 --n 1536 --k 1536 --tb 0 --dt 1
-    python -m axis_b200.opbench attn_bwd --B 4 --H 24 --KV 8 --T 2048 --DH 64
-    python -m axis_b200.opbench rmsnorm_bwd --rows 8192 --dim 1536
-    python -m axis_b200.opbench all            # the step's kernels at the 1B-class shapes
-    python -m axis_b200.opbench rmsnorm --chain 8   # eight instances back to back in one timed plan
+    python opbench.py gemm --m 8192 --n 1536 --k 1536 --tb 0 --dt 1
+    python opbench.py attn_bwd --B 4 --H 24 --KV 8 --T 2048 --DH 64
+    python opbench.py rmsnorm_bwd --rows 8192 --dim 1536
+    python opbench.py all            # the step's kernels at the 1B-class shapes
+    python opbench.py rmsnorm --chain 8   # eight instances back to back in one timed plan
 
 Each run prints one JSON line: mean milliseconds over `--reps` launches (CUDA
 events on the engine stream, L2 flushed between launches unless --no-flush),
 the algorithmic bytes or flops of the op, the achieved GB/s or TFLOP/s and
-its fraction of the measured peak (MEASURED_PEAKS.json beside the package when
+its fraction of the measured peak (MEASURED_PEAKS.json beside this file when
 present, else 6650 GB/s / 1590 TFLOP/s).  `--check` also verifies the result
 against a numpy evaluation on a sample of the output.
 """
@@ -25,7 +25,7 @@ import numpy as np
 from axis_b200 import engine as E
 from axis_b200.engine import Engine, op
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 
 
 def peaks():

@@ -24,7 +24,7 @@ def _data(rank, step):
     return x, np.roll(x, -1, axis=1)
 
 
-def _worker(rank, world, port, zero, dtype, recompute, out):
+def _worker(rank, world, port, zero, dtype, recompute, out, resume_at=0):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     from axis_b200.compile import CompiledTransformer
@@ -37,6 +37,13 @@ def _worker(rank, world, port, zero, dtype, recompute, out):
                              bucket_layers=2, recompute_blocks=recompute)
     losses = []
     for s in range(STEPS):
+        if resume_at and s == resume_at:
+            # save, rebuild from OTHER initial weights, load: the next step must continue the uninterrupted run
+            st = ct.state_dict()
+            ct = CompiledTransformer(InterpEngine(dist), CFG, O.init_weights(CFG, seed=4), B, T, dtype=dtype,
+                                     grad_sync=True, zero_stage=1 if zero else 0, rank=rank, world=world,
+                                     max_grad_norm=1.0, bucket_layers=2, recompute_blocks=recompute)
+            ct.load_state_dict(st)
         losses.append(ct.step(*_data(rank, s)))
     res = {"losses": losses, "owned": ct.owned, "norm": ct.grad_norm(),
            "w": ct.get_weights(), "g": ct.grads() if not zero else {},
@@ -47,19 +54,19 @@ def _worker(rank, world, port, zero, dtype, recompute, out):
     dist.destroy_process_group()
 
 
-def _run(world, zero, dtype, recompute=False):
+def _run(world, zero, dtype, recompute=False, resume_at=0):
     import torch.multiprocessing as mp
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, port, zero, dtype, recompute, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, zero, dtype, recompute, out, resume_at), nprocs=world, join=True)
     return [out[r] for r in range(world)]
 
 
 @pytest.fixture(scope="module")
 def runs():
     return {"dp32": _run(2, False, "fp32"), "dp16": _run(2, False, "bf16"), "z16": _run(2, True, "bf16"),
-            "z16rc": _run(2, True, "bf16", recompute=True)}
+            "z16rc": _run(2, True, "bf16", recompute=True), "z16resume": _run(2, True, "bf16", resume_at=2)}
 
 
 def test_dp_matches_single_process_on_concatenated_batch(runs):
@@ -138,3 +145,16 @@ def test_zero1_with_block_recompute_equals_zero1_bit_for_bit(runs):
         step0 = lambda tr: tr[:tr.index(E.GNORM_FLAT)]
         assert step0(rc[r]["trace"]).count(E.REDUCE) == step0(z[r]["trace"]).count(E.REDUCE)
         assert step0(rc[r]["trace"]).count(E.ATTN_FWD) == 2 * CFG["n_layers"] - 1
+
+
+def test_zero1_resume_continues_the_run_bit_for_bit(runs):
+    """state_dict -> a freshly built step (other initial weights) -> load_state_dict under ZeRO-1: the owners
+    re-publish their bf16 segments, so the step after the resume equals the uninterrupted run's on every rank
+    (engine/modal_zero_test.py:124-131 checks the saved shards; the reference's load leaves the non-owned
+    mirrors stale)."""
+    z, rs = runs["z16"], runs["z16resume"]
+    for r in range(2):
+        assert rs[r]["losses"] == z[r]["losses"]
+        for nm, w in z[r]["w"].items():
+            assert np.array_equal(w, rs[r]["w"][nm]), nm
+        assert np.array_equal(z[r]["mirror"], rs[r]["mirror"])

@@ -353,3 +353,62 @@ def test_rmsnorm_deferred_dw_and_batched_column_sum(eng, dt, dim):
     eng.run([op(E.COLSUM_BATCH, a=scratch, b=table, c=arena, m=1, n=dim, oa=0, k=unit)])
     assert eng.device_status(clear=True) == 130
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [0, 1])
+def test_out_of_range_ids_and_targets_are_skipped_with_a_status(eng, dt):
+    """An id or target that lies inside its int/float buffer but outside the table / vocabulary never reaches
+    memory: the row is skipped (gather: zero-filled) and the device status word carries a code."""
+    rng = np.random.default_rng(7)
+    N, V, D = 12, 20, 16
+    table = rnd(rng, (V, D), dt)
+    ids = rng.integers(0, V, N)
+    bad = ids.copy(); bad[5] = V + 3
+    it, io = put(eng, table, dt), eng.alloc(N * D, 2 if dt else 4)
+    assert eng.device_status() == 0
+    # gather through the reference ABI's fp32-encoded ids
+    eng.run([op(E.EMBED, a=it, b=put(eng, bad.astype(np.float32)), c=io, m=N, n=D, dt=dt)])
+    out = get(eng, io, (N, D), dt)
+    assert eng.device_status() == 0x401
+    ok = np.arange(N) != 5
+    assert np.array_equal(out[ok], table[ids][ok]) and np.all(out[5] == 0)
+    # scatter-add, both forms: the bad row adds nothing anywhere
+    g = rnd(rng, (N, D), dt)
+    ref = O.embedding_bwd(ids[ok], g[ok], V)
+    # the table gradient is a window of V rows at the front of a larger buffer: a wild write would land behind it
+    ig, ipar = put(eng, g, dt), eng.alloc(V * D + 64)
+    idT = eng.view(ipar, 0, V * D * 4)
+    iid = eng.alloc(N); eng.upload_raw(iid, bad.astype(np.int32))
+    for form in ("det", "atomic"):
+        eng.run([op(E.SCALE, a=ipar, c=ipar, n=V * D + 64, alpha=0.0)])
+        if form == "det":
+            eng.run([op(E.EMBED_BWD_DET, a=ig, b=iid, c=idT, m=N, n=D, dt=dt)])
+        else:
+            eng.run([op(E.EMBED_BWD, a=ig, b=put(eng, bad.astype(np.float32)), c=idT, m=N, n=D, dt=2 if dt else 0)])
+        full = eng.download(ipar, V * D + 64)
+        assert eng.device_status() == 0x402
+        assert np.all(full[V * D:] == 0)
+        close(full[:V * D].reshape(V, D), ref, 0)
+    # cross-entropy: a target >= V counts as ignored and is reported
+    logits = rnd(rng, (N, V), dt)
+    tgt = rng.integers(0, V, N); tgt[3] = -1
+    tbad = tgt.copy(); tbad[8] = V + 1
+    tref = tgt.copy(); tref[8] = -1
+    loss, dl, cnt = O.cross_entropy_fwd_bwd(logits, tref, -1)
+    il, itg = put(eng, logits, dt), eng.alloc(N)
+    eng.upload_raw(itg, tbad.astype(np.int32))
+    iloss, iden, iscr = eng.alloc(1), eng.alloc(1), eng.alloc(N + 8)
+    eng.run([op(E.CE_FUSED, a=il, b=itg, c=il, d=iloss, sa=iden, sb=iscr, m=N, n=V, dt=dt)])
+    assert eng.device_status() == 0x403
+    assert eng.download(iden, 1)[0] == cnt
+    assert abs(eng.download(iloss, 1)[0] - loss) <= 1e-5 * abs(loss)
+    close(get(eng, il, (N, V), dt), dl, dt)
+
+
+def test_gemm_rejects_negative_offsets_and_strides(eng):
+    a, b, c = eng.alloc(64), eng.alloc(64), eng.alloc(64)
+    for bad in (dict(oa=-8), dict(ob=-1), dict(oc=-4), dict(batch=2, sa=-16, sb=0, sc=0)):
+        kw = dict(a=a, b=b, c=c, m=4, n=4, k=4, batch=1)
+        kw.update(bad)
+        with pytest.raises(RuntimeError, match="rc=1000"):
+            eng.run([op(E.GEMM_SB, **kw)])

@@ -315,3 +315,75 @@ def test_side_stream_weight_gradients_are_ordered_by_events(world):
     for kw2 in (dict(lora_r=4), dict(recompute_blocks=True), dict(overlap_dw=False)):
         c2 = CompiledTransformer(InterpEngine(), cfg, w0, 2, 8, dtype="bf16", **kw2)
         assert not c2.overlap_dw and not any(o[0] == E.EVENT for o in c2.plan_step)
+
+
+class _ShapeOnlyEngine:
+    """Engine stand-in that holds no data: it hands out slots, tracks sizes and packs every plan it is given, so
+    a 7B-class buffer plan and op plan can be built and checked on a small host."""
+    has_flash = True
+
+    def __init__(self):
+        self.sizes, self.ran = [], []
+
+    def alloc(self, nelems, itemsize=4):
+        self.sizes.append(int(nelems) * itemsize)
+        return len(self.sizes) - 1
+
+    def alloc_zero(self, nbytes):
+        self.sizes.append(int(nbytes))
+        return len(self.sizes) - 1
+
+    def view(self, parent, byte_offset, nbytes):
+        assert 0 <= byte_offset and byte_offset + nbytes <= self.sizes[parent]
+        self.sizes.append(int(nbytes))
+        return len(self.sizes) - 1
+
+    def new_tensor(self, arr):
+        return self.alloc(arr.size)
+
+    def run(self, plan, sync=True):
+        from axis_b200.engine import PackedPlan
+        self.ran.append((list(plan), PackedPlan(plan)))
+
+    def upload(self, *a): pass
+    def upload_raw(self, *a, **k): pass
+    def set_tf32(self, *a): pass
+
+
+class _ShapeOnlyWeight:
+    def __init__(self, shape):
+        self.shape = tuple(shape)
+
+    def load_into(self, eng, dst, fp32_out, stage):
+        pass
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_7b_plan_fits_the_32bit_op_descriptor(world):
+    """The 7B-class arenas hold more elements than an int32: every integer field of every op of the plan, and of
+    the set-up ops the constructor runs (master -> bf16 mirror cast), must survive packing unchanged."""
+    from axis_b200 import engine as E
+    V, D, L, H, MLP = 32000, 4096, 32, 32, 11008
+    cfg = dict(vocab_size=V, dim=D, n_layers=L, n_heads=H, n_kv_heads=H, mlp_hidden=MLP, tie_embeddings=True)
+    shapes = {"embed.weight": (V, D), "norm.weight": (D,)}
+    for i in range(L):
+        p = f"blocks.{i}."
+        shapes.update({p + "attn_norm.weight": (D,), p + "mlp_norm.weight": (D,),
+                       p + "attn.q_proj.weight": (D, D), p + "attn.k_proj.weight": (D, D),
+                       p + "attn.v_proj.weight": (D, D), p + "attn.o_proj.weight": (D, D),
+                       p + "mlp.gate_proj.weight": (D, MLP), p + "mlp.up_proj.weight": (D, MLP),
+                       p + "mlp.down_proj.weight": (MLP, D)})
+    eng = _ShapeOnlyEngine()
+    ct = CompiledTransformer(eng, cfg, {n: _ShapeOnlyWeight(s) for n, s in shapes.items()}, 2, 4096, dtype="bf16",
+                             max_grad_norm=1.0, grad_sync=world > 1, zero_stage=1 if world > 1 else 0, rank=0, world=world)
+    assert ct._P_total > 2 ** 31 or world > 1
+    # the constructor's cast of the owned segment: element count carried as chunks x CHUNK
+    casts = [o for plan, _ in eng.ran for o in plan if o[0] == E.CAST]
+    assert sum(o[5] * max(o[6], 1) for o in casts) == ct._my_seg[1]
+    for plan in (ct.plan_step, ct.plan_fb, ct.plan_ar):
+        pp = E.PackedPlan(plan)
+        for j, name in enumerate(E._OP_DTYPE.names[:17]):
+            assert [int(v) for v in pp.arr[name]] == [int(o[j]) for o in plan], name
+    # and the packer refuses what it cannot represent instead of wrapping
+    with pytest.raises(OverflowError):
+        E.PackedPlan([E.op(E.CAST, a=0, c=1, m=ct._P_total if ct._P_total > 2 ** 31 else 2 ** 31 + 5)])

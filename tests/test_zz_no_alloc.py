@@ -17,6 +17,7 @@ import pytest
 
 from axis_b200 import engine as E
 from axis_b200.engine import Engine, op
+from oracle import step_numpy as O
 
 pytestmark = pytest.mark.gpu
 
@@ -64,6 +65,18 @@ def test_noalloc_matches_regular_entry_point_twice(dt):
         tol = 1.2e-2 if dt else 2e-5
         assert np.abs(dx - dx_ref).max() <= tol * (np.abs(dx_ref).max() + 1e-6)
         assert np.abs(dw - dw_ref).max() <= tol * (np.abs(dw_ref).max() + 1e-6)
+        # and against the CPU oracle's RMSNorm backward (plus the residual that the op adds to dx)
+        _, inv = O.rmsnorm_fwd(x, w, 1e-5)
+        dx_o, dw_o = O.rmsnorm_bwd(x, w, inv, g)
+        assert np.abs(dx - (dx_o + res)).max() <= tol * (np.abs(dx_o + res).max() + 1e-6)
+        assert np.abs(dw - dw_o).max() <= tol * (np.abs(dw_o).max() + 1e-6)
+    # an empty batch: the column sums are zero and are written as such, dx is left alone
+    tdw.fill_(7.0)
+    torch.cuda.synchronize()
+    assert fn(tx.data_ptr(), tw.data_ptr(), tg.data_ptr(), None, tdx.data_ptr(), tdw.data_ptr(), 0, dim, dt, 1e-5,
+              ctypes.c_void_p(stream)) == 0
+    torch.cuda.synchronize()
+    assert float(tdw.abs().max()) == 0.0
     # sizes beyond the built-in scratch are refused, not truncated
     assert fn(tx.data_ptr(), tw.data_ptr(), tg.data_ptr(), None, tdx.data_ptr(), None, 1, 8193, dt, 1e-5, None) == 201
     assert fn(None, tw.data_ptr(), tg.data_ptr(), None, tdx.data_ptr(), None, 1, 64, dt, 1e-5, None) == 202
