@@ -18,7 +18,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIBDIR = os.path.join(HERE, "_lib")
+LIBDIR = os.path.join(HERE, "_lib_prof" if os.environ.get("AXENG_BUILD_PROF") else "_lib")
 LIB = os.path.join(LIBDIR, "libaxeng.so")
 SOURCES = ["axeng.cu", "elementwise.cu", "norm.cu", "loss.cu", "optim.cu", "gemm_simt.cu",
            "gemm_tc.cu", "gemm_tc2.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc128.cu"]

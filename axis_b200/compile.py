@@ -527,11 +527,12 @@ class CompiledTransformer:
             plan += norm_b(r1s[i], p + "mlp_norm.weight", dz, dcur, dr1)
             plan += lin_b(dr1, at2s[i], i, "attn.o_proj", dat2)
             plan += before_write(dq, dk, dv)
+            # the inverse rotary of dq and dk is part of the op (beta / gamma name the cos / sin tables): the
+            # tensor-core backward applies it before it rounds to bf16, other paths run the rotary kernel behind it
             plan += [
                 op(ATTN_BWD, a=q2s[i], b=k2s[i], d=vs[i], c=dat2, sa=lses[i], sb=at2s[i],
-                   tb=dq, sc=dk, oa=dv, ob=H, oc=bD, m=T, n=DH, k=KV, batch=B, dt=DT, alpha=scale),
-                op(ROPE_BTHD, a=dq, b=b_cos, d=b_sin, c=dq, batch=B, m=T, k=H, n=DH, tb=1, dt=DT,
-                   sa=dk, sb=dk, sc=KV),
+                   tb=dq, sc=dk, oa=dv, ob=H, oc=bD, m=T, n=DH, k=KV, batch=B, dt=DT, alpha=scale,
+                   beta=float(b_cos), gamma=float(b_sin)),
             ]
             plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
             plan += before_write(dcur)

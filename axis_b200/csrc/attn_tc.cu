@@ -18,9 +18,12 @@
 // Every mbarrier wait is bounded; on a timeout the kernel records a status
 // code, unwinds and frees its TMEM.
 #include <cuda_bf16.h>
+
+#ifdef AXENG_PROF
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
+#endif
 
 #include "common.cuh"
 #include "kernels.h"
@@ -257,46 +260,101 @@ __global__ void k_attn_bwd_prep(const bf16* __restrict__ o, const bf16* __restri
     }
 }
 
-// Backward CTA: two softmax groups of 4 warps (group e owns the sub-tiles of parity e and TMEM buffer e; a
-// thread owns one key row and all 64 query columns of its sub-tile), 4 warps that move finished dQ tiles out
-// (TMEM -> shared memory -> TMA reduce-add), 1 MMA-issue warp, 1 TMA-load warp.
-#define BWD_SM_WARPS 8
+// Backward CTA (800 threads): sixteen softmax warps — two groups (group e owns the sub-tiles of parity e and the
+// TMEM buffers e), each of two column halves times four lane quarters, so that a thread owns one key row and 32
+// of the 64 query columns of its sub-tile — 4 warps that move finished dQ tiles out (TMEM -> shared memory -> TMA
+// reduce-add), 5 MMA-issue warps (one per product; the S^T issuer also feeds the Q / dO ring by TMA).  Four softmax warps per scheduler hide the 250-cycle
+// round trip of a TMEM load behind each other's arithmetic.
+//
+// The backward works on sub-tiles of 64 queries.  An MMA whose two operands both come from shared memory is
+// bound by the operand fetch, not the math (a 128 x 64 x 16 step reads 6 KB for 32 cycles of math and takes
+// about three times that), so every product that can takes its 128-row operand from TMEM instead:
+//   K, V              copied once into TMEM as packed bf16 (32 columns each): the A operands of S^T = K Q^T and
+//                     dP^T = V dO^T; only the 64-query Q / dO tiles are read from shared memory.
+//   S^T[e], dP^T[e]   fp32 scores of sub-tile u (e = u & 1); P^T and dS^T replace them in place as packed bf16
+//                     (columns 0..31) and are the A operands of dV += P^T dO and dK += dS^T Q.
+//   dS^T              also goes to shared memory (swizzled rows of 64 queries): the M-major A operand of
+//                     dQ = dS K per 128-query tile, the one product with both operands in shared memory.
+//   dV, dK, dQ        accumulators; dQ is single: the movers drain tile t while the sub-tiles of t+1 run.
+// Every product has its own issuing warp, each in program order behind its own barriers: a warp issues one small
+// MMA about every 50 cycles in this code, and the batches of a sub-tile (S^T and dP^T; dV and dK) sit on the
+// critical path between two softmax passes, so they are issued side by side instead of one after the other.
+// A softmax thread takes its 32 columns in two rounds of 16 (S^T and dP^T loaded together, P^T and dS^T written
+// back in place), with packed fp32x2 arithmetic.
+#define BWD_SM_WARPS 16
 #define BWD_SM_THREADS (BWD_SM_WARPS * 32)
 #define BWD_DRAIN_THREADS 128
-#define BWD_THREADS (BWD_SM_THREADS + BWD_DRAIN_THREADS + 64)
-// The backward works on sub-tiles of 64 queries so that the tensor pipe and the softmax warps overlap:
-// while one group turns S^T/dP^T of sub-tile u into P^T/dS^T, the other group does the same for sub-tile
-// u+1, and the tensor cores compute dV/dK/dQ of earlier sub-tiles and S^T/dP^T of later ones.
+#define BWD_THREADS (BWD_SM_THREADS + BWD_DRAIN_THREADS + 160)
+#define BWD_SLOTS 5            // Q/dO ring: 64-query sub-tiles in flight
 struct BwdSmem {
-    static constexpr int K = 0, V = 16384, Q0 = 32768, DO0 = Q0 + 4 * 8192, DS0 = DO0 + 4 * 8192, DQ = DS0 + 2 * 32768,
-                         STAT = DQ + 32768, BARS = STAT + 8192, TOTAL = BARS + 256 + 1024;
+    static constexpr int K = 0, V = 16384, Q0 = 32768, DO0 = Q0 + BWD_SLOTS * 8192, DS0 = DO0 + BWD_SLOTS * 8192,
+                         DQ = DS0 + 2 * 32768, STAT = DQ + 32768, BARS = STAT + 8192, TOTAL = BARS + 512 + 1024;
 };
+static_assert(BwdSmem::TOTAL <= 227 * 1024, "backward shared memory exceeds the per-CTA limit");
+static_assert(BwdSmem::DO0 % 1024 == 0 && BwdSmem::DS0 % 1024 == 0 && BwdSmem::DQ % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
 }
 
+// Issue forms for a converged warp: every lane executes the surrounding code (so addresses and descriptors stay
+// warp-uniform and cheap to form) and the elected lane issues.  Measured on B200: a 128 x 64 x 16 MMA with A in
+// TMEM issues every 32.6 cycles this way (its 32 cycles of math) against 45-50 from a lone thread in a divergent branch.
+__device__ __forceinline__ void mma_ts_e(uint32_t d, uint32_t a, uint64_t bd, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a), "l"(bd), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_ss_e(uint32_t d, uint64_t ad, uint64_t bd, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(ad), "l"(bd), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void commit_e(uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
+}
+
+#ifdef AXENG_PROF
+// instrumented builds only: per-CTA cycle counters (16 long long per CTA), see the host launcher
+__device__ long long* g_bwd_prof = nullptr;
+#define PROF_T() clock64()
+#define PROF_ADD(slot, v) do { pa[slot] += (v); } while (0)
+#define PROF_FLUSH(lo, hi) do { if (pf) for (int q_ = (lo); q_ < (hi); q_++) pf[q_] = pa[q_]; } while (0)
+#else
+#define PROF_T() 0ll
+#define PROF_ADD(slot, v) do { } while (0)
+#define PROF_FLUSH(lo, hi) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
               const __grid_constant__ CUtensorMap tmdQ, const float* __restrict__ lse, const float* __restrict__ Dv,
-              bf16* __restrict__ dk, bf16* __restrict__ dv, int T, int H, int KV, float scale, int* status,
-              long long* prof) {
-    // prof (optional, normally null): per-CTA cycle counts of the phases of softmax thread 0 —
-    // [0] wait S/dP, [1] softmax + stores, [2] wait for the dS buffer, [3] unused, [4] total, [5] query tiles
+              bf16* __restrict__ dk, bf16* __restrict__ dv, int T, int H, int KV, float scale,
+              const float* __restrict__ rope_cos, const float* __restrict__ rope_sin, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sb = smem_u32(smem);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BwdSmem::BARS);
-    // kv_full, q_full[4], q_empty[4], sdp_full[2], pds_full[2], dq_full[2], dq_empty[2]
-    const uint32_t b_kv = smem_u32(bars), b_qf = b_kv + 8, b_qe = b_qf + 32, b_sdp = b_qe + 32, b_pds = b_sdp + 16,
-                   b_dq = b_pds + 16, b_dqe = b_dq + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    // kv_full, q_full[5], q_empty[5], sdp_full[2], (unused)[2], pds_full[2], dq_full[2], dq_empty, kv_in_tmem
+    const uint32_t b_kv = smem_u32(bars), b_qf = b_kv + 8, b_qe = b_qf + 8 * BWD_SLOTS, b_s = b_qe + 8 * BWD_SLOTS,
+                   b_dp = b_s + 16, b_pds = b_dp + 16, b_dq = b_pds + 16, b_dqe = b_dq + 16, b_kvt = b_dqe + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* s_stat = reinterpret_cast<float*>(smem + BwdSmem::STAT);   // [softmax warp][2][lse*log2(e) 64 | D 64]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int CTRL_WARP = BWD_SM_WARPS + 4;
+#ifdef AXENG_PROF
+    // slots: softmax group 0 thread 0: [0] wait S [1] phase A [2] wait dP/dS buffer [3] phase B [4] wait P^T free
+    // [5] stores; issuing thread: [8] loop cycles [9] idle polls [10] batches issued [11] cycles inside issue;
+    // mover thread 0: [12] wait [13] work; [15] sub-tiles
+    long long* pf = (g_bwd_prof && (threadIdx.x == 0 || threadIdx.x == CTRL_WARP * 32 || threadIdx.x == (CTRL_WARP + 2) * 32 || threadIdx.x == BWD_SM_THREADS))
+                        ? g_bwd_prof + 32 * (long long)blockIdx.x : nullptr;
+    long long pa[24] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};      // kept in registers, written once at the end
+#endif
     // 1-D grid ordered by decreasing work: key tile 0 (attended by every query tile) of all
     // (kv head, batch) pairs first
     const int rep = H / KV, nqt = T / AT;
@@ -309,11 +367,13 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     if (threadIdx.x == 0) {
         mbar_init(b_kv, 1);
-        for (int s = 0; s < 4; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 1); }
+        for (int s = 0; s < BWD_SLOTS; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 2); }
         for (int s = 0; s < 2; s++) {
-            mbar_init(b_sdp + 8 * s, 1); mbar_init(b_pds + 8 * s, 128);
-            mbar_init(b_dq + 8 * s, 1); mbar_init(b_dqe + 8 * s, BWD_DRAIN_THREADS);
+            mbar_init(b_s + 8 * s, 2); mbar_init(b_dp + 8 * s, 1);
+            mbar_init(b_pds + 8 * s, 256); mbar_init(b_dq + 8 * s, 1);
         }
+        mbar_init(b_dqe, BWD_DRAIN_THREADS);
+        mbar_init(b_kvt, BWD_SM_THREADS);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -322,102 +382,141 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // columns: S^T/P^T [2] 0..127, dP^T/dS^T [2] 128..255, dV 256..319, dK 320..383, dQ[0] 384..447, dQ[1] 448..511
-    const uint32_t t_S = tmem, t_dP = tmem + 128, t_dV = tmem + 256, t_dK = tmem + 320, t_dQ = tmem + 384;
+    // columns: S^T/P^T[2] 0..127, dP^T/dS^T[2] 128..255, dV 256..319, dK 320..383, dQ 384..447, K 448..479, V 480..511
+    const uint32_t t_S = tmem, t_dP = tmem + 128, t_dV = tmem + 256, t_dK = tmem + 320, t_dQ = tmem + 384,
+                   t_K = tmem + 448, t_V = tmem + 480;
 
-    if (warp == CTRL_WARP) {
-        if (lane == 0) {
-            bool ok = true;
-            constexpr uint32_t id_s = tc_idesc_bf16(128, 64, 0, 0);        // S^T = K Q^T, dP^T = V dO^T (64 queries)
-            constexpr uint32_t id_acc = tc_idesc_bf16(128, 64, 0, 1);      // dV/dK: A in TMEM, B N-major
-            constexpr uint32_t id_dq = tc_idesc_bf16(128, 64, 1, 1);       // dQ: A M-major (dS^T in smem), B N-major
-            // descriptor base words (K-major operands step 32 B = 2 units per k-step, MN-major ones 2048 B = 128 units)
-            const uint32_t loK_k = desc_lo(sb + BwdSmem::K, 16), loV_k = desc_lo(sb + BwdSmem::V, 16);
-            const uint32_t loK_n = desc_lo(sb + BwdSmem::K, 16384), loDS = desc_lo(sb + BwdSmem::DS0, 16384);
-            const uint32_t loQ_k = desc_lo(sb + BwdSmem::Q0, 16), loQ_n = desc_lo(sb + BwdSmem::Q0, 16384);
-            const uint32_t loO_k = desc_lo(sb + BwdSmem::DO0, 16), loO_n = desc_lo(sb + BwdSmem::DO0, 16384);
-            auto issue_sdp = [&](int u) {           // S^T and dP^T of sub-tile u into TMEM buffer u & 1
-                const int e = u & 1;
-                const uint32_t so = (uint32_t)(u & 3) * 512;           // ring slot offset (8192 B)
-#pragma unroll
-                for (int kk = 0; kk < ADH / 16; kk++)
-                    tc_mma_ss(t_S + e * 64, desc_of(loK_k + kk * 2), desc_of(loQ_k + so + kk * 2), id_s, kk != 0);
-#pragma unroll
-                for (int kk = 0; kk < ADH / 16; kk++)
-                    tc_mma_ss(t_dP + e * 64, desc_of(loV_k + kk * 2), desc_of(loO_k + so + kk * 2), id_s, kk != 0);
-                tc_commit(b_sdp + 8 * e);
-            };
-            if (!mbar_wait(b_kv, 0)) ok = false;
-            for (int u = 0; u < 2 && ok; u++) {
-                if (!mbar_wait(b_qf + 8 * u, 0)) { ok = false; break; }
-                tc_fence_after();
-                issue_sdp(u);
+    if (warp == CTRL_WARP || warp == CTRL_WARP + 1) {
+        // ── issuers of S^T = K Q^T (warp CTRL_WARP, which also feeds the Q / dO ring) and dP^T = V dO^T
+        //    (CTRL_WARP + 1): the whole warp runs converged, one elected lane issues ──
+        const bool is_s = warp == CTRL_WARP;
+        bool ok = true;
+        constexpr uint32_t id_s = tc_idesc_bf16(128, 64, 0, 0);        // A in TMEM, B K-major
+        const uint32_t loB = is_s ? desc_lo(sb + BwdSmem::Q0, 16) : desc_lo(sb + BwdSmem::DO0, 16);
+        const uint32_t tA = is_s ? t_K : t_V, tD = is_s ? t_S : t_dP;
+        // ring producer state (S issuer only): next sub-tile to load, its head / causal tile, and the slot it goes to
+        int lu = 0, lhh = 0, lii = 0;
+        auto load_sub = [&](int slot) {
+            if (lane == 0) {
+                const int i = j + lii, h = g * rep + lhh;
+                mbar_expect_tx(b_qf + 8 * slot, 16384 + 512);
+                tma_load_4d(sb + BwdSmem::Q0 + slot * 8192, &tmQ, b_qf + 8 * slot, 0, h, i * AT + (lu & 1) * 64, b);
+                tma_load_4d(sb + BwdSmem::DO0 + slot * 8192, &tmdO, b_qf + 8 * slot, 0, h, i * AT + (lu & 1) * 64, b);
+                // the sub-tile's row statistics (64 lse, 64 D) ride on the same barrier
+                const long long sidx = ((long long)b * H + h) * T + i * AT + (lu & 1) * 64;
+                bulk_load_1d(sb + BwdSmem::STAT + 4096 + slot * 512, lse + sidx, 256, b_qf + 8 * slot);
+                bulk_load_1d(sb + BwdSmem::STAT + 4096 + slot * 512 + 256, Dv + sidx, 256, b_qf + 8 * slot);
             }
-            for (int u = 0; u < n_sub && ok; u++) {
-                const int e = u & 1, it = u >> 1, sl = u & 3;
-                if (!mbar_wait(b_pds + 8 * e, (u >> 1) & 1)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t so = (uint32_t)sl * 512;
-                // P^T / dS^T in TMEM: the 64 queries packed in columns 0..31 of the buffer
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++)             // dV += P^T dO   (k = queries)
-                    tc_mma_ts(t_dV, t_S + e * 64 + kk * 8, desc_of(loO_n + so + kk * 128), id_acc, (u | kk) != 0);
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++)             // dK += dS^T Q
-                    tc_mma_ts(t_dK, t_dP + e * 64 + kk * 8, desc_of(loQ_n + so + kk * 128), id_acc, (u | kk) != 0);
-                tc_commit(b_qe + 8 * sl);                  // the ring slot is free once these have run
-                if (u + 2 < n_sub) {
-                    if (!mbar_wait(b_qf + 8 * ((u + 2) & 3), ((u + 2) >> 2) & 1)) { ok = false; break; }
-                    // S^T/dP^T(u+2) overwrite the buffer whose P^T/dS^T the dV/dK MMAs above read as their A operands:
-                    // MMAs on different accumulators are not ordered against each other, so wait for their completion
-                    if (!mbar_wait(b_qe + 8 * sl, (u >> 2) & 1)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_sdp(u + 2);
-                }
-                if (e == 1) {
-                    // the dQ accumulator of tile it-2 must have been moved out
-                    if (it >= 2 && !mbar_wait(b_dqe + 8 * (it & 1), ((it >> 1) & 1) ^ 1)) { ok = false; break; }
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < AT / 16; kk++)   // dQ = dS K   (k = keys) for the whole 128-query tile
-                        tc_mma_ss(t_dQ + (it & 1) * 64, desc_of(loDS + (it & 1) * 2048 + kk * 128), desc_of(loK_n + kk * 128), id_dq, kk != 0);
-                    tc_commit(b_dq + 8 * (it & 1));
-                }
+            if ((lu & 1) && ++lii == per_head) { lii = 0; lhh++; }
+            lu++;
+        };
+        if (is_s) {
+            if (lane == 0) {
+                tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+                mbar_expect_tx(b_kv, 32768);
+                tma_load_4d(sb + BwdSmem::K, &tmK, b_kv, 0, g, j * AT, b);
+                tma_load_4d(sb + BwdSmem::V, &tmV, b_kv, 0, g, j * AT, b);
             }
-            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_BWD | 1); }
+            for (int q = 0; q < BWD_SLOTS && q < n_sub; q++) load_sub(q);
+            __syncwarp();
         }
-    } else if (warp == CTRL_WARP + 1) {
-        // ── TMA loads: K/V once, then the Q/dO sub-tiles through a ring of four slots ──
-        if (lane == 0) {
-            bool ok = true;
-            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
-            mbar_expect_tx(b_kv, 32768);
-            tma_load_4d(sb + BwdSmem::K, &tmK, b_kv, 0, g, j * AT, b);
-            tma_load_4d(sb + BwdSmem::V, &tmV, b_kv, 0, g, j * AT, b);
-            for (int u = 0; u < n_sub && ok; u++) {
-                const int sl = u & 3, it = u >> 1, hh = it / per_head, i = j + it % per_head, h = g * rep + hh;
-                // slot sl was last used by sub-tile u-4: free once its dV/dK MMAs have run
-                if (u >= 4 && (!mbar_wait(b_qe + 8 * sl, ((u - 4) >> 2) & 1) || *abort_flag)) { ok = false; break; }
-                mbar_expect_tx(b_qf + 8 * sl, 16384);
-                tma_load_4d(sb + BwdSmem::Q0 + sl * 8192, &tmQ, b_qf + 8 * sl, 0, h, i * AT + (u & 1) * 64, b);
-                tma_load_4d(sb + BwdSmem::DO0 + sl * 8192, &tmdO, b_qf + 8 * sl, 0, h, i * AT + (u & 1) * 64, b);
+        if (!mbar_wait_park(b_kvt, 0)) ok = false;           // K and V are in TMEM
+        tc_fence_after();
+        int sl = 0, ph = 0;                             // ring slot of sub-tile u and its fill parity
+        int sl_p = 0, ph_p = 0;                         // slot / release parity of sub-tile u - 2
+        const long long t_loop = PROF_T();
+        for (int u = 0; u < n_sub && ok; u++) {
+            const long long tw = PROF_T();
+            if (!mbar_wait_park(b_qf + 8 * sl, ph) || *abort_flag) { ok = false; break; }
+            // dV/dK(u-2) have finished reading P^T / dS^T out of the two buffers that S^T / dP^T(u) overwrite
+            // (MMAs on different accumulators are not ordered against each other: wait for the commits)
+            int freed = -1;
+            if (u >= 2) {
+                if (!mbar_wait_park(b_qe + 8 * sl_p, ph_p)) { ok = false; break; }
+                freed = sl_p;                           // that sub-tile's ring slot is free as well
+                if (++sl_p == BWD_SLOTS) { sl_p = 0; ph_p ^= 1; }
             }
-            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_BWD | 4); }
+            tc_fence_after();
+            const long long tq = PROF_T();
+            PROF_ADD(9, tq - tw);
+            const uint32_t so = (uint32_t)sl * 512;          // ring slot offset (8192 B)
+            const uint32_t d_ = tD + (u & 1) * 64;
+#pragma unroll
+            for (int kk = 0; kk < ADH / 16; kk++)
+                mma_ts_e(d_, tA + kk * 8, desc_of(loB + so + kk * 2), id_s, kk != 0);
+            commit_e(b_s + 8 * (u & 1));               // two arrivals (S^T and dP^T) complete the phase
+            PROF_ADD(16, PROF_T() - tq);
+            if (is_s && freed >= 0 && lu < n_sub) { load_sub(freed); __syncwarp(); }
+            if (++sl == BWD_SLOTS) { sl = 0; ph ^= 1; }
         }
+        PROF_ADD(8, PROF_T() - t_loop); PROF_ADD(15, n_sub);
+        __syncwarp();
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_BWD | 1); }
+        if (is_s) { PROF_FLUSH(8, 12); PROF_FLUSH(15, 20); }
+    } else if (warp == CTRL_WARP + 2 || warp == CTRL_WARP + 3) {
+        // ── issuers of dV += P^T dO (CTRL_WARP + 2) and dK += dS^T Q (CTRL_WARP + 3) ──
+        const bool is_v = warp == CTRL_WARP + 2;
+        bool ok = true;
+        constexpr uint32_t id_acc = tc_idesc_bf16(128, 64, 0, 1);      // A in TMEM, B N-major
+        const uint32_t loB = is_v ? desc_lo(sb + BwdSmem::DO0, 16384) : desc_lo(sb + BwdSmem::Q0, 16384);
+        const uint32_t tA = is_v ? t_S : t_dP, tD = is_v ? t_dV : t_dK;
+        int sl = 0;
+        for (int u = 0; u < n_sub && ok; u++) {
+            const int e = u & 1, it = u >> 1;
+            const long long tw = PROF_T();
+            if (!mbar_wait_park(b_pds + 8 * e, it & 1) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+            const long long tq = PROF_T();
+            PROF_ADD(20, tq - tw);
+            const uint32_t so = (uint32_t)sl * 512;
+            const uint32_t acc = u != 0;
+            // A operand: packed bf16 in the sub-tile's buffer; 16 queries per k-step = 8 packed columns, the packed
+            // columns of column half h start at column 32 h
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+                mma_ts_e(tD, tA + e * 64 + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loB + so + kk * 128), id_acc, kk ? 1u : acc);
+            commit_e(b_qe + 8 * sl);                   // two arrivals (dV and dK): the ring slot and both buffers are free
+            PROF_ADD(19, PROF_T() - tq);
+            if (++sl == BWD_SLOTS) sl = 0;
+        }
+        __syncwarp();
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_BWD | 5); }
+        if (is_v) PROF_FLUSH(18, 22);
+    } else if (warp == CTRL_WARP + 4) {
+        // ── issuer of dQ(it) = dS K for every 128-query tile: both sub-tiles' dS^T are in shared memory and the
+        //    movers have drained the accumulator of tile it-1 ──
+        bool ok = true;
+        constexpr uint32_t id_dq = tc_idesc_bf16(128, 64, 1, 1);       // A M-major (dS^T in smem), B N-major
+        const uint32_t loK_n = desc_lo(sb + BwdSmem::K, 16384), loDS_m = desc_lo(sb + BwdSmem::DS0, 16384);
+        for (int it = 0; it < n_it && ok; it++) {
+            if (!mbar_wait_park(b_pds, it & 1) || !mbar_wait_park(b_pds + 8, it & 1) || *abort_flag) { ok = false; break; }
+            if (it >= 1 && !mbar_wait_park(b_dqe, (it - 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < AT / 16; kk++)   // k = keys
+                mma_ss_e(t_dQ, desc_of(loDS_m + (it & 1) * 2048 + kk * 128), desc_of(loK_n + kk * 128), id_dq, kk != 0);
+            commit_e(b_dq + 8 * (it & 1));
+        }
+        __syncwarp();
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_BWD | 6); }
     } else if (warp >= BWD_SM_WARPS) {
         // ── dQ movers: tile t from TMEM -> swizzled fp32 staging -> TMA reduce-add into the fp32 dq buffer ──
         const int dt_ = threadIdx.x - BWD_SM_THREADS;        // 0..127 == TMEM lane == query row
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         bool ok = true;
+        int hh = 0, ii = 0;
         for (int t = 0; t < n_it && ok; t++) {
-            if (!mbar_wait(b_dq + 8 * (t & 1), (t >> 1) & 1) || *abort_flag) { ok = false; break; }
+            const long long tm0 = PROF_T();
+            if (!mbar_wait_park(b_dq + 8 * (t & 1), (t >> 1) & 1) || *abort_flag) { ok = false; break; }
             tc_fence_after();
+            const long long tm1 = PROF_T();
+            PROF_ADD(12, tm1 - tm0);
             if (dt_ == 0) bulk_wait_read0();                 // the previous reduce has finished reading the staging
             named_bar_sync(2, BWD_DRAIN_THREADS);
 #pragma unroll 1
             for (int hf = 0; hf < 2; hf++) {
                 uint32_t v[32];
-                tmem_ld32(t_dQ + (t & 1) * 64 + lane_base + hf * 32, v);
+                tmem_ld32(t_dQ + lane_base + hf * 32, v);
                 tmem_ld_wait();
                 uint8_t* dq_row = smem + BwdSmem::DQ + hf * 16384 + dt_ * 128;
 #pragma unroll
@@ -428,133 +527,183 @@ k_attn_bwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 }
             }
             tc_fence_before();
-            mbar_arrive(b_dqe + 8 * (t & 1));                // the accumulator may be overwritten
+            mbar_arrive(b_dqe);                              // the accumulator may be overwritten
             fence_async_smem();
             named_bar_sync(2, BWD_DRAIN_THREADS);
             if (dt_ == 0) {
-                const int hh = t / per_head, i = j + t % per_head, h = g * rep + hh;
+                const int i = j + ii, h = g * rep + hh;
                 tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ, 0, h, i * AT, b);
                 tma_reduce_add_4d(&tmdQ, sb + BwdSmem::DQ + 16384, 32, h, i * AT, b);
                 bulk_commit();
             }
+            if (++ii == per_head) { ii = 0; hh++; }
+            PROF_ADD(13, PROF_T() - tm1);
         }
         if (dt_ == 0) bulk_wait0();
         if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_BWD | 3); }
+        if (dt_ == 0) PROF_FLUSH(12, 14);
     } else {
+        // warp = 8 e + 4 hc + quarter: group e, column half hc, TMEM lane quarter (a warp reaches the 32 lanes
+        // of quarter warp % 4 only)
         const int r = threadIdx.x & 127;                    // key row of S^T == TMEM lane
-        const int e = threadIdx.x >> 7;                     // softmax group == parity of its sub-tiles == TMEM buffer
+        const int e = warp >> 3;                            // softmax group == parity of its sub-tiles == TMEM buffer
+        const int hc = (warp >> 2) & 1;                     // which 32 of the sub-tile's 64 query columns
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float c = scale * LOG2E;
-        float* my_stat = s_stat + warp * 256;               // every warp keeps its own copy: no group barrier needed
+        // The TMA warp brings the 64 lse and 64 D values of a sub-tile into the ring slot beside its Q / dO tiles.
+        // Each warp turns its 32 of them into -lse*log2(e) and -D in a private area (no barrier beyond the warp),
+        // from where the arithmetic loop takes them with broadcast 16-byte loads.  (A softmax warp never loads
+        // from global memory itself: the first scoreboard wait behind such a load would expose its latency.)
+        float* my_stat = s_stat + warp * 64;                // [-lse*log2(e) 32 | -D 32]
+        const float* ring_stat = s_stat + 1024;             // [slot][lse 64 | D 64]
         bool ok = true;
-        // row statistics of sub-tile u (64 queries): lane l holds lse of queries l, l+32 and D of queries l, l+32
-        auto stat_of = [&](int u, float* st4) {
-            const int it = u >> 1, hh = it / per_head, i = j + it % per_head, h = g * rep + hh;
-            const long long idx = ((long long)b * H + h) * T + i * AT + (u & 1) * 64 + lane;
-            st4[0] = lse[idx] * LOG2E; st4[1] = lse[idx + 32] * LOG2E; st4[2] = Dv[idx]; st4[3] = Dv[idx + 32];
-        };
-        auto stat_put = [&](int buf, const float* st4) {
-            float* d = my_stat + buf * 128;
-            d[lane] = st4[0]; d[lane + 32] = st4[1]; d[64 + lane] = st4[2]; d[96 + lane] = st4[3];
-        };
-        {
-            float st4[4];
-            stat_of(e, st4);
-            stat_put(0, st4);
+        int sl_u = e, ph_u = 0, ii_c = 0;                    // ring slot (with fill parity) and causal tile index of the current sub-tile
+        // K (group 0) / V (group 1) from the swizzled shared-memory tile into TMEM: a thread copies half of its row
+        // (a row is 128 bytes = 32 packed columns; 16-byte chunk c sits at position c ^ (row & 7))
+        if (!mbar_wait_park(b_kv, 0)) ok = false;
+        if (ok) {
+            const uint8_t* row = smem + (e ? BwdSmem::V : BwdSmem::K) + r * 128;
+            uint32_t w[16];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; c4++) {
+                const uint4 x = *reinterpret_cast<const uint4*>(row + (((hc * 4 + c4) ^ (r & 7)) << 4));
+                w[c4 * 4] = x.x; w[c4 * 4 + 1] = x.y; w[c4 * 4 + 2] = x.z; w[c4 * 4 + 3] = x.w;
+            }
+            tmem_st16((e ? t_V : t_K) + lane_base + hc * 16, w);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(b_kvt);
         }
-        long long pc[2] = {0, 0};
-        const bool timing = prof != nullptr && threadIdx.x == 0;
-        const long long t_begin = timing ? clock64() : 0;
-        __syncwarp();
+        const float2 c2 = make_float2(c, c);
+        long long t_prev = PROF_T();
         for (int u = e; u < n_sub && ok; u += 2) {
             const int it = u >> 1;
-            const int i = j + it % per_head;
-            float nxt[4] = {0.f, 0.f, 0.f, 0.f};
-            if (u + 2 < n_sub) stat_of(u + 2, nxt);              // this group's next statistics into registers
-            const long long c0t = timing ? clock64() : 0;
-            if (!mbar_wait(b_sdp + 8 * e, it & 1) || *abort_flag) { ok = false; break; }
-            // the dS buffer of this tile was last read by dQ of tile it-2
-            if (it >= 2 && !mbar_wait(b_dq + 8 * (it & 1), ((it >> 1) & 1) ^ 1)) { ok = false; break; }
+            const bool diag = ii_c == 0;
+            if (++ii_c == per_head) ii_c = 0;
+            const float* L = my_stat;
+            const float* Dr = L + 32;
+            const long long ta0 = PROF_T();
+            PROF_ADD(6, ta0 - t_prev);
+            if (!mbar_wait_park(b_s + 8 * e, it & 1) || *abort_flag) { ok = false; break; }
+            // the dS^T shared-memory buffer of this tile parity was last read by dQ of tile it-2
+            if (it >= 2 && !mbar_wait_park(b_dq + 8 * (it & 1), ((it >> 1) & 1) ^ 1)) { ok = false; break; }
             tc_fence_after();
-            const long long c1t = timing ? clock64() : 0;
-            const bool diag = i == j;
-            const float* L = my_stat + (it & 1) * 128;
-            const float* Dr = L + 64;
+            const long long ta1 = PROF_T();
+            PROF_ADD(0, ta1 - ta0);
+            {
+                // the slot's barrier completed long ago (S^T was issued behind it); observing it here makes the
+                // bulk-copied statistics visible to this thread
+                if (!mbar_wait_park(b_qf + 8 * sl_u, ph_u)) { ok = false; break; }
+                const float* rs = ring_stat + sl_u * 128 + hc * 32 + lane;
+                my_stat[lane] = -rs[0] * LOG2E;
+                my_stat[32 + lane] = -rs[64];
+                sl_u += 2;
+                if (sl_u >= BWD_SLOTS) { sl_u -= BWD_SLOTS; ph_u ^= 1; }
+                __syncwarp();
+            }
             uint8_t* ds_row = smem + BwdSmem::DS0 + (it & 1) * 32768 + e * 16384 + r * 128;
-#pragma unroll 1
-            for (int ch = 0; ch < 2; ch++) {
-                uint32_t sv[32], dp[32], wp[16], wd[16];
-                tmem_ld32(t_S + e * 64 + lane_base + ch * 32, sv);
-                tmem_ld32(t_dP + e * 64 + lane_base + ch * 32, dp);
+            const uint32_t tS = t_S + e * 64 + hc * 32 + lane_base, tdP = t_dP + e * 64 + hc * 32 + lane_base;
+#pragma unroll
+            for (int rd = 0; rd < 2; rd++) {                     // two rounds of 16 query columns
+                uint32_t sv[16], dp[16], wp[8], wd[8];
+                tmem_ld16(tS + rd * 16, sv);
+                tmem_ld16(tdP + rd * 16, dp);
                 tmem_ld_wait();
                 if (diag) {                                      // query < key: masked (score -> -inf, so P = dS = 0)
 #pragma unroll
-                    for (int q = 0; q < 32; q++)
-                        if (e * 64 + ch * 32 + q < r) sv[q] = 0xff800000u;
+                    for (int q = 0; q < 16; q++)
+                        if (e * 64 + hc * 32 + rd * 16 + q < r) sv[q] = 0xff800000u;
                 }
 #pragma unroll
-                for (int q = 0; q < 32; q += 4) {
-                    const int cs = ch * 32 + q;                  // query column within the sub-tile
-                    const float4 l4 = *reinterpret_cast<const float4*>(L + cs);       // broadcast 16-byte loads
-                    const float4 d4 = *reinterpret_cast<const float4*>(Dr + cs);
-                    const float p0 = fast_exp2(__uint_as_float(sv[q]) * c - l4.x);
-                    const float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - l4.y);
-                    const float p2 = fast_exp2(__uint_as_float(sv[q + 2]) * c - l4.z);
-                    const float p3 = fast_exp2(__uint_as_float(sv[q + 3]) * c - l4.w);
-                    wp[q >> 1] = pack_bf16(p0, p1);
-                    wp[(q >> 1) + 1] = pack_bf16(p2, p3);
-                    wd[q >> 1] = pack_bf16(p0 * (__uint_as_float(dp[q]) - d4.x), p1 * (__uint_as_float(dp[q + 1]) - d4.y));
-                    wd[(q >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[q + 2]) - d4.z), p3 * (__uint_as_float(dp[q + 3]) - d4.w));
+                for (int q = 0; q < 16; q += 4) {
+                    const float4 l4 = *reinterpret_cast<const float4*>(L + rd * 16 + q);       // broadcast 16-byte loads
+                    const float4 d4 = *reinterpret_cast<const float4*>(Dr + rd * 16 + q);
+                    // packed fp32x2 arithmetic: one instruction per pair of columns
+                    const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(sv[q]), __uint_as_float(sv[q + 1])), c2, make_float2(l4.x, l4.y));
+                    const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(sv[q + 2]), __uint_as_float(sv[q + 3])), c2, make_float2(l4.z, l4.w));
+                    const float2 p01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+                    const float2 p23 = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+                    const float2 g01 = __fadd2_rn(make_float2(__uint_as_float(dp[q]), __uint_as_float(dp[q + 1])), make_float2(d4.x, d4.y));
+                    const float2 g23 = __fadd2_rn(make_float2(__uint_as_float(dp[q + 2]), __uint_as_float(dp[q + 3])), make_float2(d4.z, d4.w));
+                    const float2 s01 = __fmul2_rn(p01, g01), s23 = __fmul2_rn(p23, g23);
+                    wp[q >> 1] = pack_bf16(p01.x, p01.y);
+                    wp[(q >> 1) + 1] = pack_bf16(p23.x, p23.y);
+                    wd[q >> 1] = pack_bf16(s01.x, s01.y);
+                    wd[(q >> 1) + 1] = pack_bf16(s23.x, s23.y);
                 }
-                // packed columns ch*16 .. ch*16+15 of the buffer: inside the columns this thread has already read
-                tmem_st16(t_S + e * 64 + lane_base + ch * 16, wp);
-                tmem_st16(t_dP + e * 64 + lane_base + ch * 16, wd);
-                // dS^T also to shared memory (A operand of dQ): block = sub-tile, 16-byte chunk index XOR (row & 7)
+                // in place: the packed columns of round rd lie inside the columns this thread has already read
+                // (its own 32-column half, columns 8 rd .. 8 rd + 7 of it)
+                tmem_st8(tS + rd * 8, wp);
+                tmem_st8(tdP + rd * 8, wd);
+                // dS^T also into the shared-memory tile of the sub-tile: row = key, 16-byte chunk index XOR (row & 7)
 #pragma unroll
-                for (int k4 = 0; k4 < 4; k4++) {
-                    const int chunk = ch * 4 + k4;
-                    uint4 pk = make_uint4(wd[k4 * 4], wd[k4 * 4 + 1], wd[k4 * 4 + 2], wd[k4 * 4 + 3]);
-                    *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) = pk;
+                for (int k4 = 0; k4 < 2; k4++) {
+                    const int chunk = hc * 4 + rd * 2 + k4;
+                    *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) =
+                        make_uint4(wd[k4 * 4], wd[k4 * 4 + 1], wd[k4 * 4 + 2], wd[k4 * 4 + 3]);
                 }
             }
+            const long long tc1 = PROF_T();
+            PROF_ADD(1, tc1 - ta1);
             tmem_st_wait();
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(b_pds + 8 * e);
-            if (timing) { const long long c2t = clock64(); pc[0] += c1t - c0t; pc[1] += c2t - c1t; }
-            if (u + 2 < n_sub) stat_put((it + 1) & 1, nxt);
-            __syncwarp();                                    // publishes the statistics just written within the warp
+            PROF_ADD(5, PROF_T() - tc1);
+            __syncwarp();                                    // the private statistics are rewritten at the top of the next iteration
+            t_prev = PROF_T();
         }
-        if (timing) {
-            long long* pp = prof + 8 * (long long)blockIdx.x;
-            pp[0] = pc[0]; pp[1] = pc[1]; pp[2] = 0; pp[3] = 0; pp[4] = clock64() - t_begin; pp[5] = n_it;
-        }
-        // dV (group 0) and dK (group 1): complete once the last dQ commit has fired
-        if (ok && !mbar_wait(b_dq + 8 * ((n_it - 1) & 1), ((n_it - 1) >> 1) & 1)) ok = false;
+        if (threadIdx.x == 0) PROF_FLUSH(0, 8);
+        // dV (group 0) and dK (group 1): complete once the last sub-tile's dV and dK commits have fired.  Column half hc writes head
+        // dimensions 16 hc .. 16 hc + 15 and their rotary partners 32 further on.
+        if (ok && !mbar_wait_park(b_qe + 8 * ((n_sub - 1) % BWD_SLOTS), ((n_sub - 1) / BWD_SLOTS) & 1)) ok = false;
         if (ok) {
             tc_fence_after();
             const int t = j * AT + r;
-            const uint32_t ta = e ? t_dK : t_dV;
+            const uint32_t ta = (e ? t_dK : t_dV) + lane_base + hc * 16;
             const float f = e ? scale : 1.f;
-            bf16* dst = (e ? dk : dv) + (((long long)b * T + t) * KV + g) * ADH;
-#pragma unroll 1
-            for (int ch = 0; ch < 2; ch++) {
-                uint32_t v[32];
-                tmem_ld32(ta + lane_base + ch * 32, v);
-                tmem_ld_wait();
-                if (t < T) {
+            bf16* dst = (e ? dk : dv) + (((long long)b * T + t) * KV + g) * ADH + hc * 16;
+            uint32_t v1[16], v2[16];
+            tmem_ld16(ta, v1);
+            tmem_ld16(ta + 32, v2);
+            tmem_ld_wait();
+            if (e && rope_cos) {
+                // inverse rotary on dK (pairs are 32 columns apart): out1 = g1 c + g2 s, out2 = -g1 s + g2 c
+                const float* cr = rope_cos + (long long)t * (ADH / 2) + hc * 16;
+                const float* sr = rope_sin + (long long)t * (ADH / 2) + hc * 16;
 #pragma unroll
-                    for (int q = 0; q < 32; q += 8) {
-                        uint4 pk;
-                        pk.x = pack_bf16(__uint_as_float(v[q]) * f, __uint_as_float(v[q + 1]) * f);
-                        pk.y = pack_bf16(__uint_as_float(v[q + 2]) * f, __uint_as_float(v[q + 3]) * f);
-                        pk.z = pack_bf16(__uint_as_float(v[q + 4]) * f, __uint_as_float(v[q + 5]) * f);
-                        pk.w = pack_bf16(__uint_as_float(v[q + 6]) * f, __uint_as_float(v[q + 7]) * f);
-                        *reinterpret_cast<uint4*>(dst + ch * 32 + q) = pk;
+                for (int q = 0; q < 16; q += 4) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(cr + q), s4 = *reinterpret_cast<const float4*>(sr + q);
+                    const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int z = 0; z < 4; z++) {
+                        const float g1 = __uint_as_float(v1[q + z]) * f, g2 = __uint_as_float(v2[q + z]) * f;
+                        v1[q + z] = __float_as_uint(g1 * cc[z] + g2 * ss[z]);
+                        v2[q + z] = __float_as_uint(g2 * cc[z] - g1 * ss[z]);
                     }
                 }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    v1[q] = __float_as_uint(__uint_as_float(v1[q]) * f);
+                    v2[q] = __float_as_uint(__uint_as_float(v2[q]) * f);
+                }
             }
-        } else if (lane == 0) {
+#pragma unroll
+            for (int q = 0; q < 16; q += 8) {
+                uint4 pk;
+                pk.x = pack_bf16(__uint_as_float(v1[q]), __uint_as_float(v1[q + 1]));
+                pk.y = pack_bf16(__uint_as_float(v1[q + 2]), __uint_as_float(v1[q + 3]));
+                pk.z = pack_bf16(__uint_as_float(v1[q + 4]), __uint_as_float(v1[q + 5]));
+                pk.w = pack_bf16(__uint_as_float(v1[q + 6]), __uint_as_float(v1[q + 7]));
+                *reinterpret_cast<uint4*>(dst + q) = pk;
+                pk.x = pack_bf16(__uint_as_float(v2[q]), __uint_as_float(v2[q + 1]));
+                pk.y = pack_bf16(__uint_as_float(v2[q + 2]), __uint_as_float(v2[q + 3]));
+                pk.z = pack_bf16(__uint_as_float(v2[q + 4]), __uint_as_float(v2[q + 5]));
+                pk.w = pack_bf16(__uint_as_float(v2[q + 6]), __uint_as_float(v2[q + 7]));
+                *reinterpret_cast<uint4*>(dst + 32 + q) = pk;
+            }
+        } else if (!ok && lane == 0) {
             *abort_flag = 1;
             atomicExch(status, STAT_BWD | 2);
         }
@@ -572,6 +721,27 @@ __global__ void k_dq_convert(const float* __restrict__ src, bf16* __restrict__ d
         Vec<float>::ld(src + i * 8, f);
         Vec<float>::ld(src + i * 8 + 4, f + 4);
         Vec<bf16>::st(dst + i * 8, f);
+    }
+}
+// The same with the inverse rotary applied on the way (head_dim 64: pairs are 32 columns apart): a thread takes
+// 8 columns of the first half of a row and their partners; rows = B*T*H, t = (row / H) % T.
+__global__ void k_dq_convert_rope(const float* __restrict__ src, bf16* __restrict__ dst, const float* __restrict__ cs,
+                                  const float* __restrict__ sn, long long rows, int T, int H) {
+    const long long total = rows * 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long row = i >> 2;
+        const int jc = (int)(i & 3) * 8;
+        const int t = (int)((row / H) % T);
+        float g1[8], g2[8], c[8], s[8], o1[8], o2[8];
+        Vec<float>::ld(src + row * ADH + jc, g1); Vec<float>::ld(src + row * ADH + jc + 4, g1 + 4);
+        Vec<float>::ld(src + row * ADH + 32 + jc, g2); Vec<float>::ld(src + row * ADH + 32 + jc + 4, g2 + 4);
+        Vec<float>::ld(cs + (long long)t * 32 + jc, c); Vec<float>::ld(cs + (long long)t * 32 + jc + 4, c + 4);
+        Vec<float>::ld(sn + (long long)t * 32 + jc, s); Vec<float>::ld(sn + (long long)t * 32 + jc + 4, s + 4);
+#pragma unroll
+        for (int q = 0; q < 8; q++) { o1[q] = g1[q] * c[q] + g2[q] * s[q]; o2[q] = g2[q] * c[q] - g1[q] * s[q]; }
+        Vec<bf16>::st(dst + row * ADH + jc, o1);
+        Vec<bf16>::st(dst + row * ADH + 32 + jc, o2);
     }
 }
 
@@ -619,10 +789,14 @@ int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* 
 
 int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dO,
                    const float* lse, float* Dscratch, float* g_dq_acc, void* dq, void* dk, void* dv,
-                   const AttnShape& s, int* status, cudaStream_t st) {
-    if (s.DH == 128) return ax_attn_bwd_tc128(q, k, v, o, dO, lse, Dscratch, g_dq_acc, dq, dk, dv, s, status, st);
+                   const AttnShape& s, const float* rope_cos, const float* rope_sin, int* status, cudaStream_t st) {
+    if (s.DH == 128) {
+        if (rope_cos) return -1;                 // the inverse rotary is fused for head_dim 64 only
+        return ax_attn_bwd_tc128(q, k, v, o, dO, lse, Dscratch, g_dq_acc, dq, dk, dv, s, status, st);
+    }
     if (!served(s) || !g_dq_acc || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) ||
         !aligned16(dq) || !aligned16(dk) || !aligned16(dv) || !aligned16(g_dq_acc)) return -1;
+    if (rope_cos && (!rope_sin || !aligned16(rope_cos) || !aligned16(rope_sin))) return -1;
     const size_t need = (size_t)s.B * s.T * s.H * ADH * 4;
     CUtensorMap tq, tk, tv, tdo, tdq;
     if (map_bthd(&tq, q, s.B, s.T, s.H, 64) || map_bthd(&tk, k, s.B, s.T, s.KV) || map_bthd(&tv, v, s.B, s.T, s.KV) ||
@@ -631,23 +805,35 @@ int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, c
     const long long rows = (long long)s.B * s.T * s.H;
     k_attn_bwd_prep<<<ew_grid(rows * 8, 256), 256, 0, st>>>((const bf16*)o, (const bf16*)dO, Dscratch, s.B, s.T, s.H);
     dim3 grid((s.T / AT) * s.KV * s.B);
+#ifdef AXENG_PROF       // instrumented builds: allocates, synchronises and prints per launch (AXENG_ATTN_PROF=1)
     static const bool want_prof = getenv("AXENG_ATTN_PROF") != nullptr;
     long long* prof = nullptr;
-    const int nblk = (s.T / AT) * s.KV * s.B;
-    if (want_prof && cudaMalloc(&prof, (size_t)nblk * 64) != cudaSuccess) prof = nullptr;
+    const int nblk = (int)grid.x;
+    if (want_prof && cudaMalloc(&prof, (size_t)nblk * 256) == cudaSuccess) cudaMemset(prof, 0, (size_t)nblk * 256); else prof = nullptr;
+    cudaMemcpyToSymbol(g_bwd_prof, &prof, sizeof(prof));
+#endif
     k_attn_bwd_tc<<<grid, BWD_THREADS, BwdSmem::TOTAL, st>>>(tq, tk, tv, tdo, tdq, lse, Dscratch, (bf16*)dk, (bf16*)dv,
-                                                              s.T, s.H, s.KV, s.scale, status, prof);
-    if (prof) {     // debugging aid: phase cycle counts summed over CTAs, printed to stderr
-        std::vector<long long> h((size_t)nblk * 8);
+                                                              s.T, s.H, s.KV, s.scale, rope_cos, rope_sin, status);
+#ifdef AXENG_PROF
+    if (prof) {
+        std::vector<long long> h((size_t)nblk * 32);
         cudaStreamSynchronize(st);
-        cudaMemcpy(h.data(), prof, (size_t)nblk * 64, cudaMemcpyDeviceToHost);
+        cudaMemcpy(h.data(), prof, (size_t)nblk * 256, cudaMemcpyDeviceToHost);
         cudaFree(prof);
-        long long sum[6] = {0, 0, 0, 0, 0, 0}, mx = 0;
-        for (int i = 0; i < nblk; i++) { for (int q = 0; q < 6; q++) sum[q] += h[i * 8 + q]; if (h[i * 8 + 4] > mx) mx = h[i * 8 + 4]; }
-        fprintf(stderr, "attn_bwd phases (cycles per 128-query tile): wait_sdp %.0f softmax %.0f total %.0f | tiles %lld, longest CTA %lld cycles\n",
-                (double)sum[0] / sum[5], (double)sum[1] / sum[5], (double)sum[4] / sum[5], sum[5], mx);
+        double sum[32] = {0};
+        for (int i = 0; i < nblk; i++) for (int q = 0; q < 32; q++) sum[q] += (double)h[(size_t)i * 32 + q];
+        const double nt = sum[15] / 2.0;       // 128-query tiles
+        fprintf(stderr, "attn_bwd per 128-query tile (cycles): softmax w0 top %.0f wait %.0f compute %.0f (%.0f %.0f %.0f) store %.0f | "
+                        "issuer A loop %.0f wait %.0f S+dP issue %.0f | issuer B wait %.0f dV/dK issue %.0f wait drain %.0f dQ issue %.0f | mover wait %.0f work %.0f | tiles %.0f\n",
+                sum[6] / nt, sum[0] / nt, sum[1] / nt, sum[2] / nt, sum[3] / nt, sum[4] / nt, sum[5] / nt, sum[8] / nt, sum[9] / nt, sum[16] / nt,
+                sum[20] / nt, sum[19] / nt, sum[21] / nt, sum[18] / nt, sum[12] / nt, sum[13] / nt, nt);
     }
-    const long long n8 = rows * ADH / 8;
-    k_dq_convert<<<ew_grid(n8, 256), 256, 0, st>>>(g_dq_acc, (bf16*)dq, n8);
+#endif
+    if (rope_cos) {
+        k_dq_convert_rope<<<ew_grid(rows * 4, 256), 256, 0, st>>>(g_dq_acc, (bf16*)dq, rope_cos, rope_sin, rows, s.T, s.H);
+    } else {
+        const long long n8 = rows * ADH / 8;
+        k_dq_convert<<<ew_grid(n8, 256), 256, 0, st>>>(g_dq_acc, (bf16*)dq, n8);
+    }
     return 0;
 }

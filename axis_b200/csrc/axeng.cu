@@ -709,28 +709,53 @@ static int exec_op(const EngOp* op) {
             return ax_attn_fwd_simt(dt, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (float*)BUFP(op->sa), s, st);
         }
         case ENG_ATTN_BWD: {
-            // a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=D scratch [B,T,H] fp32
+            // a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=D scratch [B,T,H] fp32.
+            // gamma > 0: the inverse rotary of dq and dk is part of the op; beta / gamma hold the buffer
+            // indices of the cos / sin tables (float-encoded like the reference's ids; sin is never slot 0)
             const int T = op->m, DH = op->n, KV = op->k, B = op->batch, H = op->ob;
             if (KV <= 0 || H <= 0 || H % KV) { set_err("attn_bwd: H %% KV != 0"); return 102; }
             const long long qe = (long long)B * H * T * DH, ke = (long long)B * KV * T * DH;
             NEED(op->a, qe * es); NEED(op->c, qe * es); NEED(op->sb, qe * es); NEED(op->b, ke * es); NEED(op->d, ke * es);
             NEED(op->sa, (long long)B * H * T * 4); NEED(op->oc, (long long)B * H * T * 4);
             NEED(op->tb, qe * es); NEED(op->sc, ke * es); NEED(op->oa, ke * es);
+            const float* rc_ = nullptr; const float* rs_ = nullptr;
+            if (op->gamma > 0.f) {
+                const int ic = (int)op->beta, is = (int)op->gamma;
+                NEED(ic, (long long)T * (DH / 2) * 4); NEED(is, (long long)T * (DH / 2) * 4);
+                rc_ = (const float*)BUFP(ic); rs_ = (const float*)BUFP(is);
+            }
             AttnShape s = shape_bthd(B, H, KV, T, DH, op->alpha);
+            bool rotated = false;
+            int done = 0;
             if (dt == 1 && !(G.fallback & 2)) {
                 // the tensor-core path needs an fp32 dQ accumulator behind the D scratch in the same buffer
                 const long long dwords = (long long)B * H * T;
                 float* dq_acc = have(op->oc, (dwords + qe) * 4) ? (float*)BUFP(op->oc) + dwords : nullptr;
-                const int rc = ax_attn_bwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->sb), BUFP(op->c), (const float*)BUFP(op->sa),
-                                              (float*)BUFP(op->oc), dq_acc, BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, G.d_status, st);
-                if (rc == 0) { G.launches += 4; return 0; }
+                int rc = ax_attn_bwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->sb), BUFP(op->c), (const float*)BUFP(op->sa),
+                                        (float*)BUFP(op->oc), dq_acc, BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, rc_, rs_, G.d_status, st);
+                if (rc == 0) { rotated = rc_ != nullptr; done = 1; }
+                else if (rc < 0 && rc_) {        // served without the fused rotary (head_dim 128)?
+                    rc = ax_attn_bwd_tc(BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->sb), BUFP(op->c), (const float*)BUFP(op->sa),
+                                        (float*)BUFP(op->oc), dq_acc, BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, nullptr, nullptr, G.d_status, st);
+                    if (rc == 0) done = 1;
+                }
                 if (rc > 0) return rc;
+                if (done) G.launches += 4;
             }
-            G.launches += 3;
-            int rc = ax_rowdot(dt, BUFP(op->c), BUFP(op->sb), (float*)BUFP(op->oc), (long long)B * T * H, DH, st);
-            if (rc) return rc;
-            return ax_attn_bwd_simt(dt, dt == 1 ? 1 : 0, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (const float*)BUFP(op->sa),
-                                    (const float*)BUFP(op->oc), BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, st);
+            if (!done) {
+                G.launches += 3;
+                int rc = ax_rowdot(dt, BUFP(op->c), BUFP(op->sb), (float*)BUFP(op->oc), (long long)B * T * H, DH, st);
+                if (rc) return rc;
+                rc = ax_attn_bwd_simt(dt, dt == 1 ? 1 : 0, BUFP(op->a), BUFP(op->b), BUFP(op->d), BUFP(op->c), (const float*)BUFP(op->sa),
+                                      (const float*)BUFP(op->oc), BUFP(op->tb), BUFP(op->sc), BUFP(op->oa), s, st);
+                if (rc) return rc;
+            }
+            if (rc_ && !rotated) {
+                G.launches++;
+                return ax_rope2(dt, BUFP(op->tb), rc_, rs_, BUFP(op->tb), T, DH, (long long)B * T * H, H, 1,
+                                BUFP(op->sc), BUFP(op->sc), (long long)B * T * KV, KV, st);
+            }
+            return 0;
         }
         case ENG_L2ACC:
             NEED(op->a, (long long)op->n * 4); NEED(op->c, 4);

@@ -115,10 +115,12 @@ int ax_attn_tc_init(void);
 int ax_attn_tc128_init(void);
 int ax_attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
                    const AttnShape& s, int* status, cudaStream_t st);
-// dq_acc: fp32 accumulator of B*T*H*DH elements for the dQ reduce-add (null -> not served)
+// dq_acc: fp32 accumulator of B*T*H*DH elements for the dQ reduce-add (null -> not served).
+// rope_cos / rope_sin (fp32 [T, DH/2], may be null): when given, the inverse rotary is applied to dq and dk
+// before they are rounded to bf16 (head_dim 64 only; -1 otherwise, the caller then runs the rotary op itself).
 int ax_attn_bwd_tc(const void* q, const void* k, const void* v, const void* o, const void* dO,
                    const float* lse, float* Dscratch, float* dq_acc, void* dq, void* dk, void* dv,
-                   const AttnShape& s, int* status, cudaStream_t st);
+                   const AttnShape& s, const float* rope_cos, const float* rope_sin, int* status, cudaStream_t st);
 // attn_tc128.cu — the head_dim-128 kernels behind the two entry points above.
 int ax_attn_fwd_tc128(const void* q, const void* k, const void* v, void* o, float* lse,
                       const AttnShape& s, int* status, cudaStream_t st);

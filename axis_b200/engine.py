@@ -82,7 +82,9 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                m=T n=DH k=KV batch=B tb=H; alpha=scale
     ATTN_BWD:  a=q b=k d=v c=dO; sa=lse sb=o tb=dq sc=dk oa=dv ob=H oc=scratch (B*H*T
                floats, plus B*T*H*DH floats to enable the tensor-core path);
-               m=T n=DH k=KV batch=B; alpha=scale; outputs in storage dtype
+               m=T n=DH k=KV batch=B; alpha=scale; outputs in storage dtype;
+               gamma > 0: dq and dk leave the op with the inverse rotary applied, beta / gamma
+               being the buffer indices of the cos / sin tables (float-encoded, sin never slot 0)
     RMSNORM_BWD_ACC: a=x b=w d=g c=dx; tb=residual added to dx; sa=dw (fp32);
                sb=scratch; m=N n=D; alpha=eps
     CE_FUSED:  a=logits b=targets(int32) c=dlogits (may alias a) d=loss; sa=count

@@ -213,6 +213,10 @@ class InterpEngine:
             v = self._get(d, B_ * T * KV * DH, dt).reshape(B_, T, KV, DH).transpose(0, 2, 1, 3)
             do = self._get(c, B_ * T * H * DH, dt).reshape(B_, T, H, DH).transpose(0, 2, 1, 3)
             dq, dk, dv = O.attention_bwd(q, kk, v, do, alpha)
+            if gamma > 0:       # inverse rotary of dq and dk inside the op; beta / gamma name the cos / sin tables
+                cos = self._f32(int(beta), T * (DH // 2)).reshape(T, DH // 2)
+                sin = self._f32(int(gamma), T * (DH // 2)).reshape(T, DH // 2)
+                dq, dk = O.rope_bwd(dq, cos, sin), O.rope_bwd(dk, cos, sin)
             self._put(tb, dq.transpose(0, 2, 1, 3), dt)
             self._put(sc, dk.transpose(0, 2, 1, 3), dt)
             return self._put(oa, dv.transpose(0, 2, 1, 3), dt)

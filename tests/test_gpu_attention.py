@@ -153,3 +153,30 @@ def test_attention_backward_is_deterministic(eng, fallback, DH, T):
                 assert np.array_equal(f, again)
     eng.set_fallback(0)
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt,B,H,KV,T,DH", [(1, 2, 6, 2, 256, 64), (1, 1, 4, 2, 256, 128), (0, 1, 4, 2, 40, 32), (1, 1, 3, 1, 130, 64)])
+def test_attention_backward_with_the_inverse_rotary_inside(eng, dt, B, H, KV, T, DH):
+    """ATTN_BWD with gamma > 0 returns dq and dk already rotated back (the compiled step's form): the head_dim-64
+    tensor-core kernel applies the rotation before rounding, every other path runs the rotary kernel behind the
+    attention kernels.  Reference: attention_bwd followed by rope_bwd of the oracle."""
+    rng = np.random.default_rng(7 * T + DH)
+    q, k, v, do = make(rng, B, H, KV, T, DH, dt)
+    scale = 1.0 / np.sqrt(DH)
+    cos, sin = O.rope_tables(T, DH)
+    t = lambda x: np.ascontiguousarray(x.transpose(0, 2, 1, 3))
+    iq, ik, iv, ido = put(eng, t(q), dt), put(eng, t(k), dt), put(eng, t(v), dt), put(eng, t(do), dt)
+    ic, isn = put(eng, cos, 0), put(eng, sin, 0)
+    io, ilse, iD = eng.alloc(q.size), eng.alloc(B * H * T), eng.alloc(B * H * T + q.size)
+    idq, idk, idv = eng.alloc(q.size), eng.alloc(k.size), eng.alloc(k.size)
+    eng.run([op(E.ATTN_FWD, a=iq, b=ik, d=iv, c=io, sa=ilse, m=T, n=DH, k=KV, batch=B, tb=H, dt=dt, alpha=scale),
+             op(E.ATTN_BWD, a=iq, b=ik, d=iv, c=ido, sa=ilse, sb=io, tb=idq, sc=idk, oa=idv, ob=H, oc=iD,
+                m=T, n=DH, k=KV, batch=B, dt=dt, alpha=scale, beta=float(ic), gamma=float(isn))])
+    dq_ref, dk_ref, dv_ref = O.attention_bwd(q, k, v, do, scale)
+    dq_ref, dk_ref = O.rope_bwd(dq_ref, cos, sin), O.rope_bwd(dk_ref, cos, sin)
+    dq = get(eng, idq, (B, T, H, DH), dt).transpose(0, 2, 1, 3)
+    dk = get(eng, idk, (B, T, KV, DH), dt).transpose(0, 2, 1, 3)
+    dv = get(eng, idv, (B, T, KV, DH), dt).transpose(0, 2, 1, 3)
+    lim = 2e-2 if dt else 3e-5
+    assert rel(dq, dq_ref) <= lim and rel(dk, dk_ref) <= lim and rel(dv, dv_ref) <= lim
+    assert eng.device_status() == 0
