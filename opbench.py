@@ -12,6 +12,15 @@ the algorithmic bytes or flops of the op, the achieved GB/s or TFLOP/s and
 its fraction of the measured peak (MEASURED_PEAKS.json beside this file when
 present, else 6650 GB/s / 1590 TFLOP/s).  `--check` also verifies the result
 against a numpy evaluation on a sample of the output.
+
+    python opbench.py refcmp [--lib oracle/_ref/libaxeng_ref.so]
+
+times, at the 1B-class shapes, the plan fragments that the reference's own lowering emits for the hot ops
+(reference op kinds only: its flash backward with row dots, zero fills and casts; RMSNorm backward + column sum;
+count + cross-entropy; per-tensor L2 / clip / AdamW; rotary + permutes; SwiGLU; cuBLAS GEMMs) on the library
+given by --lib (the reference's engine, built by oracle/build_ref.py: the kernels to beat), and beside each the
+fused op of this library that replaces the fragment.  Both run as captured graphs replayed back to back on
+buffer sets larger than L2; one JSON line per case.
 """
 from __future__ import annotations
 
@@ -216,6 +225,262 @@ def run_adamw(b, n):
     return b.report(f"clip + AdamW over a flat arena of {n} params", ms, bytes_=34 * n)
 
 
+class RawEngine:
+    """The reference's twelve exports only (axis/engine.py:78-174): what any libaxeng-compatible library offers."""
+
+    def __init__(self, lib_path):
+        import ctypes
+        self.ct = ctypes
+        self.lib = L = ctypes.CDLL(lib_path)
+        L.eng_init.restype = ctypes.c_int
+        L.eng_alloc.argtypes = [ctypes.c_int, ctypes.c_longlong, ctypes.c_int]
+        L.eng_upload.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_float), ctypes.c_longlong]
+        L.eng_run_plan.argtypes = [ctypes.POINTER(E._EngOp), ctypes.c_int, ctypes.c_int]
+        L.eng_capture_plan.argtypes = [ctypes.POINTER(E._EngOp), ctypes.c_int]
+        L.eng_replay.argtypes = [ctypes.c_int, ctypes.c_int]
+        rc = L.eng_init()
+        if rc:
+            raise RuntimeError(f"eng_init rc={rc}")
+        self.next = 0
+
+    def alloc(self, n, itemsize=4):
+        i = self.next
+        self.next += 1
+        rc = self.lib.eng_alloc(i, int(n), int(itemsize))
+        if rc:
+            raise RuntimeError(f"eng_alloc rc={rc}")
+        return i
+
+    def fill(self, i, nbytes, rng, scale=1.0):
+        """Random fp32 words (a bf16 buffer gets random bf16 pairs of modest size: zero the low mantissa noise)"""
+        n = nbytes // 4
+        step = 1 << 24
+        for o in range(0, n, step):
+            m = min(step, n - o)
+            a = (rng.standard_normal(m, dtype=np.float32) * scale)
+            # upload goes to the start of the buffer only; larger buffers are filled in one call
+            if o == 0 and m == n:
+                self.lib.eng_upload(i, a.ctypes.data_as(self.ct.POINTER(self.ct.c_float)), m)
+                return
+        a = rng.standard_normal(n, dtype=np.float32) * scale
+        self.lib.eng_upload(i, a.ctypes.data_as(self.ct.POINTER(self.ct.c_float)), n)
+
+    def time_graph(self, plan, reps):
+        pp = E.PackedPlan(plan)
+        rc = self.lib.eng_run_plan(pp.ptr, pp.n, 1)
+        if rc:
+            raise RuntimeError(f"run_plan rc={rc}")
+        rc = self.lib.eng_capture_plan(pp.ptr, pp.n)
+        if rc:
+            raise RuntimeError(f"capture rc={rc}")
+        self.lib.eng_replay(2, 1)
+        import time
+        t0 = time.perf_counter()
+        rc = self.lib.eng_replay(reps, 1)
+        dt = time.perf_counter() - t0
+        if rc:
+            raise RuntimeError(f"replay rc={rc}")
+        return dt / reps * 1e3
+
+
+def bf16_buf(e, rng, n, scale=1.0):
+    """n bf16 elements holding N(0, scale) values (uploaded as fp32 words whose halves are valid bf16 numbers)"""
+    i = e.alloc(n, 2)
+    a = rng.standard_normal(n, dtype=np.float32) * scale
+    bits = E.f32_to_bf16_bits(a)
+    words = bits.view(np.uint32) if n % 2 == 0 else np.concatenate([bits, np.zeros(1, np.uint16)]).view(np.uint32)
+    f = words.view(np.float32)
+    e.lib.eng_upload(i, f.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), f.size)
+    return i
+
+
+def refcmp(lib_path, reps):
+    """Reference fragments on `lib_path` vs this library's fused ops; shapes of the 1B-class step."""
+    from axis_b200._build import engine_lib
+    N, D, MLP, V = 8192, 1536, 4096, 32000
+    B, H, KV, T, DH = 4, 24, 8, 2048, 64
+    rng = np.random.default_rng(0)
+    out = []
+
+    def run(which, name, build, chain, algo_bytes=None, flops=None):
+        e = RawEngine(lib_path if which == "reference" else engine_lib())
+        e.alloc(4)
+        plan = []
+        for _ in range(chain):
+            plan += build(e)
+        ms = e.time_graph(plan, reps) / chain
+        rec = {"case": name, "library": which, "ms": round(ms, 5), "instances_per_replay": chain, "reps": reps}
+        if algo_bytes:
+            rec["gbs_algorithmic"] = round(algo_bytes / (ms * 1e-3) / 1e9, 1)
+        if flops:
+            rec["tflops"] = round(flops / (ms * 1e-3) / 1e12, 1)
+        print(json.dumps(rec), flush=True)
+        out.append(rec)
+        e.lib.eng_shutdown() if hasattr(e.lib, "eng_shutdown") else None
+        return ms
+
+    nq, nk = B * T * H * DH, B * T * KV * DH
+
+    # flash-attention backward: reference fragment (axis/compile.py:406-421) on [B,H,T,DH] vs ATTN_BWD on [B,T,H,DH]
+    def ref_flash_bwd(e):
+        q, k, v, do, o = (bf16_buf(e, rng, nq), bf16_buf(e, rng, nk), bf16_buf(e, rng, nk), bf16_buf(e, rng, nq), e.alloc(nq, 2))
+        lse, bD = e.alloc(B * H * T), e.alloc(B * H * T)
+        dqf, dkf, dvf = e.alloc(nq), e.alloc(nk), e.alloc(nk)
+        dq, dk, dv = e.alloc(nq, 2), e.alloc(nk, 2), e.alloc(nk, 2)
+        pre = [op(E.FLASH, a=q, b=k, d=v, c=o, m=T, n=DH, k=KV, batch=B, tb=H, sa=lse, dt=1, alpha=0.125)]
+        pp = E.PackedPlan(pre)
+        e.lib.eng_run_plan(pp.ptr, pp.n, 1)
+        return [op(E.ROWDOT, a=do, b=o, c=bD, m=B * T * H, n=DH, dt=1),
+                op(E.SCALE, a=dqf, c=dqf, n=nq, alpha=0.0), op(E.SCALE, a=dkf, c=dkf, n=nk, alpha=0.0),
+                op(E.SCALE, a=dvf, c=dvf, n=nk, alpha=0.0),
+                op(E.FLASH_BWD, a=q, b=k, d=v, c=do, sa=lse, sb=bD, tb=dqf, sc=dkf, oa=dvf, ob=H, m=T, n=DH, k=KV, batch=B,
+                   dt=1, alpha=0.125),
+                op(E.CAST, a=dqf, c=dq, m=nq, tb=0), op(E.CAST, a=dkf, c=dk, m=nk, tb=0), op(E.CAST, a=dvf, c=dv, m=nk, tb=0)]
+
+    def our_attn_bwd(e):
+        q, k, v, do, o = (bf16_buf(e, rng, nq), bf16_buf(e, rng, nk), bf16_buf(e, rng, nk), bf16_buf(e, rng, nq), e.alloc(nq, 2))
+        lse, scr = e.alloc(B * H * T), e.alloc(B * H * T + nq)
+        dq, dk, dv = e.alloc(nq, 2), e.alloc(nk, 2), e.alloc(nk, 2)
+        pre = [op(E.ATTN_FWD, a=q, b=k, d=v, c=o, sa=lse, m=T, n=DH, k=KV, batch=B, tb=H, dt=1, alpha=0.125)]
+        pp = E.PackedPlan(pre)
+        e.lib.eng_run_plan(pp.ptr, pp.n, 1)
+        return [op(E.ATTN_BWD, a=q, b=k, d=v, c=do, sa=lse, sb=o, tb=dq, sc=dk, oa=dv, ob=H, oc=scr, m=T, n=DH, k=KV,
+                   batch=B, dt=1, alpha=0.125)]
+    fl = 5.0 * B * H * T * T * DH
+    run("reference", "flash-attention backward (row dots, zero fills, kernel, casts)", ref_flash_bwd, 3, flops=fl)
+    run("this", "flash-attention backward (ATTN_BWD)", our_attn_bwd, 3, flops=fl)
+
+    def ref_flash_fwd(e):
+        q, k, v, o = bf16_buf(e, rng, nq), bf16_buf(e, rng, nk), bf16_buf(e, rng, nk), e.alloc(nq, 2)
+        return [op(E.FLASH, a=q, b=k, d=v, c=o, m=T, n=DH, k=KV, batch=B, tb=H, sa=e.alloc(B * H * T), dt=1, alpha=0.125)]
+
+    def our_attn_fwd(e):
+        q, k, v, o = bf16_buf(e, rng, nq), bf16_buf(e, rng, nk), bf16_buf(e, rng, nk), e.alloc(nq, 2)
+        return [op(E.ATTN_FWD, a=q, b=k, d=v, c=o, sa=e.alloc(B * H * T), m=T, n=DH, k=KV, batch=B, tb=H, dt=1, alpha=0.125)]
+    run("reference", "flash-attention forward (FLASH)", ref_flash_fwd, 3, flops=2.0 * B * H * T * T * DH)
+    run("this", "flash-attention forward (ATTN_FWD)", our_attn_fwd, 3, flops=2.0 * B * H * T * T * DH)
+
+    # RMSNorm backward + weight gradient (axis/compile.py:397-400) vs the fused pass with residual
+    def ref_norm_bwd(e):
+        x, w, g = bf16_buf(e, rng, N * D), bf16_buf(e, rng, D), bf16_buf(e, rng, N * D)
+        dx, tmp, dw = e.alloc(N * D, 2), e.alloc(N * D, 2), e.alloc(D)
+        res, out_ = bf16_buf(e, rng, N * D), e.alloc(N * D, 2)
+        return [op(E.RMSNORM_BWD, a=x, b=w, d=g, c=dx, tb=tmp, m=N, n=D, dt=1, alpha=1e-5),
+                op(E.COLSUM, a=tmp, c=dw, m=N, n=D, dt=2),
+                op(E.ADD, a=res, b=dx, c=out_, n=N * D, dt=1)]
+
+    def our_norm_bwd(e):
+        x, w, g, res = bf16_buf(e, rng, N * D), bf16_buf(e, rng, D), bf16_buf(e, rng, N * D), bf16_buf(e, rng, N * D)
+        dx, dw, scr = e.alloc(N * D, 2), e.alloc(D), e.alloc(296 * D)
+        return [op(E.RMSNORM_BWD_ACC, a=x, b=w, d=g, c=dx, tb=res, sa=dw, sb=scr, m=N, n=D, dt=1, alpha=1e-5)]
+    nb = 4 * N * D * 2
+    run("reference", "RMSNorm backward + column sum + residual add", ref_norm_bwd, 8, algo_bytes=nb)
+    run("this", "RMSNorm backward (RMSNORM_BWD_ACC: dx + residual + dw)", our_norm_bwd, 8, algo_bytes=nb)
+
+    def ref_norm(e):
+        x, w, y = bf16_buf(e, rng, N * D), bf16_buf(e, rng, D), e.alloc(N * D, 2)
+        return [op(E.RMSNORM, a=x, b=w, c=y, m=N, n=D, dt=1, alpha=1e-5)]
+    run("reference", "RMSNorm forward", ref_norm, 8, algo_bytes=2 * N * D * 2)
+    run("this", "RMSNorm forward", ref_norm, 8, algo_bytes=2 * N * D * 2)
+
+    # count + cross-entropy (axis/compile.py:369-372) vs CE_FUSED
+    tg_f = rng.integers(0, V, N).astype(np.float32)
+
+    def ref_ce(e):
+        lg, dl = bf16_buf(e, rng, N * V), e.alloc(N * V, 2)
+        tg = e.alloc(N)
+        e.lib.eng_upload(tg, tg_f.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), N)
+        loss, den = e.alloc(1), e.alloc(1)
+        return [op(E.SCALE, a=loss, c=loss, n=1, alpha=0.0), op(E.SCALE, a=den, c=den, n=1, alpha=0.0),
+                op(E.COUNTVALID, a=tg, c=den, m=N), op(E.CE, a=lg, b=tg, c=dl, d=loss, sa=den, m=N, n=V, dt=1)]
+
+    def our_ce(e):
+        lg = bf16_buf(e, rng, N * V)
+        tg = e.alloc(N)
+        ti = rng.integers(0, V, N).astype(np.int32).view(np.float32)
+        e.lib.eng_upload(tg, ti.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), N)
+        loss, den, scr = e.alloc(1), e.alloc(1), e.alloc(N + 8)
+        return [op(E.CE_FUSED, a=lg, b=tg, c=lg, d=loss, sa=den, sb=scr, m=N, n=V, dt=1)]
+    run("reference", "count + cross-entropy forward/backward", ref_ce, 1, algo_bytes=2 * N * V * 2)
+    run("this", "cross-entropy (CE_FUSED, in place)", our_ce, 1, algo_bytes=2 * N * V * 2)
+
+    # clip + AdamW over 16 tensors of 1536 x 4096 (axis/compile.py:497-532) vs the flat pass
+    nt, el = 16, D * MLP
+
+    def ref_adamw(e):
+        ps = [(e.alloc(el), e.alloc(el), e.alloc(el), e.alloc(el), e.alloc(el, 2)) for _ in range(nt)]
+        for (p_, g_, m_, v_, _) in ps:
+            e.fill(p_, el * 4, rng, 0.02); e.fill(g_, el * 4, rng, 1e-3); e.fill(m_, el * 4, rng, 0.0); e.fill(v_, el * 4, rng, 0.0)
+        gn, gs, t_, lr = e.alloc(1), e.alloc(1), e.alloc(1), e.alloc(1)
+        one = np.array([3e-4], np.float32)
+        e.lib.eng_upload(lr, one.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), 1)
+        z = np.zeros(1, np.float32)
+        e.lib.eng_upload(t_, z.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), 1)
+        return ([op(E.SCALE, a=gn, c=gn, n=1, alpha=0.0)] + [op(E.L2ACC, a=g_, c=gn, n=el) for (_, g_, _, _, _) in ps] +
+                [op(E.CLIPSCALE, a=gn, c=gs, alpha=1.0), op(E.TICK, a=t_)] +
+                [op(E.ADAMW, a=p_, b=g_, c=m_, d=v_, tb=t_, sa=mir, sb=lr, oa=gs, n=el, alpha=3e-4, beta=0.1, gamma=1e-8)
+                 for (p_, g_, m_, v_, mir) in ps])
+
+    def our_adamw(e):
+        n = nt * el
+        p_, g_, m_, v_, mir = e.alloc(n), e.alloc(n), e.alloc(n), e.alloc(n), e.alloc(n, 2)
+        e.fill(p_, n * 4, rng, 0.02); e.fill(g_, n * 4, rng, 1e-3); e.fill(m_, n * 4, rng, 0.0); e.fill(v_, n * 4, rng, 0.0)
+        fl_ = e.alloc(n // 1024, 1)
+        ones = np.ones(n // 1024, np.uint8).view(np.float32)
+        e.lib.eng_upload(fl_, ones.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), ones.size)
+        t_, lr, part, ss, gn = e.alloc(1), e.alloc(1), e.alloc(n // 8192 + 1), e.alloc(1), e.alloc(1)
+        one = np.array([3e-4], np.float32)
+        e.lib.eng_upload(lr, one.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), 1)
+        z = np.zeros(1, np.float32)
+        e.lib.eng_upload(t_, z.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), 1)
+        return [op(E.GNORM_FLAT, a=g_, c=part, d=ss, ob=0, m=n // 1024, oa=0, tb=t_),
+                op(E.ADAMW_FLAT, a=p_, b=g_, c=m_, d=v_, m=n // 1024, k=0, sa=mir, sb=lr, tb=t_, sc=fl_, oa=ss, ob=1, oc=gn,
+                   alpha=1.0, beta=0.1, gamma=1e-8)]
+    run("reference", "L2 norm + clip + per-tensor AdamW (16 tensors, 100.7 M params)", ref_adamw, 1, algo_bytes=34 * nt * el)
+    run("this", "clip + AdamW over the flat arena (100.7 M params)", our_adamw, 1, algo_bytes=34 * nt * el)
+
+    # rotary on q: reference permutes to [B,H,T,DH] and rotates there (axis/compile.py:319-323); here in place on [B,T,H,DH]
+    half = DH // 2
+    ang = np.outer(np.arange(T, dtype=np.float32), 1.0 / (10000.0 ** (np.arange(half, dtype=np.float32) / half)))
+    cosv, sinv = np.cos(ang).astype(np.float32).reshape(-1), np.sin(ang).astype(np.float32).reshape(-1)
+
+    def tables(e):
+        cs, sn = e.alloc(T * half), e.alloc(T * half)
+        e.lib.eng_upload(cs, cosv.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), cosv.size)
+        e.lib.eng_upload(sn, sinv.ctypes.data_as(e.ct.POINTER(e.ct.c_float)), sinv.size)
+        return cs, sn
+
+    def ref_rope(e):
+        cs, sn = tables(e)
+        x, xp, xr = bf16_buf(e, rng, nq), e.alloc(nq, 2), e.alloc(nq, 2)
+        return [op(E.PERM_0213, a=x, c=xp, m=B, n=T, k=H, batch=DH, dt=1),
+                op(E.ROPE, a=xp, b=cs, d=sn, c=xr, batch=B * H, m=T, n=DH, dt=1)]
+
+    def our_rope(e):
+        cs, sn = tables(e)
+        x = bf16_buf(e, rng, nq)
+        return [op(E.ROPE_BTHD, a=x, b=cs, d=sn, c=x, batch=B, m=T, k=H, n=DH, dt=1)]
+    run("reference", "head permute + rotary on q", ref_rope, 6, algo_bytes=2 * nq * 2)
+    run("this", "rotary in place on [B,T,H,DH] (ROPE_BTHD)", our_rope, 6, algo_bytes=2 * nq * 2)
+
+    def silu_bwd(e):
+        g, u, gr = bf16_buf(e, rng, N * MLP), bf16_buf(e, rng, N * MLP), bf16_buf(e, rng, N * MLP)
+        return [op(E.SILU_BWD, a=g, b=u, d=gr, c=e.alloc(N * MLP, 2), tb=e.alloc(N * MLP, 2), n=N * MLP, dt=1)]
+    run("reference", "SwiGLU backward (SILU_BWD)", silu_bwd, 2, algo_bytes=5 * N * MLP * 2)
+    run("this", "SwiGLU backward (SILU_BWD)", silu_bwd, 2, algo_bytes=5 * N * MLP * 2)
+
+    # GEMMs: the reference calls cuBLAS (runtime.cu:878-917)
+    for (m, n, k, tb, dt) in [(N, MLP, D, 0, 1), (N, D, MLP, 0, 1), (N, D, D, 1, 1), (D, MLP, N, 2, 2), (N, V, D, 1, 1)]:
+        def gemm(e, m=m, n=n, k=k, tb=tb, dt=dt):
+            a, b_ = bf16_buf(e, rng, m * k), bf16_buf(e, rng, k * n)
+            return [op(E.GEMM_SB, a=a, b=b_, c=e.alloc(m * n, 2 if dt == 1 else 4), m=m, n=n, k=k, batch=1, tb=tb, dt=dt)]
+        nm = f"GEMM tb={tb} dt={dt} {m}x{n}x{k}"
+        ch = 1 if m * n > (1 << 27) else 4
+        run("reference", nm + " (cuBLAS)", gemm, ch, flops=2.0 * m * n * k)
+        run("this", nm, gemm, ch, flops=2.0 * m * n * k)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what")
@@ -223,9 +488,13 @@ def main():
                  ("DH", 64), ("rows", 8192), ("dim", 1536), ("V", 32000), ("count", 8192 * 4096), ("reps", 20), ("fallback", 0),
                  ("chain", 1)):
         ap.add_argument("--" + a, type=int, default=d)
+    ap.add_argument("--lib", default=os.path.join(ROOT, "oracle", "_ref", "libaxeng_ref.so"))
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--check", action="store_true")
     a = ap.parse_args()
+    if a.what == "refcmp":
+        refcmp(a.lib, a.reps)
+        return
     b = Bench(a.reps, not a.no_flush)
     w = a.what
     if w == "gemm":
