@@ -403,14 +403,16 @@ class CompiledTransformer:
                     op(GEMM_SB, a=u, b=P[key + ".lora_b"], c=y, m=N, k=lora_r, n=fout, batch=1, dt=DT,
                        alpha=sc_l, beta=1.0)]
 
-        def lin_f_group(x, i, prefs, ys_):
-            """ys_[g] = x@W_g for projections that share their input: one grouped launch (+ adapters)"""
+        def lin_f_group(x, i, prefs, ys_, rope=False):
+            """ys_[g] = x@W_g for projections that share their input: one grouped launch (+ adapters).  rope: the
+            first two outputs (query and key projections) leave the launch with the rotary embedding applied"""
             fin = lin_geom[prefs[0]][0]
             fo = [lin_geom[p][1] for p in prefs] + [0]
             w = [P[f"blocks.{i}.{p}.weight"] for p in prefs] + [0]
             yy = list(ys_) + [0]
             o_ = [op(GEMM_GROUP, a=x, b=w[0], sa=w[1], sb=w[2], c=yy[0], d=yy[1], sc=yy[2], m=N, k=fin,
-                     n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, dt=DT)]
+                     n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, dt=DT,
+                     beta=float(b_cos) if rope else 0.0, gamma=float(b_sin) if rope else 0.0)]
             for p_, y_ in zip(prefs, ys_):
                 o_ += lora_f(x, i, p_, y_)
             return o_
@@ -467,13 +469,15 @@ class CompiledTransformer:
             plan = []
             p = f"blocks.{i}."
             plan += [op(RMSNORM, a=xs[i], b=P[p + "attn_norm.weight"], c=ys[i], m=N, n=D, dt=DT, alpha=eps)]
-            plan += lin_f_group(ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), (q2s[i], k2s[i], vs[i]))
-            plan += [
-                op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT,
-                   sa=k2s[i], sb=k2s[i], sc=KV),                     # q and k in one launch
-                op(ATTN_FWD, a=q2s[i], b=k2s[i], d=vs[i], c=at2s[i], sa=lses[i],
-                   m=T, n=DH, k=KV, batch=B, tb=H, dt=DT, alpha=scale),
-            ]
+            # rotary of q and k: in the epilogue of the projection launch (head_dim 64, no adapters: an adapter's
+            # contribution is added to the projection before the rotation), else one launch over both, in place
+            fuse_rope = DH == 64 and not lora
+            plan += lin_f_group(ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), (q2s[i], k2s[i], vs[i]), rope=fuse_rope)
+            if not fuse_rope:
+                plan += [op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT,
+                            sa=k2s[i], sb=k2s[i], sc=KV)]
+            plan += [op(ATTN_FWD, a=q2s[i], b=k2s[i], d=vs[i], c=at2s[i], sa=lses[i],
+                        m=T, n=DH, k=KV, batch=B, tb=H, dt=DT, alpha=scale)]
             plan += lin_f(at2s[i], i, "attn.o_proj", r1s[i], res=xs[i])
             plan += [op(RMSNORM, a=r1s[i], b=P[p + "mlp_norm.weight"], c=zs[i], m=N, n=D, dt=DT, alpha=eps)]
             if lora:

@@ -404,6 +404,17 @@ static int do_gemm_group(const EngOp* op) {
         }
     }
     const int dt = op->dt;
+    // mode 1 with gamma > 0: outputs 0 and 1 (the query and key projections) leave the op with the rotary embedding
+    // applied; beta / gamma hold the buffer indices of the cos / sin tables ([T, 32] fp32: head_dim 64)
+    const float* rcos = nullptr; const float* rsin = nullptr; int ropeT = 0;
+    if (op->gamma > 0.f) {
+        const int ic = (int)op->beta, is = (int)op->gamma;
+        if (mode != 1 || count < 2 || op->tb != 0 || op->n % 64 || op->oa % 64) { set_err("gemm_group: rotary needs mode 1 and head_dim 64"); return 112; }
+        NEED(ic, 128); NEED(is, 128);
+        ropeT = (int)(G.bufs[ic].bytes / 128);
+        NEED(is, (long long)ropeT * 128);
+        rcos = (const float*)BUFP(ic); rsin = (const float*)BUFP(is);
+    }
     if (dt >= 1 && !(G.fallback & 1) && !(G.fallback & 4)) {
         const long long ei = 2, eo = dt == 1 ? 2 : 4;
         const void* A[3]; const void* B[3]; void* C[3]; int mv[3], nv[3], kv[3];
@@ -413,6 +424,7 @@ static int do_gemm_group(const EngOp* op) {
             A[g] = BUFP(q->a); B[g] = BUFP(q->b); C[g] = BUFP(q->c); mv[g] = q->m; nv[g] = q->n; kv[g] = q->k;
         }
         const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
+        if (rcos) ax_gemm_group_rope(rcos, rsin, ropeT, 3);
         const int rc = ax_gemm_tc2_group(dt == 1, op->tb, mode, count, A, B, C, mv, nv, kv, alpha, G.d_status, G.cur);
         if (rc == 0) { G.launches++; return 0; }
         if (rc > 0) { set_err("grouped tensor-core gemm failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
@@ -420,6 +432,13 @@ static int do_gemm_group(const EngOp* op) {
     for (int g = 0; g < count; g++) {
         const int rc = do_gemm(&sub[g], false);
         if (rc) return rc;
+    }
+    if (rcos) {          // unfused: the rotary kernel over the two projections, in place
+        const long long e2 = esz(dt);
+        NEED(op->c, (long long)op->m * op->n * e2); NEED(op->d, (long long)op->m * op->oa * e2);
+        G.launches++;
+        return ax_rope2(dt, BUFP(op->c), rcos, rsin, BUFP(op->c), ropeT, 64, (long long)op->m * (op->n / 64), op->n / 64, 0,
+                        BUFP(op->d), BUFP(op->d), (long long)op->m * (op->oa / 64), op->oa / 64, G.cur);
     }
     return 0;
 }

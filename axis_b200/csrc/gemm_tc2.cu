@@ -112,7 +112,17 @@ struct GemmGroup {
     int n[3];
     int kb[3];
     int m[3];
+    // rotary embedding in the epilogue of a mode-1 launch with bf16 output: the outputs g whose bit is set in
+    // rope_mask are [rows, heads * 64] projections (row = batch * rope_T + token); every 64-column piece of the
+    // epilogue is one head, its columns i and i + 32 form a rotary pair (tables: fp32 [rope_T, 32])
+    const float* rope_cos;
+    const float* rope_sin;
+    int rope_T, rope_mask;
 };
+static GemmGroup g_rope_req = {};        // rotary request for the next grouped launch (host side, one stream of launches)
+void ax_gemm_group_rope(const float* cs, const float* sn, int T, int mask) {
+    g_rope_req.rope_cos = cs; g_rope_req.rope_sin = sn; g_rope_req.rope_T = T; g_rope_req.rope_mask = mask;
+}
 
 template <int A_MN, int B_MN, typename TO>
 __global__ void __launch_bounds__(THREADS2, 1)
@@ -323,6 +333,8 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const int m_g = grp.mode == 3 ? grp.m[g] : m;
             const int npc = (tma_out && !swiglu && row0 < m_g) ? (ncols + cw - 1) / cw : 0;   // pieces this warp writes
             const uint32_t pbase = pieces;
+            const bool do_rope = sizeof(TO) == 2 && grp.mode == 1 && ((grp.rope_mask >> g) & 1);
+            const int rope_t = do_rope ? (row < m_g ? row : 0) % grp.rope_T : 0;
             auto fetch_d = [&](int j) {                          // lane 0: addend piece j of this tile -> its buffer
                 const uint32_t bi = (pbase + j) & 3;
                 mbar_expect_tx(my_bar_d + 8 * bi, 4096);
@@ -411,6 +423,32 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                                 f.x += beta * d.x; f.y += beta * d.y; f.z += beta * d.z; f.w += beta * d.w;
                             }
                             *slot = f;
+                        }
+                    } else if (do_rope) {
+                        // the piece is one head: rotate the pairs (i, i + 32) in fp32, round once
+                        uint32_t r2[32];
+                        tmem_ld32(taddr + c + 32, r2);
+                        tmem_ld_wait();
+                        const float* cr = grp.rope_cos + (long long)rope_t * 32;
+                        const float* sr = grp.rope_sin + (long long)rope_t * 32;
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const float4 c0 = __ldg(reinterpret_cast<const float4*>(cr + q * 8)), c1 = __ldg(reinterpret_cast<const float4*>(cr + q * 8 + 4));
+                            const float4 s0 = __ldg(reinterpret_cast<const float4*>(sr + q * 8)), s1 = __ldg(reinterpret_cast<const float4*>(sr + q * 8 + 4));
+                            const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                            float o1[8], o2[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const float x1 = a_eff * __uint_as_float(r[q * 8 + e]), x2 = a_eff * __uint_as_float(r2[q * 8 + e]);
+                                o1[e] = x1 * cc[e] - x2 * ss[e];
+                                o2[e] = x1 * ss[e] + x2 * cc[e];
+                            }
+                            uint4 pk;
+                            pk.x = pack2_bf16(o1[0], o1[1]); pk.y = pack2_bf16(o1[2], o1[3]); pk.z = pack2_bf16(o1[4], o1[5]); pk.w = pack2_bf16(o1[6], o1[7]);
+                            *reinterpret_cast<uint4*>(buf + ((q ^ (lane & 7)) << 4)) = pk;
+                            pk.x = pack2_bf16(o2[0], o2[1]); pk.y = pack2_bf16(o2[2], o2[3]); pk.z = pack2_bf16(o2[4], o2[5]); pk.w = pack2_bf16(o2[6], o2[7]);
+                            *reinterpret_cast<uint4*>(buf + (((4 + q) ^ (lane & 7)) << 4)) = pk;
                         }
                     } else {
 #pragma unroll
@@ -543,6 +581,13 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     const int m = mv[0], n = nv[0], k = kv[0];
     GemmGroup grp = {};
     grp.mode = mode; grp.count = count;
+    if (g_rope_req.rope_mask) {              // a rotary request is honoured by a mode-1 bf16 launch or refused
+        grp.rope_cos = g_rope_req.rope_cos; grp.rope_sin = g_rope_req.rope_sin;
+        grp.rope_T = g_rope_req.rope_T; grp.rope_mask = g_rope_req.rope_mask;
+        g_rope_req.rope_mask = 0;
+        if (mode != 1 || sizeof(TO) != 2 || grp.rope_T < 1 || !grp.rope_cos || !grp.rope_sin) return -1;
+        for (int g = 0; g < count; g++) if (((grp.rope_mask >> g) & 1) && nv[g] % 64) return -1;
+    }
     CUtensorMap tmA[3], tmB[3], tmC[3], tmD;
     int tiles_n = 0;
     if (mode == 0) {
@@ -580,6 +625,7 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
         c_ok = c_ok && ((uintptr_t)C[g] & 15) == 0 && ((long long)nv[per_problem_c ? g : 0] * osz) % 16 == 0;
     if (c_ok && (!has_d || ((uintptr_t)D & 15) == 0)) tma_out = has_d ? 2 : 1;
     if (mode != 0 && (tma_out != 1 || ksplit != 1)) return -1;          // grouped launches need the plain TMA-store epilogue
+    if (grp.rope_mask && tma_out != 1) return -1;
     if (tma_out) {
         size_t wsb0 = 0;
         if (per_problem_c) {
@@ -667,15 +713,18 @@ int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, con
 // B[1] = up weights (both n[0] wide), C[0] = g, C[1] = u, C[2] = silu(g) * u; bf16 output only.
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
                       const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st) {
-    if (count < 2 || count > 3 || mode < 1 || mode > 4) return -1;
-    if (mode == 4 && (!out_bf16 || count != 2 || !aligned16(C[2]))) return -1;
+    const int rope_mask = g_rope_req.rope_mask;
+    if (count < 2 || count > 3 || mode < 1 || mode > 4) { g_rope_req.rope_mask = 0; return -1; }
+    if (mode == 4 && (!out_bf16 || count != 2 || !aligned16(C[2]))) { g_rope_req.rope_mask = 0; return -1; }
+    if (rope_mask && (mode != 1 || !out_bf16 || tb != 0)) { g_rope_req.rope_mask = 0; return -1; }
     for (int g = 0; g < count; g++) {
-        if (!aligned16(A[(mode == 2 || mode == 3) ? g : 0]) || !aligned16(B[g])) return -1;
+        bool bad = !aligned16(A[(mode == 2 || mode == 3) ? g : 0]) || !aligned16(B[g]);
         const int mg = m[mode == 3 ? g : 0], ng = n[(mode == 1 || mode == 3) ? g : 0], kg = k[mode == 2 ? g : 0];
-        if (mg < 256 || ng < 8 || kg < 8) return -1;
-        if (tb == 0) { if (kg % 8 || ng % 8) return -1; }
-        else if (tb == 1) { if (kg % 8) return -1; }
-        else { if (mg % 8 || ng % 8) return -1; }
+        bad = bad || mg < 256 || ng < 8 || kg < 8;
+        if (tb == 0) bad = bad || kg % 8 || ng % 8;
+        else if (tb == 1) bad = bad || kg % 8;
+        else bad = bad || mg % 8 || ng % 8;
+        if (bad) { g_rope_req.rope_mask = 0; return -1; }
     }
 #define G2(AM, BMj, SL)                                                                                                        \
     (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, mode, count, A, B, C, nullptr, m, n, k, alpha, 0.f, status, 1, st)            \

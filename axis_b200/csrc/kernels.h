@@ -107,6 +107,10 @@ int ax_attn_bwd_simt(int dt, int out_dt, const void* q, const void* k, const voi
 // gemm_tc2.cu — grouped launch of the paired-CTA GEMM (mode 1: shared A, per-problem B/C/n; mode 2: one C summed
 // over per-segment A/B/k; mode 3: independent problems A/B/C/m/n of one depth k).  -1 when not served.
 void ax_gemm_side(int on);
+// Rotary request for the NEXT ax_gemm_tc2_group call (mode 1, bf16 output, tb 0): outputs g with bit g of `mask` set are
+// [rows, heads * 64] projections and leave the launch rotated (tables fp32 [T, 32], row = batch * T + token).  The call
+// either honours the request or returns -1; it never ignores it.
+void ax_gemm_group_rope(const float* cs, const float* sn, int T, int mask);
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
                       const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st);
 

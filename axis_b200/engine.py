@@ -103,7 +103,10 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                2 side stream of the overlapped weight-gradient GEMMs)
     EVENT: tb=1 record event oa on stream sa / tb=2 stream sa waits for event oa (sa as STREAM's tb)
     GEMM_GROUP: batch = 2 or 3 GEMMs of one layer as one launch; m, tb, dt, alpha as GEMM_SB.
-               oc=1 (one input, several outputs): a=A; b,sa,sb = B_g; c,d,sc = C_g; n,oa,ob = n_g; k
+               oc=1 (one input, several outputs): a=A; b,sa,sb = B_g; c,d,sc = C_g; n,oa,ob = n_g; k;
+                    gamma > 0: outputs 0 and 1 are [m, heads*64] query / key projections (row = batch*T + token)
+                    and leave the op with the rotary embedding applied; beta / gamma = buffer indices of the
+                    cos / sin tables ([T, 32] fp32)
                oc=2 (one output summed over K-segments): c=C; a,sa,sb = A_s; b,d,sc = B_s;
                k,oa,ob = k_s; n
                oc=3 (two independent problems of one depth k): a,sa = A_g; b,sb = B_g; c,d = C_g;

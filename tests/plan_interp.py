@@ -180,6 +180,13 @@ class InterpEngine:
                                beta=1.0 if g_ else 0.0)
                 self.launches += 1
                 self._gemm(sub, False)
+            if oc == 1 and gamma > 0:       # rotary on the first two outputs ([m, heads*64], row = batch*T + token)
+                T_ = self.bufs[int(beta)].size // (32 * 4)
+                cos = self._f32(int(beta), T_ * 32).reshape(T_, 32)
+                sin = self._f32(int(gamma), T_ * 32).reshape(T_, 32)
+                for buf_, width in ((c, n), (d, oa)):
+                    x = self._get(buf_, m * width, dt).reshape(m // T_, T_, width // 64, 64).transpose(0, 2, 1, 3)
+                    self._put(buf_, O.rope_fwd(x, cos, sin).transpose(0, 2, 1, 3), dt)
             return None
         if kind == E.EMBED_I32:
             ids = self.bufs[b].view(np.int32)[:m]

@@ -7,6 +7,7 @@ import pytest
 
 from axis_b200 import engine as E
 from axis_b200.engine import Engine, op
+from oracle import step_numpy as O
 
 pytestmark = pytest.mark.gpu
 
@@ -239,4 +240,38 @@ def test_grouped_gemm_swiglu_pair(eng, dt, m, n, k):
     check(get_(og), g.astype(np.float32), dt == 1, k)
     check(get_(ou), u.astype(np.float32), dt == 1, k)
     check(get_(oh), h.astype(np.float32), dt == 1, k)
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("fallback", [0, 1])
+def test_grouped_projection_with_rotary_in_the_epilogue(eng, fallback):
+    """GEMM_GROUP mode 1 with gamma > 0: q and k leave the launch rotated, v does not.  fallback 0: the paired-CTA
+    kernel rotates in its epilogue (fp32 accumulators, one rounding); fallback 1: general GEMMs, then the rotary kernel."""
+    rng = np.random.default_rng(5)
+    B_, T, D, H, KV = 2, 256, 192, 6, 2
+    N = B_ * T
+    bf = lambda a: E.bf16_bits_to_f32(E.f32_to_bf16_bits(a))
+    x = bf(rng.standard_normal((N, D)).astype(np.float32))
+    wq, wk, wv = (bf(rng.standard_normal((D, w)).astype(np.float32) * 0.1) for w in (H * 64, KV * 64, KV * 64))
+    cos, sin = O.rope_tables(T, 64)
+
+    def put(a, bf16=True):
+        i = eng.alloc(a.size, 2 if bf16 else 4)
+        eng.upload_bf16(i, a) if bf16 else eng.upload(i, a)
+        return i
+    ix, iq, ik, iv = put(x), put(wq), put(wk), put(wv)
+    ic, isn = put(cos, False), put(sin, False)
+    oq, ok_, ov = eng.alloc(N * H * 64, 2), eng.alloc(N * KV * 64, 2), eng.alloc(N * KV * 64, 2)
+    eng.set_fallback(fallback)
+    eng.launch_count(reset=True)
+    eng.run([op(E.GEMM_GROUP, a=ix, b=iq, sa=ik, sb=iv, c=oq, d=ok_, sc=ov, m=N, k=D, n=H * 64, oa=KV * 64, ob=KV * 64,
+                batch=3, oc=1, dt=1, beta=float(ic), gamma=float(isn))])
+    launches = eng.launch_count()
+    eng.set_fallback(0)
+    assert launches == (1 if fallback == 0 else 4)
+    rot = lambda y, heads: O.rope_fwd(y.reshape(B_, T, heads, 64).transpose(0, 2, 1, 3), cos, sin).transpose(0, 2, 1, 3).reshape(N, heads * 64)
+    q_ref, k_ref, v_ref = rot(x @ wq, H), rot(x @ wk, KV), x @ wv
+    for got, ref in ((eng.download_bf16(oq, (N, H * 64)), q_ref), (eng.download_bf16(ok_, (N, KV * 64)), k_ref),
+                     (eng.download_bf16(ov, (N, KV * 64)), v_ref)):
+        assert np.abs(got - ref).max() <= 1.2e-2 * np.abs(ref).max()
     assert eng.device_status() == 0

@@ -71,16 +71,17 @@ def test_reference_python_drives_this_library(ref, dtype, loss_tol, grad_tol):
 
 
 def test_reference_python_capture_and_replay_on_this_library(ref):
-    """The reference's graph path (capture / replay_step / set_lr, axis/compile.py:560-573) on this library:
-    three replayed steps equal three eager steps of a second instance bit for bit."""
+    """The reference's graph path (capture / replay_step, axis/compile.py:560-573) on this library: three
+    replayed steps track three eager steps of a second instance.  Not bit for bit: the reference's own op kinds
+    that its plan uses here sum with fp32 atomics (row losses in CE, EMBED_BWD, L2ACC), as in its own engine."""
     a = ref["CT"](_our_lib(), ref["cfg"], ref["weights"], ref["B"], ref["T"], tf32=False, max_grad_norm=1.0)
     eager = [a.step(ref["inp"], ref["tgt"]) for _ in range(3)]
     wa = a.get_weights()
     b = ref["CT"](_our_lib(), ref["cfg"], ref["weights"], ref["B"], ref["T"], tf32=False, max_grad_norm=1.0)
     b.capture()
     replayed = [b.replay_step(ref["inp"], ref["tgt"]) for _ in range(3)]
-    assert replayed == eager
+    assert np.allclose(replayed, eager, rtol=2e-6, atol=0)
     wb = b.get_weights()
     for n in wa:
-        assert np.array_equal(wa[n], wb[n]), n
+        assert np.abs(wa[n] - wb[n]).max() <= 1e-6, n
     assert eager[2] < eager[0]

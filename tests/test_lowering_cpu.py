@@ -387,3 +387,22 @@ def test_7b_plan_fits_the_32bit_op_descriptor(world):
     # and the packer refuses what it cannot represent instead of wrapping
     with pytest.raises(OverflowError):
         E.PackedPlan([E.op(E.CAST, a=0, c=1, m=ct._P_total if ct._P_total > 2 ** 31 else 2 ** 31 + 5)])
+
+
+@pytest.mark.parametrize("dtype,lim_l,lim_g", [("fp32", 2e-6, 1e-5), ("bf16", 2e-3, 3e-2)])
+def test_head_dim_64_plan_with_rotary_inside_the_projection_and_the_attention_backward(dtype, lim_l, lim_g):
+    """At head_dim 64 the plan has no rotary op of its own: the forward rotation rides in the q/k/v projection launch
+    (GEMM_GROUP with gamma > 0) and the inverse one in ATTN_BWD.  Against the oracle."""
+    from axis_b200 import engine as E
+    cfg = dict(vocab_size=70, dim=128, n_layers=2, n_heads=2, n_kv_heads=1, mlp_hidden=96, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=11)
+    rng = np.random.default_rng(11)
+    x, y = O.make_batch(rng, 70, 2, 24, 0.1)
+    l_ref, g_ref = O.OracleTransformer(cfg, w0).loss_and_grads(x, y)
+    ct = CompiledTransformer(InterpEngine(), cfg, w0, 2, 24, dtype=dtype, max_grad_norm=1.0)
+    assert not any(o[0] in (E.ROPE, E.ROPE_BTHD) for o in ct.plan_step)
+    loss = ct.forward_backward(x, y)
+    assert abs(loss - l_ref) <= lim_l * abs(l_ref)
+    g = ct.grads()
+    for nm in g_ref:
+        assert rel(g[nm], g_ref[nm]) <= lim_g, nm
