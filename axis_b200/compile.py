@@ -168,11 +168,11 @@ class CompiledTransformer:
         def bucket_of(nm: str) -> int:
             if nm in ("norm.weight", "lm_head.weight"):
                 return 0
-            if nm == "embed.weight":
-                return 1 + (L - 1) // bucket_layers
+            if nm == "embed.weight":         # its scatter-add ends the backward: a bucket of its own, reduced last
+                return 2 + (L - 1) // bucket_layers
             layer = int(nm.split(".")[1])
             return 1 + (L - 1 - layer) // bucket_layers
-        nb = 2 + (L - 1) // bucket_layers
+        nb = 3 + (L - 1) // bucket_layers
         self._nbuckets = nb
         off = 0
         self._off: Dict[str, int] = {}
@@ -490,12 +490,24 @@ class CompiledTransformer:
                 plan += lin_f(hs[i], i, "mlp.down_proj", xs[i + 1], res=r1s[i])
             return plan
 
-        plan = [op(EMBED_I32, a=P["embed.weight"], b=self.b_ids, c=xs[0], m=N, n=D, dt=DT)]
+        # ZeRO-1: the owners' bf16 segments are broadcast at the START of the step, bucket by bucket in forward
+        # order on the collectives stream, and the forward waits for a bucket's event just before its first use —
+        # the gather of the weights that the previous step's AdamW wrote overlaps the forward instead of ending
+        # that step on the main stream.  (The first step broadcasts the initial weights: a no-op in value.)
+        EV_W = 1 << 14                         # event ids of the weight buckets (the side-stream ids stay below)
+        self._w_events = zero and not lora
+
+        def wait_weights(b):
+            return [op(EVENT, tb=2, sa=0, oa=EV_W + b)] if self._w_events else []
+        plan = wait_weights(nb - 1) + [op(EMBED_I32, a=P["embed.weight"], b=self.b_ids, c=xs[0], m=N, n=D, dt=DT)]
         for i in range(L):
+            if i == 0 or bucket_of(f"blocks.{i}.x") != bucket_of(f"blocks.{i - 1}.x"):
+                plan += wait_weights(bucket_of(f"blocks.{i}.x"))
             plan += block_f(i)
 
         # ── head + loss ──
         lm_w = P["embed.weight"] if tied else P["lm_head.weight"]
+        plan += wait_weights(0)
         plan += [
             op(RMSNORM, a=xs[L], b=P["norm.weight"], c=xf, m=N, n=D, dt=DT, alpha=eps),
             op(GEMM_SB, a=xf, b=lm_w, c=logits, m=N, k=D, n=V, batch=1, tb=(1 if tied else 0), dt=DT),
@@ -541,7 +553,7 @@ class CompiledTransformer:
             plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
             plan += before_write(dcur)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
-            if (L - 1 - i) % bucket_layers == bucket_layers - 1 and i > 0:
+            if (L - 1 - i) % bucket_layers == bucket_layers - 1 or i == 0:
                 plan += flush_dw()
                 marks[1 + (L - 1 - i) // bucket_layers] = len(plan)
                 mark_ev[1 + (L - 1 - i) // bucket_layers] = ev[0]
@@ -602,11 +614,25 @@ class CompiledTransformer:
                         m=sl // CHUNK, k=s0 // CHUNK, sa=(self.a_mirror if hf else 0), sb=self.b_lr,
                         tb=self.b_t, sc=self.b_wdflag, oa=self.b_sumsq, ob=cw, oc=self.b_gnorm,
                         alpha=float(max_norm or 0.0), beta=self.wd, gamma=adam_eps)]
-            if zero:
+            if zero and not self._w_events:
                 ops_ += self._mirror_bcast_ops()
             return ops_
         self._opt_ops = opt_ops
-        self.plan_step = self._plan_fb_sync + opt_ops(max_grad_norm)
+
+        def gather_ops():
+            """mirror broadcasts of every bucket in forward order on the collectives stream, one event each"""
+            if not self._w_events:
+                return []
+            out = [op(FORK), op(STREAM, tb=1)]
+            for b in reversed(range(nb)):
+                segs = [(r, self._groups[r][b]) for r in range(cw) if self._groups[r][b][1] > 0]
+                if segs:
+                    out += [op(GROUP, tb=0)] + [op(BROADCAST, a=self.a_mirror, m=ln // CHUNK, oa=st // CHUNK, tb=r, dt=1)
+                                                for r, (st, ln) in segs] + [op(GROUP, tb=1)]
+                out += [op(EVENT, tb=1, sa=1, oa=EV_W + b)]
+            return out + [op(STREAM, tb=0)]
+        self._gather_ops = gather_ops
+        self.plan_step = gather_ops() + self._plan_fb_sync + opt_ops(max_grad_norm)
         self._plan_noclip = None
         self._captured = False
         self._pending_loss = None            # read-back ticket of the last replay_step_async
@@ -646,7 +672,7 @@ class CompiledTransformer:
         else:
             # parity path: bias correction for step t, no clipping
             if self._plan_noclip is None:
-                self._plan_noclip = self._plan_fb_sync + self._opt_ops(0.0)
+                self._plan_noclip = self._gather_ops() + self._plan_fb_sync + self._opt_ops(0.0)
             self.eng.upload(self.b_t, np.array([t - 1], dtype=np.float32))
             self.eng.run(self._plan_noclip, sync=False)
         return float(self.eng.download(self.b_loss, (1,))[0])
@@ -656,7 +682,7 @@ class CompiledTransformer:
             self.eng.capture(self.plan_step)
         else:
             if self._plan_noclip is None:
-                self._plan_noclip = self._plan_fb_sync + self._opt_ops(0.0)
+                self._plan_noclip = self._gather_ops() + self._plan_fb_sync + self._opt_ops(0.0)
             self.eng.upload(self.b_t, np.array([t - 1], dtype=np.float32))
             self.eng.capture(self._plan_noclip)
         self._captured = True
@@ -709,7 +735,7 @@ class CompiledTransformer:
             self._acc_plans = {}
         if n not in self._acc_plans:
             inv = 1.0 / n
-            first = self.plan_fb + self._acc_flat(SCALE, bufs=dict(a=self.a_grad, c=self.a_gacc), alpha=inv)
+            first = self._gather_ops() + self.plan_fb + self._acc_flat(SCALE, bufs=dict(a=self.a_grad, c=self.a_gacc), alpha=inv)
             nxt = self.plan_fb + self._acc_flat(SCALE, bufs=dict(a=self.a_grad, c=self.a_grad), alpha=inv) \
                 + self._acc_flat(ADD, bufs=dict(a=self.a_gacc, b=self.a_grad, c=self.a_gacc))
             last = self._acc_flat(COPY, bufs=dict(a=self.a_gacc, c=self.a_grad)) + self.plan_ar \
@@ -727,8 +753,17 @@ class CompiledTransformer:
     def forward_backward(self, tokens: np.ndarray, targets: np.ndarray) -> float:
         """Forward + backward only (no reduction, no update); for gradient checks."""
         self._feed(tokens, targets)
-        self.eng.run(self.plan_fb, sync=False)
+        if self._w_events and not hasattr(self, "_plan_fb_gather"):
+            self._plan_fb_gather = self._gather_ops() + self.plan_fb + [op(JOIN)]
+        self.eng.run(self._plan_fb_gather if self._w_events else self.plan_fb, sync=False)
         return float(self.eng.download(self.b_loss, (1,))[0])
+
+    def gather_weights(self) -> None:
+        """ZeRO-1: bring every rank's bf16 compute copy up to date with the owners' last update now.  A step does
+        this by itself at its start (overlapped with its forward); call it before reading the compute weights of
+        tensors this rank does not own outside a step.  Collective: every rank calls it.  No-op otherwise."""
+        if self._w_events:
+            self.eng.run(self._gather_ops() + [op(JOIN)], sync=True)
 
     def grad_norm(self) -> float:
         """Global gradient norm seen by the last optimizer step (before clipping)."""

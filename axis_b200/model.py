@@ -79,3 +79,46 @@ class Transformer:
         self.lora_a = True               # marks the container as adapter-carrying
         self.scaling = float(alpha) / rank
         return self
+
+
+class LazyNormal:
+    """A weight that exists only as (shape, seed): drawn from N(0, std) (ones for 1-D tensors) at the moment it is
+    uploaded, so a model too large to hold on the host in fp32 — every rank of a multi-GPU job builds its own —
+    costs one tensor of host memory at a time.  `CompiledTransformer` accepts it wherever it accepts an array
+    (the `shape` / `load_into` protocol of pretrained.HfTensor)."""
+
+    def __init__(self, shape, seed, std: float = 0.02):
+        self.shape = tuple(int(v) for v in shape)
+        self.seed, self.std = seed, std
+
+    def to_f32(self) -> np.ndarray:
+        if len(self.shape) == 1:
+            return np.ones(self.shape, dtype=np.float32)
+        rng = np.random.default_rng(self.seed)
+        return rng.standard_normal(self.shape, dtype=np.float32) * np.float32(self.std)
+
+    def load_into(self, eng, dst: int, fp32_out: bool, stage: int) -> None:
+        from axis_b200.engine import f32_to_bf16_bits
+        a = self.to_f32()
+        if fp32_out:
+            eng.upload(dst, a.reshape(-1))
+        else:
+            eng.upload_raw(dst, f32_to_bf16_bits(a))
+        eng.sync()                       # the host array is dropped on return
+
+
+def lazy_weights(cfg: dict, seed: int = 42, std: float = 0.02) -> Dict[str, LazyNormal]:
+    """{name: LazyNormal} for a Llama-class decoder configuration (names and shapes as `Transformer`)."""
+    V, D, L, H = cfg["vocab_size"], cfg["dim"], cfg["n_layers"], cfg["n_heads"]
+    KV = cfg.get("n_kv_heads") or H
+    MLP, dh = cfg["mlp_hidden"], D // H
+    shapes = {"embed.weight": (V, D)}
+    for i in range(L):
+        p = f"blocks.{i}."
+        shapes.update({p + "attn_norm.weight": (D,), p + "attn.q_proj.weight": (D, H * dh), p + "attn.k_proj.weight": (D, KV * dh),
+                       p + "attn.v_proj.weight": (D, KV * dh), p + "attn.o_proj.weight": (H * dh, D), p + "mlp_norm.weight": (D,),
+                       p + "mlp.gate_proj.weight": (D, MLP), p + "mlp.up_proj.weight": (D, MLP), p + "mlp.down_proj.weight": (MLP, D)})
+    shapes["norm.weight"] = (D,)
+    if not cfg.get("tie_embeddings", True):
+        shapes["lm_head.weight"] = (D, V)
+    return {nm: LazyNormal(sh, [seed, idx], std) for idx, (nm, sh) in enumerate(shapes.items())}

@@ -332,14 +332,22 @@ def main():
         dist.init_process_group("gloo", init_method=f"tcp://{os.environ.get('MASTER_ADDR', '127.0.0.1')}:"
                                 f"{os.environ.get('MASTER_PORT', '29500')}", rank=RANK, world_size=WORLD)
 
-    from axis_b200.compile import compile_model
-    model = make_weights(c["cfg"], seed=42)
-    if c["lora"]:
-        model.apply_lora(rank=c["lora"], alpha=2.0 * c["lora"])
-    ct = compile_model(model, batch=c["B"], seq=c["T"], dtype=c["dtype"], lr=c["lr"], max_grad_norm=1.0,
-                       grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD,
-                       recompute_blocks=args.recompute, overlap_dw=not args.no_overlap_dw)
-    del model
+    from axis_b200.compile import CompiledTransformer, compile_model
+    if c["cfg"]["dim"] >= 4096 and not c["lora"]:
+        # 7B-class: weights are drawn tensor by tensor while they are uploaded (every rank would otherwise hold
+        # 26 GB of fp32 host arrays at once)
+        from axis_b200.model import lazy_weights
+        ct = CompiledTransformer(None, c["cfg"], lazy_weights(c["cfg"], seed=42), c["B"], c["T"], dtype=c["dtype"], lr=c["lr"],
+                                 max_grad_norm=1.0, grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD,
+                                 recompute_blocks=args.recompute, overlap_dw=not args.no_overlap_dw)
+    else:
+        model = make_weights(c["cfg"], seed=42)
+        if c["lora"]:
+            model.apply_lora(rank=c["lora"], alpha=2.0 * c["lora"])
+        ct = compile_model(model, batch=c["B"], seq=c["T"], dtype=c["dtype"], lr=c["lr"], max_grad_norm=1.0,
+                           grad_sync=WORLD > 1, zero_stage=zero, rank=RANK, world=WORLD,
+                           recompute_blocks=args.recompute, overlap_dw=not args.no_overlap_dw)
+        del model
     eng = ct.eng
     if WORLD > 1:
         import torch

@@ -45,6 +45,7 @@ def _worker(rank, world, port, zero, dtype, recompute, out, resume_at=0):
                                      max_grad_norm=1.0, bucket_layers=2, recompute_blocks=recompute)
             ct.load_state_dict(st)
         losses.append(ct.step(*_data(rank, s)))
+    ct.gather_weights()          # ZeRO-1 gathers the updated compute weights at the start of the NEXT step
     res = {"losses": losses, "owned": ct.owned, "norm": ct.grad_norm(),
            "w": ct.get_weights(), "g": ct.grads() if not zero else {},
            "mirror": ct.eng.bufs[ct.a_mirror].copy() if dtype == "bf16" else None,
@@ -158,3 +159,17 @@ def test_zero1_resume_continues_the_run_bit_for_bit(runs):
         for nm, w in z[r]["w"].items():
             assert np.array_equal(w, rs[r]["w"][nm]), nm
         assert np.array_equal(z[r]["mirror"], rs[r]["mirror"])
+
+
+def test_zero1_gathers_the_weights_at_the_start_of_the_step(runs):
+    """ZeRO-1: the owners' bf16 segments are broadcast before the first forward kernel of a step (one event per
+    bucket, waited for just before the bucket's first use) and nothing follows the optimizer on the main chain."""
+    from axis_b200 import engine as E
+    tr = runs["z16"][0]["trace"]
+    end = tr.index(E.ADAMW_FLAT)
+    step0 = tr[:end + 1]
+    assert step0.index(E.BROADCAST) < step0.index(E.EMBED_I32)
+    first_gemm = min(step0.index(k) for k in (E.GEMM_GROUP, E.GEMM_SB) if k in step0)
+    assert step0[:first_gemm].count(E.BROADCAST) == step0.count(E.BROADCAST) > 0
+    nxt = tr[end + 1:]
+    assert nxt[0] == E.FORK and E.BROADCAST in nxt[:8]          # the next step opens with the gather, not this one's tail

@@ -59,6 +59,7 @@ def _worker(rank, world, zero, dtype, graph, q_uid, q_out):
         for s in range(STEPS):
             x, y = _data(rank, s)
             losses.append(ct.replay_step(x, y) if graph else ct.step(x, y))
+        ct.gather_weights()      # ZeRO-1 gathers the updated compute weights at the start of the next step
         mirror = ct.eng.download_raw(ct.a_mirror, ct._P_total, np.uint16) if dtype == "bf16" else None
         q_out.put((rank, dict(losses=losses, owned=ct.owned, norm=ct.grad_norm(), w=ct.get_weights(),
                               g=ct.grads() if not zero else {}, mirror=mirror, status=ct.eng.device_status())))
