@@ -41,6 +41,29 @@ struct FwdSmem {
     static constexpr int Q = 0, K0 = 16384, V0 = K0 + 2 * 16384, BARS = V0 + 2 * 16384, TOTAL = BARS + 128 + 1024;
 };
 
+// Issue forms for a converged warp: every lane executes the surrounding code (so addresses and descriptors stay
+// warp-uniform and cheap to form) and the elected lane issues.  Measured on B200: a 128 x 64 x 16 MMA with A in
+// TMEM issues every 32.6 cycles this way (its 32 cycles of math) against 45-50 from a lone thread in a divergent branch.
+__device__ __forceinline__ void mma_ts_e(uint32_t d, uint32_t a, uint64_t bd, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a), "l"(bd), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma_ss_e(uint32_t d, uint64_t ad, uint64_t bd, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(ad), "l"(bd), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void commit_e(uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
+}
+
+// Forward CTA: 128 queries of one head; four softmax warps (a thread owns a query row) and one control warp that
+// loads by TMA and issues the MMAs.  TMEM (256 columns, two CTAs per SM): S 0..127, P 128..191 (packed bf16),
+// O 192..255.  P has columns of its own, so S(j+1) = Q K(j+1)^T is issued as soon as the softmax threads have read
+// S(j) into registers and runs under the exponentials of tile j; K and V tiles travel on separate barriers (a K slot
+// is free once its S MMA has run, a V slot once its P V MMA has).
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse,
@@ -49,8 +72,10 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sb = smem_u32(smem);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FwdSmem::BARS);
-    const uint32_t b_q = smem_u32(bars), b_kvf = b_q + 8, b_kve = b_kvf + 16, b_s = b_kve + 16, b_p = b_s + 8, b_o = b_p + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    // q_full, k_full[2], v_full[2], s_full, s_free, p_full, o_done
+    const uint32_t b_q = smem_u32(bars), b_kf = b_q + 8, b_vf = b_kf + 16, b_s = b_vf + 16, b_sfree = b_s + 8, b_p = b_sfree + 8,
+                   b_o = b_p + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -63,8 +88,8 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
     if (threadIdx.x == 0) {
         mbar_init(b_q, 1);
-        for (int s = 0; s < 2; s++) { mbar_init(b_kvf + 8 * s, 1); mbar_init(b_kve + 8 * s, 1); }
-        mbar_init(b_s, 1); mbar_init(b_p, 128); mbar_init(b_o, 1);
+        for (int s = 0; s < 2; s++) { mbar_init(b_kf + 8 * s, 1); mbar_init(b_vf + 8 * s, 1); }
+        mbar_init(b_s, 1); mbar_init(b_sfree, 128); mbar_init(b_p, 128); mbar_init(b_o, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -73,64 +98,85 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_S = tmem, t_O = tmem + 128;
+    const uint32_t t_S = tmem, t_P = tmem + 128, t_O = tmem + 192;
 
     if (warp == 4) {
+        // ── control warp (converged; one elected lane issues MMAs, lane 0 issues the TMA loads) ──
+        bool ok = true;
+        constexpr uint32_t id_s = tc_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t id_pv = tc_idesc_bf16(128, 64, 0, 1);
+        const uint32_t loQ = desc_lo(sb + FwdSmem::Q, 16), loK = desc_lo(sb + FwdSmem::K0, 16), loV = desc_lo(sb + FwdSmem::V0, 16384);
+        auto load_k = [&](int j) {
+            if (lane == 0) {
+                mbar_expect_tx(b_kf + 8 * (j & 1), 16384);
+                tma_load_4d(sb + FwdSmem::K0 + (j & 1) * 16384, &tmK, b_kf + 8 * (j & 1), 0, g, j * AT, b);
+            }
+        };
+        auto load_v = [&](int j) {
+            if (lane == 0) {
+                mbar_expect_tx(b_vf + 8 * (j & 1), 16384);
+                tma_load_4d(sb + FwdSmem::V0 + (j & 1) * 16384, &tmV, b_vf + 8 * (j & 1), 0, g, j * AT, b);
+            }
+        };
+        auto issue_s = [&](int j) {
+#pragma unroll
+            for (int kk = 0; kk < ADH / 16; kk++)
+                mma_ss_e(t_S, desc_of(loQ + kk * 2), desc_of(loK + (j & 1) * 1024 + kk * 2), id_s, kk != 0);
+            commit_e(b_s);
+        };
         if (lane == 0) {
-            bool ok = true;
-            constexpr uint32_t id_s = tc_idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t id_pv = tc_idesc_bf16(128, 64, 0, 1);
-            const uint32_t loQ = desc_lo(sb + FwdSmem::Q, 16), loK = desc_lo(sb + FwdSmem::K0, 16), loV = desc_lo(sb + FwdSmem::V0, 16384);
             tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
             mbar_expect_tx(b_q, 16384);
             tma_load_4d(sb + FwdSmem::Q, &tmQ, b_q, 0, h, qt * AT, b);
-            mbar_expect_tx(b_kvf, 32768);
-            tma_load_4d(sb + FwdSmem::K0, &tmK, b_kvf, 0, g, 0, b);
-            tma_load_4d(sb + FwdSmem::V0, &tmV, b_kvf, 0, g, 0, b);
-            if (!mbar_wait(b_q, 0)) ok = false;
-            for (int j = 0; j < nkt && ok; j++) {
-                const int s = j & 1;
-                if (!mbar_wait(b_kvf + 8 * s, (j >> 1) & 1)) { ok = false; break; }
-                // S(j) overwrites the columns that P V(j-1) reads P from: MMAs on different accumulators are not
-                // ordered against each other, so wait for that MMA's completion instead of relying on issue order
-                if (j >= 1 && !mbar_wait(b_o, (j - 1) & 1)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < ADH / 16; kk++)
-                    tc_mma_ss(t_S, desc_of(loQ + kk * 2), desc_of(loK + s * 1024 + kk * 2), id_s, kk != 0);
-                tc_commit(b_s);
-                if (j + 1 < nkt) {      // next K/V tile into the other stage, once PV(j-1) has released it
-                    const int s2 = s ^ 1;
-                    if (j >= 1 && !mbar_wait(b_kve + 8 * s2, ((j - 1) >> 1) & 1)) { ok = false; break; }
-                    mbar_expect_tx(b_kvf + 8 * s2, 32768);
-                    tma_load_4d(sb + FwdSmem::K0 + s2 * 16384, &tmK, b_kvf + 8 * s2, 0, g, (j + 1) * AT, b);
-                    tma_load_4d(sb + FwdSmem::V0 + s2 * 16384, &tmV, b_kvf + 8 * s2, 0, g, (j + 1) * AT, b);
-                }
-                if (!mbar_wait(b_p, j & 1)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < AT / 16; kk++)
-                    tc_mma_ts(t_O, t_S + kk * 8, desc_of(loV + s * 1024 + kk * 128), id_pv, (j | kk) != 0);
-                tc_commit(b_kve + 8 * s);
-                tc_commit(b_o);
-            }
-            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_FWD | 1); }
         }
+        load_k(0); load_v(0);
+        if (nkt > 1) { load_k(1); load_v(1); }
+        __syncwarp();
+        if (!mbar_wait_park(b_q, 0) || !mbar_wait_park(b_kf, 0)) ok = false;
+        if (ok) { tc_fence_after(); issue_s(0); }
+        for (int j = 0; j < nkt && ok; j++) {
+            const int s = j & 1;
+            if (j + 1 < nkt) {
+                // S(j+1): its K tile has landed and every softmax thread holds S(j) in registers
+                if (!mbar_wait_park(b_kf + 8 * (s ^ 1), ((j + 1) >> 1) & 1) || !mbar_wait_park(b_sfree, j & 1) || *abort_flag) { ok = false; break; }
+                tc_fence_after();
+                issue_s(j + 1);
+                // K slot s was read by S(j), complete long since (its result has been read): K(j+2) may overwrite it
+                if (j + 2 < nkt) { load_k(j + 2); __syncwarp(); }
+            }
+            // O += P(j) V(j)
+            if (!mbar_wait_park(b_vf + 8 * s, (j >> 1) & 1) || !mbar_wait_park(b_p, j & 1) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < AT / 16; kk++)
+                mma_ts_e(t_O, t_P + kk * 8, desc_of(loV + s * 1024 + kk * 128), id_pv, (j | kk) != 0);
+            commit_e(b_o);
+            if (j + 2 < nkt) {                          // V slot s is free once P V(j) has run
+                if (!mbar_wait_park(b_o, j & 1)) { ok = false; break; }
+                load_v(j + 2);
+                __syncwarp();
+            }
+        }
+        __syncwarp();
+        if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_FWD | 1); }
     } else {
         const int r = threadIdx.x;                         // query row within the tile == TMEM lane
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         const float c = scale * LOG2E;
+        const float2 c2 = make_float2(c, c);
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < nkt && ok; j++) {
-            if (!mbar_wait(b_s, j & 1) || *abort_flag) { ok = false; break; }
+            if (!mbar_wait_park(b_s, j & 1) || *abort_flag) { ok = false; break; }
             tc_fence_after();
             const bool diag = j == qt;
-            // the whole S row (128 scores) stays in registers between the max pass and the exp pass
+            // the whole S row (128 scores) goes into registers; the buffer is then free for S(j+1)
             uint32_t sv[128];
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) tmem_ld32(t_S + lane_base + ch * 32, sv + ch * 32);
             tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(b_sfree);
             // raw maximum first (c > 0), one multiply at the end; the mask only on the diagonal tile
             if (diag) {
 #pragma unroll
@@ -156,7 +202,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const bool need = mx > m_used + 8.f;
                 if (__any_sync(0xffffffffu, need)) {
                     // rescale this warp's rows of O; PV(j-1) must have landed first
-                    if (!mbar_wait(b_o, (j - 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait_park(b_o, (j - 1) & 1)) { ok = false; break; }
                     tc_fence_after();
                     const float m_new = fmaxf(m_used, mx);
                     const float f = fast_exp2(m_used - m_new);
@@ -175,31 +221,34 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     tmem_st_wait();
                 }
             }
+            // P(j-1) is read by P V(j-1): it must have run before the columns are rewritten
+            if (j >= 1 && !mbar_wait_park(b_o, (j - 1) & 1)) { ok = false; break; }
             {
-                float l0 = 0.f, l1 = 0.f;
+                const float2 nm2 = make_float2(-m_used, -m_used);
+                float2 l2 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int ch = 0; ch < 4; ch++) {
                     uint32_t w[16];
 #pragma unroll
                     for (int q = 0; q < 32; q += 4) {
-                        const float p0 = fast_exp2(__uint_as_float(sv[ch * 32 + q]) * c - m_used);
-                        const float p1 = fast_exp2(__uint_as_float(sv[ch * 32 + q + 1]) * c - m_used);
-                        const float p2 = fast_exp2(__uint_as_float(sv[ch * 32 + q + 2]) * c - m_used);
-                        const float p3 = fast_exp2(__uint_as_float(sv[ch * 32 + q + 3]) * c - m_used);
-                        l0 += p0 + p1;
-                        l1 += p2 + p3;
-                        w[q >> 1] = pack_bf16(p0, p1);
-                        w[(q >> 1) + 1] = pack_bf16(p2, p3);
+                        // packed fp32x2 arithmetic: one instruction per pair of scores
+                        const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(sv[ch * 32 + q]), __uint_as_float(sv[ch * 32 + q + 1])), c2, nm2);
+                        const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(sv[ch * 32 + q + 2]), __uint_as_float(sv[ch * 32 + q + 3])), c2, nm2);
+                        const float2 p01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+                        const float2 p23 = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+                        l2 = __fadd2_rn(l2, __fadd2_rn(p01, p23));
+                        w[q >> 1] = pack_bf16(p01.x, p01.y);
+                        w[(q >> 1) + 1] = pack_bf16(p23.x, p23.y);
                     }
-                    tmem_st16(t_S + lane_base + ch * 16, w);   // P replaces S (all of it is in registers by now)
+                    tmem_st16(t_P + lane_base + ch * 16, w);
                 }
-                l += l0 + l1;
+                l += l2.x + l2.y;
             }
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(b_p);
         }
-        if (ok && mbar_wait(b_o, (nkt - 1) & 1)) {
+        if (ok && mbar_wait_park(b_o, (nkt - 1) & 1)) {
             tc_fence_after();
             const int t = qt * AT + r;
             const float il = 1.f / l;
@@ -296,24 +345,6 @@ static_assert(BwdSmem::DO0 % 1024 == 0 && BwdSmem::DS0 % 1024 == 0 && BwdSmem::D
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
-}
-
-// Issue forms for a converged warp: every lane executes the surrounding code (so addresses and descriptors stay
-// warp-uniform and cheap to form) and the elected lane issues.  Measured on B200: a 128 x 64 x 16 MMA with A in
-// TMEM issues every 32.6 cycles this way (its 32 cycles of math) against 45-50 from a lone thread in a divergent branch.
-__device__ __forceinline__ void mma_ts_e(uint32_t d, uint32_t a, uint64_t bd, uint32_t id, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(d), "r"(a), "l"(bd), "r"(id), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void mma_ss_e(uint32_t d, uint64_t ad, uint64_t bd, uint32_t id, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d), "l"(ad), "l"(bd), "r"(id), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void commit_e(uint32_t bar) {
-    asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
-                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
 }
 
 #ifdef AXENG_PROF

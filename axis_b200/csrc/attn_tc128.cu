@@ -30,6 +30,23 @@ struct Fwd128Smem {
     static constexpr int Q = 0, K = 32768, V = 65536, BARS = 98304, TOTAL = BARS + 128 + 1024;
 };
 
+// Issue forms for a converged warp (every lane runs the surrounding code, the elected lane issues): a lone thread in a
+// divergent branch needs 45-50 cycles per MMA issue, this form 33 (measured on B200).
+__device__ __forceinline__ void mma128_ts_e(uint32_t d, uint32_t a, uint64_t bd, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a), "l"(bd), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma128_ss_e(uint32_t d, uint64_t ad, uint64_t bd, uint32_t id, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p, q;\n\telect.sync _|q, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(ad), "l"(bd), "r"(id), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void commit128_e(uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
+}
+
 __global__ void __launch_bounds__(ATT_THREADS, 2)
 k_attn_fwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, bf16* __restrict__ o, float* __restrict__ lse,
@@ -65,18 +82,21 @@ k_attn_fwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t t_S = tmem, t_O = tmem + 128;
 
     if (warp == 4) {
-        if (lane == 0) {
+        {   // the whole warp runs the loop converged; lane 0 issues the TMA loads, one elected lane the MMAs
             bool ok = true;
             constexpr uint32_t id_s = tc_idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t id_pv = tc_idesc_bf16(128, 128, 0, 1);
             // K-major tiles: two 64-wide blocks 16 KB apart, 2 units (32 B) per k-step inside a block;
             // V as the MN-major B operand: head-dim blocks 16 KB apart (LBO), 128 units (2 KB) per 16 keys
             const uint32_t loQ = desc_lo(sb + Fwd128Smem::Q, 16), loK = desc_lo(sb + Fwd128Smem::K, 16), loV = desc_lo(sb + Fwd128Smem::V, 16384);
-            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+            if (lane == 0) { tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
             auto load_tile = [&](uint32_t dst, const CUtensorMap* m, uint32_t bar, int heads_idx, int row0) {
-                mbar_expect_tx(bar, 32768);
-                tma_load_4d(dst, m, bar, 0, heads_idx, row0, b);
-                tma_load_4d(dst + 16384, m, bar, 64, heads_idx, row0, b);
+                if (lane == 0) {
+                    mbar_expect_tx(bar, 32768);
+                    tma_load_4d(dst, m, bar, 0, heads_idx, row0, b);
+                    tma_load_4d(dst + 16384, m, bar, 64, heads_idx, row0, b);
+                }
+                __syncwarp();
             };
             load_tile(sb + Fwd128Smem::Q, &tmQ, b_q, h, qt * AT);
             load_tile(sb + Fwd128Smem::K, &tmK, b_kf, g, 0);
@@ -88,8 +108,8 @@ k_attn_fwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < DH2 / 16; kk++)
-                    tc_mma_ss(t_S, desc_of(loQ + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loK + (kk >> 2) * 1024 + (kk & 3) * 2), id_s, kk != 0);
-                tc_commit(b_s);
+                    mma128_ss_e(t_S, desc_of(loQ + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loK + (kk >> 2) * 1024 + (kk & 3) * 2), id_s, kk != 0);
+                commit128_e(b_s);
                 if (j + 1 < nkt) {          // K is free once S(j) has run
                     if (!mbar_wait(b_s, ph)) { ok = false; break; }
                     load_tile(sb + Fwd128Smem::K, &tmK, b_kf, g, (j + 1) * AT);
@@ -98,15 +118,16 @@ k_attn_fwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < AT / 16; kk++)
-                    tc_mma_ts(t_O, t_S + kk * 8, desc_of(loV + kk * 128), id_pv, (j | kk) != 0);
-                tc_commit(b_ve);
-                tc_commit(b_o);
+                    mma128_ts_e(t_O, t_S + kk * 8, desc_of(loV + kk * 128), id_pv, (j | kk) != 0);
+                commit128_e(b_ve);
+                commit128_e(b_o);
                 if (j + 1 < nkt) {          // V is free once P V(j) has run
                     if (!mbar_wait(b_ve, ph)) { ok = false; break; }
                     load_tile(sb + Fwd128Smem::V, &tmV, b_vf, g, (j + 1) * AT);
                 }
             }
-            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_FWD128 | 1); }
+            __syncwarp();
+            if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_FWD128 | 1); }
         }
     } else {
         const int r = threadIdx.x;                         // query row within the tile == TMEM lane
@@ -301,7 +322,7 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t t_S = tmem, t_dP = tmem + 64, t_dV = tmem + 128, t_dK = tmem + 256, t_dQ = tmem + 384;
 
     if (warp == 8) {
-        if (lane == 0) {
+        {   // the whole warp runs the loop converged; lane 0 issues the TMA loads, one elected lane the MMAs
             bool ok = true;
             constexpr uint32_t id_s = tc_idesc_bf16(128, QS, 0, 0);        // S^T = K Q^T, dP^T = V dO^T (64 queries)
             constexpr uint32_t id_acc = tc_idesc_bf16(128, DH2, 0, 1);     // dV/dK: A in TMEM, B N-major (128 wide)
@@ -310,13 +331,16 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint32_t loK_m = desc_lo(sb + Bwd128Smem::K, 16384), loDS = desc_lo(sb + Bwd128Smem::DS, 16);
             const uint32_t loQ_k = desc_lo(sb + Bwd128Smem::Q0, 16), loQ_n = desc_lo(sb + Bwd128Smem::Q0, 8192);
             const uint32_t loO_k = desc_lo(sb + Bwd128Smem::DO0, 16), loO_n = desc_lo(sb + Bwd128Smem::DO0, 8192);
-            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
-            mbar_expect_tx(b_kv, 65536);
-            tma_load_4d(sb + Bwd128Smem::K, &tmK, b_kv, 0, g, j * AT, b);
-            tma_load_4d(sb + Bwd128Smem::K + 16384, &tmK, b_kv, 64, g, j * AT, b);
-            tma_load_4d(sb + Bwd128Smem::V, &tmV, b_kv, 0, g, j * AT, b);
-            tma_load_4d(sb + Bwd128Smem::V + 16384, &tmV, b_kv, 64, g, j * AT, b);
+            if (lane == 0) {
+                tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+                mbar_expect_tx(b_kv, 65536);
+                tma_load_4d(sb + Bwd128Smem::K, &tmK, b_kv, 0, g, j * AT, b);
+                tma_load_4d(sb + Bwd128Smem::K + 16384, &tmK, b_kv, 64, g, j * AT, b);
+                tma_load_4d(sb + Bwd128Smem::V, &tmV, b_kv, 0, g, j * AT, b);
+                tma_load_4d(sb + Bwd128Smem::V + 16384, &tmV, b_kv, 64, g, j * AT, b);
+            }
             auto load_q = [&](int it) {
+                if (lane != 0) return;
                 const int s = it & 1, hh = it / per_head, u = 2 * j + it % per_head, h = g * rep + hh;
                 mbar_expect_tx(b_qf + 8 * s, 32768);
                 tma_load_4d(sb + Bwd128Smem::Q0 + s * 16384, &tmQ, b_qf + 8 * s, 0, h, u * QS, b);
@@ -325,6 +349,7 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tma_load_4d(sb + Bwd128Smem::DO0 + s * 16384 + 8192, &tmdO, b_qf + 8 * s, 64, h, u * QS, b);
             };
             load_q(0);
+            __syncwarp();
             if (!mbar_wait(b_kv, 0)) ok = false;
             for (int it = 0; it < n_it && ok; it++) {
                 const int s = it & 1;
@@ -332,6 +357,7 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (it + 1 < n_it) {        // prefetch the next Q/dO sub-tile once its stage is free
                     if (it >= 1 && !mbar_wait(b_qe + 8 * (s ^ 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
                     load_q(it + 1);
+                    __syncwarp();
                 }
                 if (!mbar_wait(b_qf + 8 * s, (it >> 1) & 1)) { ok = false; break; }
                 // S^T/dP^T(it) overwrite the columns whose P^T/dS^T the dV/dK MMAs of it-1 read as A operands: MMAs on
@@ -341,27 +367,28 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 // S^T (128 keys x 64 queries) = K Q^T and dP^T = V dO^T over the 128-wide head: 8 k-steps each
 #pragma unroll
                 for (int kk = 0; kk < DH2 / 16; kk++)
-                    tc_mma_ss(t_S, desc_of(loK_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loQ_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
+                    mma128_ss_e(t_S, desc_of(loK_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loQ_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
 #pragma unroll
                 for (int kk = 0; kk < DH2 / 16; kk++)
-                    tc_mma_ss(t_dP, desc_of(loV_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loO_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
-                tc_commit(b_sdp);
+                    mma128_ss_e(t_dP, desc_of(loV_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loO_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
+                commit128_e(b_sdp);
                 if (!mbar_wait(b_pds, it & 1)) { ok = false; break; }
                 tc_fence_after();
                 // P^T / dS^T in TMEM: queries 0..31 packed in columns 0..15, queries 32..63 in columns 32..47
 #pragma unroll
                 for (int kk = 0; kk < QS / 16; kk++)       // dV += P^T dO   (k = queries; B = dO sub-tile, head-dim blocks 8 KB apart)
-                    tc_mma_ts(t_dV, t_S + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loO_n + so + kk * 128), id_acc, (it | kk) != 0);
+                    mma128_ts_e(t_dV, t_S + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loO_n + so + kk * 128), id_acc, (it | kk) != 0);
 #pragma unroll
                 for (int kk = 0; kk < QS / 16; kk++)       // dK += dS^T Q
-                    tc_mma_ts(t_dK, t_dP + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loQ_n + so + kk * 128), id_acc, (it | kk) != 0);
-                tc_commit(b_qe + 8 * s);                   // Q/dO stage and the P^T/dS^T columns are free once these have run
+                    mma128_ts_e(t_dK, t_dP + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loQ_n + so + kk * 128), id_acc, (it | kk) != 0);
+                commit128_e(b_qe + 8 * s);                   // Q/dO stage and the P^T/dS^T columns are free once these have run
 #pragma unroll
                 for (int kk = 0; kk < AT / 16; kk++)       // dQ^T = K^T dS^T   (k = keys), double-buffered
-                    tc_mma_ss(t_dQ + (it & 1) * 64, desc_of(loK_m + kk * 128), desc_of(loDS + kk * 128), id_dq, kk != 0);
-                tc_commit(b_dq + 8 * (it & 1));
+                    mma128_ss_e(t_dQ + (it & 1) * 64, desc_of(loK_m + kk * 128), desc_of(loDS + kk * 128), id_dq, kk != 0);
+                commit128_e(b_dq + 8 * (it & 1));
             }
-            if (!ok) { *abort_flag = 1; atomicExch(status, STAT_BWD128 | 1); }
+            __syncwarp();
+            if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_BWD128 | 1); }
         }
     } else {
         const int r = threadIdx.x & 127;                    // key row of S^T / head-dim row of dQ^T == TMEM lane
