@@ -72,7 +72,8 @@ METRIC = "train tok/s (fwd+bwd+AdamW)"
 PUBLISHED_TOK_S = {"c3": 10279.0}
 # DRAM bytes per GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, mean over the GEMM launches of one step)
 # from an ncu capture of `bench.py --layers 2` of the same workload, and where its summary is committed
-GEMM_TRAFFIC = {}
+GEMM_TRAFFIC = {"c3": (148.1e6, "ncu dram__bytes_read.sum + dram__bytes_write.sum of the GEMM launches of 2- and 3-layer variants, "
+                               "scaled to 48 layers: profiles/gemm_step_dram_traffic_1b.md")}
 
 
 def step_flops(c) -> float:

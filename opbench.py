@@ -209,6 +209,18 @@ def run_ce(b, N, V, dt):
     return b.report(f"cross-entropy fwd+bwd in place {N}x{V} dt={dt}", ms, bytes_=2 * N * V * es)
 
 
+def run_embed_bwd(b, N, D, V, dt):
+    """Deterministic embedding gradient: N token rows of width D summed into the fp32 table rows of their ids."""
+    es = 2 if dt else 4
+    g = b.buf(N * D, dt)
+    ids = b.eng.alloc(N)
+    b.eng.upload_tokens(ids, b.rng.integers(0, V, N), V)
+    table = b.eng.alloc(V * D)
+    ms = b.time([op(E.EMBED_BWD_DET, a=g, b=ids, c=table, m=N, n=D, dt=dt)])
+    # read the gradient rows once, read-modify-write one table row per token at most
+    return b.report(f"embed_bwd_det {N} tokens x {D} into {V} rows dt={dt}", ms, bytes_=N * D * es + 2 * min(N, V) * D * 4)
+
+
 def run_adamw(b, n):
     n = n // 1024 * 1024
     p, g = b.buf(n, 0, scale=0.02), b.buf(n, 0, scale=1e-3)
@@ -509,6 +521,8 @@ def main():
         run_ce(b, a.rows, a.V, a.dt)
     elif w == "adamw":
         run_adamw(b, a.count)
+    elif w == "embed_bwd":
+        run_embed_bwd(b, a.rows, a.dim, a.V, a.dt)
     elif w == "all":
         N, D, MLP, V = 8192, 1536, 4096, 32000
         for (m, n, k, tb, dt) in [(N, D, D, 0, 1), (N, 512, D, 0, 1), (N, MLP, D, 0, 1), (N, D, MLP, 0, 1), (N, V, D, 1, 1),
@@ -520,6 +534,7 @@ def main():
         run_rows(b, "rmsnorm", N, D, 1); run_rows(b, "rmsnorm_bwd", N, D, 1)
         run_elem(b, "rope", 0, 1); run_elem(b, "silu", N * MLP, 1); run_elem(b, "silu_bwd", N * MLP, 1)
         run_ce(b, N, V, 1)
+        run_embed_bwd(b, N, D, V, 1)
         run_adamw(b, 256 * 1024 * 1024)
     else:
         sys.exit(f"unknown op {w}")
