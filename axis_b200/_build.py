@@ -21,7 +21,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib_prof" if os.environ.get("AXENG_BUILD_PROF") else "_lib")
 LIB = os.path.join(LIBDIR, "libaxeng.so")
 SOURCES = ["axeng.cu", "elementwise.cu", "norm.cu", "loss.cu", "optim.cu", "gemm_simt.cu",
-           "gemm_tc.cu", "gemm_tc2.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc128.cu"]
+           "gemm_tc.cu", "gemm_tc2.cu", "attn_simt.cu", "attn_tc.cu", "attn_tc128.cu", "lora.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 if os.environ.get("AXENG_BUILD_PROF"):      # instrumented build: in-kernel cycle stamps of the GEMM / attention kernels

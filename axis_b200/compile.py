@@ -33,7 +33,7 @@ import numpy as np
 
 from axis_b200.engine import (
     ADAMW_FLAT, ADD, ALLGATHER_F32, ATTN_BWD, ATTN_FWD, BROADCAST, CAST, CE_FUSED, CHUNK, COLSUM_BATCH, COPY, EMBED_BWD_DET,
-    EMBED_I32, FORK, GEMM_EX, GEMM_GROUP, GEMM_SB, GNORM_FLAT, GROUP, JOIN, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
+    EMBED_I32, FORK, GEMM_EX, GEMM_GROUP, GEMM_SB, GEMM_XSEG, GNORM_FLAT, GROUP, JOIN, LORA_GRAD, LORA_PROJ, REDUCE, RMSNORM, RMSNORM_BWD_ACC,
     ROPE_BTHD, SCALE, SILU_BWD, SILU_MUL, STREAM, EVENT, Engine, f32_to_bf16_bits, op)
 
 LIN_ORDER = ("attn.q_proj", "attn.k_proj", "attn.v_proj", "attn.o_proj",
@@ -321,25 +321,57 @@ class CompiledTransformer:
         dk = A(N * KV * DH, isz); dv = A(N * KV * DH, isz)
         bD = A(N * H + (N * H * DH if hf else 0))     # row dots, then the fp32 dQ accumulator of the bf16 path
         if lora:
+            # u = s * x@A of every adapted projection is kept for the backward; t = s * g@B^T lives until the
+            # projection's gradient ops have run (one buffer per projection kind, reused by every layer)
             u_l = {(i, pref): A(N * lora_r, isz) for i in range(L) for pref in lin_geom
                    if pref.split(".")[-1] in lset}
-            t1 = A(N * lora_r, isz)
+            t_l = {pref: A(N * lora_r, isz) for pref in lin_geom if pref.split(".")[-1] in lset}
         G = self.gbuf
 
+        def adapted(pref):
+            return lora and pref.split(".")[-1] in lset
+
+        def lora_proj(xs_, ws_, outs_, fs_, tb):
+            """outs_[g] [N, r] = s * xs_[g] @ W_g (W_g [F, r], tb=0) or @ W_g^T (W_g [r, F], tb=1): the skinny products of up
+            to three adapters as one streaming launch"""
+            pad = lambda v: list(v) + [0] * (3 - len(v))
+            x_, w_, o_, f_ = pad(xs_), pad(ws_), pad(outs_), pad(fs_)
+            same = all(v == x_[0] for v in xs_)
+            return [op(LORA_PROJ, a=x_[0], sa=0 if same else x_[1], sb=0 if same else x_[2], b=w_[0], d=w_[1], sc=w_[2],
+                       c=o_[0], oa=o_[1], ob=o_[2], n=f_[0], k=f_[1], oc=f_[2], m=N, batch=len(xs_), tb=tb,
+                       gamma=float(lora_r), alpha=sc_l, dt=DT)]
+
+        def lora_grads(i, prefs, x, gs_):
+            """dA_p = x^T t_p and dB_p = u_p^T g_p of the adapted projections among prefs (x shared): two ops, each a
+            stream over its wide operands with a fixed summation order"""
+            pp = [(p_, g_) for p_, g_ in zip(prefs, gs_) if adapted(p_)]
+            if not pp:
+                return []
+            pad = lambda v: list(v) + [0] * (3 - len(v))
+            ts, us_ = pad([t_l[p_] for p_, _ in pp]), pad([u_l[(i, p_)] for p_, _ in pp])
+            gg = pad([g_ for _, g_ in pp])
+            offa = pad([self._off[f"blocks.{i}.{p_}.lora_a"] for p_, _ in pp])
+            offb = pad([self._off[f"blocks.{i}.{p_}.lora_b"] for p_, _ in pp])
+            fin = lin_geom[pp[0][0]][0]
+            fo = pad([lin_geom[p_][1] for p_, _ in pp])
+            return [op(LORA_GRAD, a=x, b=ts[0], d=ts[1], sc=ts[2], c=self.a_grad, oa=offa[0], ob=offa[1], oc=offa[2],
+                       n=fin, k=fin, tb=fin, m=N, batch=len(pp), gamma=float(lora_r), dt=DT),
+                    op(LORA_GRAD, a=gg[0], sa=gg[1], sb=gg[2], b=us_[0], d=us_[1], sc=us_[2], c=self.a_grad,
+                       oa=offb[0], ob=offb[1], oc=offb[2], n=fo[0], k=fo[1], tb=fo[2], m=N, batch=len(pp),
+                       gamma=float(lora_r), beta=1.0, dt=DT)]
+
         def lin_f(x, i, pref, y, res=-1):
-            """y = x@W (+ res) (+ s*(x@A)@B, with u = x@A saved)"""
+            """y = x@W (+ res) (+ u@B with u = s * x@A saved: the adapter's term is a K-segment of the same launch)"""
             fin, fout = lin_geom[pref]
             key = f"blocks.{i}.{pref}"
-            if res >= 0:
-                o_ = [op(GEMM_EX, a=x, b=P[key + ".weight"], c=y, d=res, m=N, k=fin, n=fout, batch=1, dt=DT, beta=1.0)]
-            else:
-                o_ = [op(GEMM_SB, a=x, b=P[key + ".weight"], c=y, m=N, k=fin, n=fout, batch=1, dt=DT)]
-            if lora and pref.split(".")[-1] in lset:
+            if adapted(pref):
                 u = u_l[(i, pref)]
-                o_ += [op(GEMM_SB, a=x, b=P[key + ".lora_a"], c=u, m=N, k=fin, n=lora_r, batch=1, dt=DT),
-                       op(GEMM_SB, a=u, b=P[key + ".lora_b"], c=y, m=N, k=lora_r, n=fout, batch=1, dt=DT,
-                          alpha=sc_l, beta=1.0)]
-            return o_
+                return lora_proj([x], [P[key + ".lora_a"]], [u], [fin], 0) + [
+                        op(GEMM_XSEG, a=u, sa=P[key + ".lora_b"], k=lora_r, batch=1, c=(res if res >= 0 else 0), beta=1.0),
+                        op(GEMM_GROUP, a=x, b=P[key + ".weight"], c=y, m=N, k=fin, n=fout, batch=1, oc=2, dt=DT)]
+            if res >= 0:
+                return [op(GEMM_EX, a=x, b=P[key + ".weight"], c=y, d=res, m=N, k=fin, n=fout, batch=1, dt=DT, beta=1.0)]
+            return [op(GEMM_SB, a=x, b=P[key + ".weight"], c=y, m=N, k=fin, n=fout, batch=1, dt=DT)]
 
         # ── weight-gradient GEMMs on a side stream ──
         # The dW GEMMs of a block feed nothing until the optimizer (or the bucket's reduction), so they are
@@ -374,74 +406,85 @@ class CompiledTransformer:
                 del side_reads[b_]
             return [op(EVENT, tb=2, sa=0, oa=e)]
 
-        def lin_b(g, x, i, pref, dx, acc=False, dw=True):
-            """dx (+)= g@W_eff^T ; weight grads: dW (full; dw=False leaves it to a later grouped launch) or dA/dB (LoRA)"""
+        def lin_b(g, x, i, pref, dx, dw=True):
+            """dx = g@W^T (+ t@A^T with t = s * g@B^T); weight grads: dW (dw=False leaves it to a later grouped launch),
+            or the adapter's dA / dB"""
             fin, fout = lin_geom[pref]
             key = f"blocks.{i}.{pref}"
-            o_ = [op(GEMM_SB, a=g, b=P[key + ".weight"], c=dx, m=N, k=fout, n=fin, batch=1, tb=1, dt=DT,
-                     beta=1.0 if acc else 0.0)]
-            if not lora:
-                if dw:
-                    o_ += on_side([op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)], [g])
-            elif pref.split(".")[-1] in lset:
-                u = u_l[(i, pref)]
-                o_ += [op(GEMM_SB, a=g, b=P[key + ".lora_b"], c=t1, m=N, k=fout, n=lora_r, batch=1, tb=1, dt=DT),
-                       op(GEMM_SB, a=t1, b=P[key + ".lora_a"], c=dx, m=N, k=lora_r, n=fin, batch=1, tb=1, dt=DT,
-                          alpha=sc_l, beta=1.0),
-                       op(GEMM_SB, a=x, b=t1, c=G[key + ".lora_a"], m=fin, n=lora_r, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l),
-                       op(GEMM_SB, a=u, b=g, c=G[key + ".lora_b"], m=lora_r, n=fout, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l)]
+            if adapted(pref):
+                t = t_l[pref]
+                return lora_proj([g], [P[key + ".lora_b"]], [t], [fout], 1) + [
+                        op(GEMM_XSEG, a=t, sa=P[key + ".lora_a"], k=lora_r, batch=1),
+                        op(GEMM_GROUP, a=g, b=P[key + ".weight"], c=dx, m=N, k=fout, n=fin, batch=1, oc=2, tb=1, dt=DT)] + \
+                    lora_grads(i, (pref,), x, (g,))
+            o_ = [op(GEMM_SB, a=g, b=P[key + ".weight"], c=dx, m=N, k=fout, n=fin, batch=1, tb=1, dt=DT)]
+            if not lora and dw:
+                o_ += on_side([op(GEMM_SB, a=x, b=g, c=G[key + ".weight"], m=fin, n=fout, k=N, batch=1, tb=2, dt=DTW)], [g])
             return o_
 
-        def lora_f(x, i, pref, y):
-            """y += s*(x@A)@B for an adapted projection, u = x@A saved"""
-            if not (lora and pref.split(".")[-1] in lset):
-                return []
-            fin, fout = lin_geom[pref]
-            key = f"blocks.{i}.{pref}"
-            u = u_l[(i, pref)]
-            return [op(GEMM_SB, a=x, b=P[key + ".lora_a"], c=u, m=N, k=fin, n=lora_r, batch=1, dt=DT),
-                    op(GEMM_SB, a=u, b=P[key + ".lora_b"], c=y, m=N, k=lora_r, n=fout, batch=1, dt=DT,
-                       alpha=sc_l, beta=1.0)]
-
-        def lin_f_group(x, i, prefs, ys_, rope=False):
-            """ys_[g] = x@W_g for projections that share their input: one grouped launch (+ adapters).  rope: the
-            first two outputs (query and key projections) leave the launch with the rotary embedding applied"""
+        def lin_f_group(x, i, prefs, ys_, rope=False, adapters=True):
+            """ys_[g] = x@W_g for projections that share their input: one grouped launch.  With adapters on all of
+            them a second grouped launch computes the u_g = s * x@A_g first and every output takes its u_g@B_g as a
+            K-segment of its own.  rope: the first two outputs (query and key projections) leave the launch with the
+            rotary embedding applied"""
             fin = lin_geom[prefs[0]][0]
             fo = [lin_geom[p][1] for p in prefs] + [0]
             w = [P[f"blocks.{i}.{p}.weight"] for p in prefs] + [0]
             yy = list(ys_) + [0]
-            o_ = [op(GEMM_GROUP, a=x, b=w[0], sa=w[1], sb=w[2], c=yy[0], d=yy[1], sc=yy[2], m=N, k=fin,
-                     n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, dt=DT,
-                     beta=float(b_cos) if rope else 0.0, gamma=float(b_sin) if rope else 0.0)]
-            for p_, y_ in zip(prefs, ys_):
-                o_ += lora_f(x, i, p_, y_)
+            o_ = []
+            if adapters and adapted(prefs[0]):  # the caller passes projections that are all adapted or all plain
+                la = [P[f"blocks.{i}.{p}.lora_a"] for p in prefs] + [0]
+                lb = [P[f"blocks.{i}.{p}.lora_b"] for p in prefs] + [0]
+                uu = [u_l[(i, p)] for p in prefs] + [0]
+                o_ += lora_proj([x] * len(prefs), la[:len(prefs)], uu[:len(prefs)], [fin] * len(prefs), 0)
+                o_ += [op(GEMM_XSEG, a=uu[0], b=uu[1], d=uu[2], sa=lb[0], sb=lb[1], sc=lb[2], k=lora_r, batch=len(prefs))]
+            o_ += [op(GEMM_GROUP, a=x, b=w[0], sa=w[1], sb=w[2], c=yy[0], d=yy[1], sc=yy[2], m=N, k=fin,
+                      n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, dt=DT,
+                      beta=float(b_cos) if rope else 0.0, gamma=float(b_sin) if rope else 0.0)]
             return o_
 
         def lin_b_group(gs_, x, i, prefs, dx):
-            """dx = sum_g gs_[g]@W_g^T in one launch; weight grads of all g in one launch (or adapter grads)"""
+            """dx = sum_g gs_[g]@W_g^T in one launch (with adapters: + sum_g t_g@A_g^T as further K-segments of it, the
+            t_g = s * gs_[g]@B_g^T computed first); weight grads of all g in one launch, or the adapters' dA / dB"""
             fin = lin_geom[prefs[0]][0]
             fo = [lin_geom[p][1] for p in prefs] + [0]
             keys = [f"blocks.{i}.{p}" for p in prefs]
             w = [P[k_ + ".weight"] for k_ in keys] + [0]
             gg = list(gs_) + [0]
-            o_ = [op(GEMM_GROUP, c=dx, a=gg[0], sa=gg[1], sb=gg[2], b=w[0], d=w[1], sc=w[2], m=N, n=fin,
-                     k=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=2, tb=1, dt=DT)]
+            o_ = []
+            ad = [q for q, p in enumerate(prefs) if adapted(p)]
+            if ad:
+                pad = lambda v: list(v) + [0] * (3 - len(v))
+                tt = [t_l[p] if adapted(p) else 0 for p in prefs]
+                lb = [P[k_ + ".lora_b"] if adapted(p) else 0 for p, k_ in zip(prefs, keys)]
+                o_ += lora_proj([gg[q] for q in ad], [lb[q] for q in ad], [tt[q] for q in ad], [fo[q] for q in ad], 1)
+                xa, xb = pad([tt[q] for q in ad]), pad([P[keys[q] + ".lora_a"] for q in ad])
+                o_ += [op(GEMM_XSEG, a=xa[0], b=xa[1], d=xa[2], sa=xb[0], sb=xb[1], sc=xb[2], k=lora_r, batch=len(ad))]
+            o_ += [op(GEMM_GROUP, c=dx, a=gg[0], sa=gg[1], sb=gg[2], b=w[0], d=w[1], sc=w[2], m=N, n=fin,
+                      k=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=2, tb=1, dt=DT)]
             if not lora:
                 gw = [G[k_ + ".weight"] for k_ in keys] + [0]
                 o_ += on_side([op(GEMM_GROUP, a=x, b=gg[0], sa=gg[1], sb=gg[2], c=gw[0], d=gw[1], sc=gw[2], m=fin, k=N,
                                   n=fo[0], oa=fo[1], ob=fo[2], batch=len(prefs), oc=1, tb=2, dt=DTW)], list(gs_))
             else:
-                for p_, g_, k_ in zip(prefs, gs_, keys):
-                    if p_.split(".")[-1] not in lset:
-                        continue
-                    fout = lin_geom[p_][1]
-                    u = u_l[(i, p_)]
-                    o_ += [op(GEMM_SB, a=g_, b=P[k_ + ".lora_b"], c=t1, m=N, k=fout, n=lora_r, batch=1, tb=1, dt=DT),
-                           op(GEMM_SB, a=t1, b=P[k_ + ".lora_a"], c=dx, m=N, k=lora_r, n=fin, batch=1, tb=1, dt=DT,
-                              alpha=sc_l, beta=1.0),
-                           op(GEMM_SB, a=x, b=t1, c=G[k_ + ".lora_a"], m=fin, n=lora_r, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l),
-                           op(GEMM_SB, a=u, b=g_, c=G[k_ + ".lora_b"], m=lora_r, n=fout, k=N, batch=1, tb=2, dt=DTW, alpha=sc_l)]
+                o_ += lora_grads(i, prefs, x, gs_)
             return o_
+
+        def lin_f_mixed(x, i, prefs, ys_):
+            """projections of one input of which only some carry an adapter: the grouped base launch, then every
+            adapter's two products one by one"""
+            o_ = lin_f_group(x, i, prefs, ys_, adapters=False)
+            for p_, y_ in zip(prefs, ys_):
+                if adapted(p_):
+                    fin, fout = lin_geom[p_]
+                    key, u = f"blocks.{i}.{p_}", u_l[(i, p_)]
+                    o_ += lora_proj([x], [P[key + ".lora_a"]], [u], [fin], 0)
+                    o_ += [op(GEMM_SB, a=u, b=P[key + ".lora_b"], c=y_, m=N, k=lora_r, n=fout, batch=1, dt=DT, beta=1.0)]
+            return o_
+
+        def lin_group_ok(prefs):
+            """projections that share an input run as one group when all of them, or none, carry an adapter"""
+            return len({adapted(p) for p in prefs}) == 1
 
         def norm_b(x, wname, g, res, out):
             """out = res + rmsnorm_bwd(x, w, g); dw -> G[wname] unless frozen"""
@@ -469,10 +512,14 @@ class CompiledTransformer:
             plan = []
             p = f"blocks.{i}."
             plan += [op(RMSNORM, a=xs[i], b=P[p + "attn_norm.weight"], c=ys[i], m=N, n=D, dt=DT, alpha=eps)]
-            # rotary of q and k: in the epilogue of the projection launch (head_dim 64, no adapters: an adapter's
-            # contribution is added to the projection before the rotation), else one launch over both, in place
-            fuse_rope = DH == 64 and not lora
-            plan += lin_f_group(ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), (q2s[i], k2s[i], vs[i]), rope=fuse_rope)
+            # rotary of q and k: in the epilogue of the projection launch (head_dim 64; an adapter's term is part of
+            # the same accumulator, so it is rotated with it), else one launch over both, in place
+            qkv = ("attn.q_proj", "attn.k_proj", "attn.v_proj")
+            fuse_rope = DH == 64 and lin_group_ok(qkv)
+            if lin_group_ok(qkv):
+                plan += lin_f_group(ys[i], i, qkv, (q2s[i], k2s[i], vs[i]), rope=fuse_rope)
+            else:
+                plan += lin_f_mixed(ys[i], i, qkv, (q2s[i], k2s[i], vs[i]))
             if not fuse_rope:
                 plan += [op(ROPE_BTHD, a=q2s[i], b=b_cos, d=b_sin, c=q2s[i], batch=B, m=T, k=H, n=DH, dt=DT,
                             sa=k2s[i], sb=k2s[i], sc=KV)]
@@ -480,8 +527,9 @@ class CompiledTransformer:
                         m=T, n=DH, k=KV, batch=B, tb=H, dt=DT, alpha=scale)]
             plan += lin_f(at2s[i], i, "attn.o_proj", r1s[i], res=xs[i])
             plan += [op(RMSNORM, a=r1s[i], b=P[p + "mlp_norm.weight"], c=zs[i], m=N, n=D, dt=DT, alpha=eps)]
-            if lora:
-                plan += lin_f_group(zs[i], i, ("mlp.gate_proj", "mlp.up_proj"), (gs[i], us[i]))
+            gu = ("mlp.gate_proj", "mlp.up_proj")
+            if adapted(gu[0]) or adapted(gu[1]):
+                plan += lin_f_group(zs[i], i, gu, (gs[i], us[i])) if lin_group_ok(gu) else lin_f_mixed(zs[i], i, gu, (gs[i], us[i]))
                 plan += [op(SILU_MUL, a=gs[i], b=us[i], c=hs[i], n=N * MLP, dt=DT)]
             else:   # gate and up projections with the activation in the epilogue: g, u and h = silu(g)*u in one launch
                 plan += [op(GEMM_GROUP, a=zs[i], b=P[p + "mlp.gate_proj.weight"], sa=P[p + "mlp.up_proj.weight"],

@@ -363,9 +363,104 @@ static int do_gemm(const EngOp* op, bool ex) {
 //           h = silu(g) * u = sc.
 // When the grouped tensor-core kernel cannot serve the request (fp32 plan, shapes, alignment) the problems run
 // one after another through the ordinary GEMM path: mode 2 as one GEMM plus accumulating ones.
+// Extra operands announced by a GEMM_XSEG op for the next GEMM_GROUP op (host state of the single enqueueing thread).
+//   a, b, d = A'_0..2   sa, sb, sc = B'_0..2 (0 / negative = none)   batch = how many   k = depth of each
+//   c = addend buffer (mode 2 only, 0 / negative = none)   beta = its factor
+// Before a mode-1 group: output g gets + A'_g B'_g.  Before a mode-2 group: the pairs are further K-segments of the sum
+// (at most six in all) and the addend joins it: C = alpha * sum + beta * D.
+static struct { int n, a[3], b[3], k, addend; float beta; } g_xseg = {};
+
+static int do_gemm_xseg(const EngOp* op) {
+    g_xseg = {};
+    if (op->batch < 0 || op->batch > 3 || (op->batch > 0 && op->k < 1)) { set_err("gemm_xseg: bad count/depth"); return 112; }
+    const int xa[3] = {op->a, op->b, op->d}, xb[3] = {op->sa, op->sb, op->sc};
+    for (int g = 0; g < op->batch; g++) {
+        if (xa[g] <= 0 || xb[g] <= 0) { set_err("gemm_xseg: operand %d missing", g); return 110; }
+        g_xseg.a[g] = xa[g]; g_xseg.b[g] = xb[g];
+    }
+    g_xseg.n = op->batch; g_xseg.k = op->k;
+    g_xseg.addend = op->c > 0 ? op->c : 0; g_xseg.beta = op->beta;
+    if (g_xseg.n == 0 && !g_xseg.addend) { set_err("gemm_xseg: nothing to add"); return 112; }
+    return 0;
+}
+
+// Adapter weight gradients out_g = alpha * X_g^T S_g of up to three projections (batch = count):
+//   X_g = a, sa, sb (sa / sb <= 0: the same X as problem 0)   S_g = b, d, sc   F_g (columns of X_g) = n, k, tb
+//   out_g = buffer c (fp32) at element offsets oa, ob, oc   m = tokens   gamma = rank R   beta = 1: out_g is [R, F_g]
+//   (the transposed layout), else [F_g, R]   dt: 1 / 2 = bf16 inputs, 0 = fp32 inputs (GEMM path)
+static int do_lora_grad(const EngOp* op) {
+    const int count = op->batch, R = (int)op->gamma, layout = op->beta != 0.f ? 1 : 0, N = op->m;
+    if (count < 1 || count > 3 || R < 1 || N < 1) { set_err("lora_grad: bad count/rank/tokens"); return 112; }
+    const int ix[3] = {op->a, op->sa > 0 ? op->sa : op->a, op->sb > 0 ? op->sb : op->a}, is[3] = {op->b, op->d, op->sc};
+    const int F[3] = {op->n, op->k, op->tb}, off[3] = {op->oa, op->ob, op->oc};
+    const long long ei = op->dt >= 1 ? 2 : 4;
+    const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
+    const void* X[3]; const void* S[3]; float* out[3];
+    for (int g = 0; g < count; g++) {
+        if (F[g] < 1 || off[g] < 0) { set_err("lora_grad: bad width/offset"); return 112; }
+        NEED(ix[g], (long long)N * F[g] * ei); NEED(is[g], (long long)N * R * ei);
+        NEED(op->c, ((long long)off[g] + (long long)F[g] * R) * 4);
+        X[g] = BUFP(ix[g]); S[g] = BUFP(is[g]); out[g] = (float*)BUFP(op->c) + off[g];
+    }
+    if (op->dt >= 1 && !(G.fallback & 1)) {
+        size_t wsb = 0;
+        float* ws = ax_splitk_ws(&wsb);
+        const int rc = ax_lora_grad(count, X, S, out, F, N, R, layout, alpha, ws, wsb, G.cur);
+        if (rc == 0) { G.launches += 2; ax_variant = 0x60; return 0; }
+        if (rc > 0) { set_err("lora_grad failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+    }
+    for (int g = 0; g < count; g++) {          // as transposed-A GEMMs, one per product
+        EngOp q = {};
+        q.kind = ENG_GEMM_SB; q.batch = 1; q.tb = 2; q.dt = op->dt >= 1 ? 2 : 0; q.k = N; q.alpha = alpha; q.d = -1;
+        q.c = op->c; q.oc = off[g];
+        if (layout) { q.a = is[g]; q.b = ix[g]; q.m = R; q.n = F[g]; }
+        else { q.a = ix[g]; q.b = is[g]; q.m = F[g]; q.n = R; }
+        const int rc = do_gemm(&q, false);
+        if (rc) return rc;
+    }
+    ax_variant = 0x61;
+    return 0;
+}
+
+// The skinny products of adapters, out_g [m, R] = alpha * X_g W_g (batch = count <= 3):
+//   X_g = a, sa, sb (sa / sb <= 0: the same X as problem 0) [m, F_g]   W_g = b, d, sc   out_g = buffers c, oa, ob
+//   F_g = n, k, oc   tb = 0: W_g is [F_g, R] (u = x A), 1: [R, F_g] (t = g B^T)   gamma = R   dt as GEMM (0 / 1)
+static int do_lora_proj(const EngOp* op) {
+    const int count = op->batch, R = (int)op->gamma, N = op->m;
+    if (count < 1 || count > 3 || R < 1 || N < 1 || op->tb < 0 || op->tb > 1) { set_err("lora_proj: bad count/rank/tokens/layout"); return 112; }
+    const int ix[3] = {op->a, op->sa > 0 ? op->sa : op->a, op->sb > 0 ? op->sb : op->a}, iw[3] = {op->b, op->d, op->sc};
+    const int io[3] = {op->c, op->oa, op->ob}, F[3] = {op->n, op->k, op->oc};
+    const long long e = op->dt >= 1 ? 2 : 4;
+    const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
+    const void* X[3]; const void* W[3]; void* out[3];
+    for (int g = 0; g < count; g++) {
+        if (F[g] < 1) { set_err("lora_proj: bad width"); return 112; }
+        NEED(ix[g], (long long)N * F[g] * e); NEED(iw[g], (long long)F[g] * R * e); NEED(io[g], (long long)N * R * e);
+        X[g] = BUFP(ix[g]); W[g] = BUFP(iw[g]); out[g] = BUFP(io[g]);
+    }
+    if (op->dt == 1 && !(G.fallback & 1)) {
+        const int rc = ax_lora_proj(count, op->tb, X, W, out, F, N, R, alpha, G.cur);
+        if (rc == 0) { G.launches++; ax_variant = 0x62; return 0; }
+        if (rc > 0) { set_err("lora_proj failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
+    }
+    for (int g = 0; g < count; g++) {          // as GEMMs, one per product
+        EngOp q = {};
+        q.kind = ENG_GEMM_SB; q.batch = 1; q.tb = op->tb; q.dt = op->dt; q.alpha = alpha; q.d = -1;
+        q.a = ix[g]; q.b = iw[g]; q.c = io[g]; q.m = N; q.n = R; q.k = F[g];
+        const int rc = do_gemm(&q, false);
+        if (rc) return rc;
+    }
+    ax_variant = 0x63;
+    return 0;
+}
+
 static int do_gemm_group(const EngOp* op) {
     const int count = op->batch, mode = op->oc;
-    if (count < 2 || count > 3 || mode < 1 || mode > 4 || ((mode == 3 || mode == 4) && count != 2)) { set_err("gemm_group: bad count/mode"); return 112; }
+    const auto xs = g_xseg;                   // consumed by this op whatever happens
+    g_xseg = {};
+    if ((xs.n || xs.addend) && !(mode == 1 || mode == 2)) { set_err("gemm_group: extra operands need mode 1 or 2"); return 112; }
+    if (mode == 1 && ((xs.n && xs.n != count) || xs.addend)) { set_err("gemm_group: mode 1 takes one extra term per output and no addend"); return 112; }
+    if (count < (mode == 2 && xs.n ? 1 : 2) || count > 3 || mode < 1 || mode > 4 || ((mode == 3 || mode == 4) && count != 2)) { set_err("gemm_group: bad count/mode"); return 112; }
     if (mode == 4) {
         const int dt4 = op->dt;
         const long long e4 = dt4 == 1 ? 2 : 4;
@@ -391,7 +486,8 @@ static int do_gemm_group(const EngOp* op) {
     }
     const int ia[3] = {op->a, op->sa, op->sb}, ib[3] = {op->b, mode == 1 ? op->sa : op->d, mode == 1 ? op->sb : op->sc};
     const int ic[3] = {op->c, op->d, op->sc}, dims[3] = {mode == 1 ? op->n : op->k, op->oa, op->ob};
-    EngOp sub[3];
+    EngOp sub[6], xsub[3];
+    int nsub = count;
     for (int g = 0; g < count; g++) {
         sub[g] = *op;
         sub[g].kind = ENG_GEMM_SB;
@@ -401,6 +497,18 @@ static int do_gemm_group(const EngOp* op) {
         else {
             sub[g].a = g ? op->sa : op->a; sub[g].b = g ? op->sb : op->b; sub[g].c = g ? op->d : op->c;
             sub[g].m = g ? op->oa : op->m; sub[g].n = g ? op->ob : op->n; sub[g].beta = 0.f;
+        }
+    }
+    if (mode == 2) {
+        for (int g = 0; g < xs.n; g++, nsub++) {            // further K-segments
+            sub[nsub] = sub[0];
+            sub[nsub].a = xs.a[g]; sub[nsub].b = xs.b[g]; sub[nsub].k = xs.k; sub[nsub].beta = 1.f;
+        }
+        if (xs.addend) { sub[0].kind = ENG_GEMM_EX; sub[0].d = xs.addend; sub[0].beta = xs.beta; }   // one-by-one form: the first product takes the addend
+    } else if (mode == 1) {
+        for (int g = 0; g < xs.n; g++) {                    // one-by-one form: C_g += A'_g B'_g
+            xsub[g] = sub[g];
+            xsub[g].a = xs.a[g]; xsub[g].b = xs.b[g]; xsub[g].k = xs.k; xsub[g].beta = 1.f;
         }
     }
     const int dt = op->dt;
@@ -417,20 +525,31 @@ static int do_gemm_group(const EngOp* op) {
     }
     if (dt >= 1 && !(G.fallback & 1) && !(G.fallback & 4)) {
         const long long ei = 2, eo = dt == 1 ? 2 : 4;
-        const void* A[3]; const void* B[3]; void* C[3]; int mv[3], nv[3], kv[3];
-        for (int g = 0; g < count; g++) {
+        const void* A[6]; const void* B[6]; void* C[6]; int mv[6], nv[6], kv[6];
+        const void* XA[3] = {nullptr, nullptr, nullptr}; const void* XB[3] = {nullptr, nullptr, nullptr};
+        for (int g = 0; g < nsub; g++) {
             const EngOp* q = &sub[g];
             NEED(q->a, (long long)q->m * q->k * ei); NEED(q->b, (long long)q->k * q->n * ei); NEED(q->c, (long long)q->m * q->n * eo);
             A[g] = BUFP(q->a); B[g] = BUFP(q->b); C[g] = BUFP(q->c); mv[g] = q->m; nv[g] = q->n; kv[g] = q->k;
         }
+        if (mode == 1)
+            for (int g = 0; g < xs.n; g++) {
+                const EngOp* q = &xsub[g];
+                NEED(q->a, (long long)q->m * q->k * ei); NEED(q->b, (long long)q->k * q->n * ei);
+                XA[g] = BUFP(q->a); XB[g] = BUFP(q->b);
+            }
+        const void* D = nullptr;
+        if (mode == 2 && xs.addend) { NEED(xs.addend, (long long)op->m * op->n * eo); D = BUFP(xs.addend); }
         const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
         if (rcos) ax_gemm_group_rope(rcos, rsin, ropeT, 3);
-        const int rc = ax_gemm_tc2_group(dt == 1, op->tb, mode, count, A, B, C, mv, nv, kv, alpha, G.d_status, G.cur);
+        const int rc = ax_gemm_tc2_group(dt == 1, op->tb, mode, nsub, A, B, C, mv, nv, kv, alpha, G.d_status, G.cur,
+                                         (mode == 1 && xs.n) ? XA : nullptr, XB, xs.k, D, xs.beta);
         if (rc == 0) { G.launches++; return 0; }
         if (rc > 0) { set_err("grouped tensor-core gemm failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
     }
-    for (int g = 0; g < count; g++) {
-        const int rc = do_gemm(&sub[g], false);
+    for (int g = 0; g < nsub; g++) {
+        int rc = do_gemm(&sub[g], sub[g].kind == ENG_GEMM_EX);
+        if (!rc && mode == 1 && g < xs.n) rc = do_gemm(&xsub[g], false);
         if (rc) return rc;
     }
     if (rcos) {          // unfused: the rotary kernel over the two projections, in place
@@ -474,6 +593,9 @@ static int exec_op(const EngOp* op) {
         case ENG_GEMM: case ENG_GEMM_SB: return do_gemm(op, false);
         case ENG_GEMM_EX: return do_gemm(op, true);
         case ENG_GEMM_GROUP: return do_gemm_group(op);
+        case ENG_GEMM_XSEG: return do_gemm_xseg(op);
+        case ENG_LORA_GRAD: return do_lora_grad(op);
+        case ENG_LORA_PROJ: return do_lora_proj(op);
         case ENG_ADD: case ENG_MUL: case ENG_SILU_MUL: {
             const long long n = op->n;
             NEED(op->a, n * es); NEED(op->b, n * es); NEED(op->c, n * es);

@@ -114,20 +114,24 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar) {
 // Grouped launch: several GEMMs of one layer run as one persistent kernel.
 //   mode 1: `count` problems share A; problem g has its own B (n[g] columns) and its own C — their column
 //           tiles form one tile space (q/k/v or gate/up projections of the same input; their weight gradients).
-//   mode 2: one output accumulates over `count` K-segments, each with its own A and B (kb[s] k-blocks):
-//           dX = dY0 W0^T + dY1 W1^T + ... without round trips of the partial sums through memory.
+//           With xkb > 0 every problem has an extra K-segment of its own behind the shared one: C_g = A B_g + A'_g B'_g
+//           (xkb k-blocks; a low-rank adapter's contribution inside its projection's launch).
+//   mode 2: one output accumulates over `count` (up to 6) K-segments, each with its own A and B (kb[s] k-blocks):
+//           dX = dY0 W0^T + dY1 W1^T + ... without round trips of the partial sums through memory; an addend
+//           (residual) may be fetched by TMA as in the plain GEMM.
 //   mode 3: `count` independent problems of the same depth k, each with its own A, B, C, m[g] and n[g] (weight
 //           gradients of different projections of a layer): their tiles form one tile space, so the second
 //           problem fills the wave the first one leaves half empty.
 //   mode 4: SwiGLU pair — gate and up projections of one input with the activation fused: a 256-wide pair tile holds
 //           128 gate columns (B from problem 0, loaded by CTA 0) and the same 128 up columns (problem 1, CTA 1), so an
 //           epilogue thread has g and u of its row side by side and writes g, u and h = silu(g) * u (three outputs).
-// Grouped launches write through TMA stores, take no addend and do not split K.
+// Grouped launches write through TMA stores and do not split K; only mode 2 takes an addend.
 struct GemmGroup {
     int mode, count;
     int n[3];
-    int kb[3];
+    int kb[6];
     int m[3];
+    int xkb;
     // rotary embedding in the epilogue of a mode-1 launch with bf16 output: the outputs g whose bit is set in
     // rope_mask are [rows, heads * 64] projections (row = batch * rope_T + token); every 64-column piece of the
     // epilogue is one head, its columns i and i + 32 form a rotary pair (tables: fp32 [rope_T, 32])
@@ -147,6 +151,9 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
            const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
            const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
            const __grid_constant__ CUtensorMap tmC1, const __grid_constant__ CUtensorMap tmC2,
+           const __grid_constant__ CUtensorMap tmEA0, const __grid_constant__ CUtensorMap tmEA1,
+           const __grid_constant__ CUtensorMap tmEA2, const __grid_constant__ CUtensorMap tmEB0,
+           const __grid_constant__ CUtensorMap tmEB1, const __grid_constant__ CUtensorMap tmEB2,
            const GemmGroup grp, int tma_out,
            TO* __restrict__ C, const TO* D, int m, int n, int k, float alpha, float beta, int* status,
            int ksplit, float* __restrict__ ws, long long* prof) {
@@ -183,7 +190,12 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int tiles_m = (m + 2 * BM2 - 1) / (2 * BM2);
     int tiles_n = (n + BN2 - 1) / BN2, kblocks_all = (k + BK2 - 1) / BK2;
-    if (grp.mode == 1) { tiles_n = 0; for (int q = 0; q < grp.count; q++) tiles_n += (grp.n[q] + BN2 - 1) / BN2; }
+    const int kb_main = kblocks_all;                       // mode 1: k-blocks of the shared segment
+    if (grp.mode == 1) {
+        tiles_n = 0;
+        for (int q = 0; q < grp.count; q++) tiles_n += (grp.n[q] + BN2 - 1) / BN2;
+        kblocks_all += grp.xkb;
+    }
     if (grp.mode == 2) { kblocks_all = 0; for (int q = 0; q < grp.count; q++) kblocks_all += grp.kb[q]; }
     if (swiglu) tiles_n = (n + 127) / 128;
     int num_tiles = tiles_m * tiles_n;
@@ -262,9 +274,13 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             if (grp.mode == 2) while (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl -= grp.kb[seg]; seg++; }
             for (int kb = kb0; kb < kb1; kb++, kl++, it++, s = (s + 1 == nst ? 0 : s + 1), ph ^= (s == 0)) {
                 if (grp.mode == 2) {
-                    if (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl = 0; seg++; }
-                    pA = seg == 0 ? &tmA : (seg == 1 ? &tmA1 : &tmA2);
-                    pB = seg == 0 ? &tmB : (seg == 1 ? &tmB1 : &tmB2);
+                    while (seg + 1 < grp.count && kl >= grp.kb[seg]) { kl = 0; seg++; }
+                    pA = seg == 0 ? &tmA : seg == 1 ? &tmA1 : seg == 2 ? &tmA2 : seg == 3 ? &tmEA0 : seg == 4 ? &tmEA1 : &tmEA2;
+                    pB = seg == 0 ? &tmB : seg == 1 ? &tmB1 : seg == 2 ? &tmB2 : seg == 3 ? &tmEB0 : seg == 4 ? &tmEB1 : &tmEB2;
+                } else if (grp.mode == 1 && kb == kb_main) {         // the problem's own extra segment
+                    kl = 0;
+                    pA = g == 0 ? &tmEA0 : (g == 1 ? &tmEA1 : &tmEA2);
+                    pB = g == 0 ? &tmEB0 : (g == 1 ? &tmEB1 : &tmEB2);
                 }
                 if (it >= (uint32_t)nst && !mbar_wait(bar_empty + 8 * s, ph ^ 1)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
@@ -595,9 +611,12 @@ static int map_c(CUtensorMap* t, void* base, int m, int n, int nz, int osz) {
 
 // One launch.  grp.mode 0: the plain GEMM (A, B, C, D are element 0 of the arrays).  Grouped modes: see GemmGroup;
 // n[] / k[] then hold the per-problem widths (mode 1) or per-segment depths (mode 2).
+// Extra K-segments of a grouped launch: mode 1 — problem g adds XA[g] XB[g] (depth xk) to its output; mode 2 — they are
+// appended to the launch's own segments (A, B, kv then hold count + xcount entries, at most 6).
 template <int A_MN, int B_MN, typename TO>
 static int gemm2_launch(int slot, int mode, int count, const void* const* A, const void* const* B, void* const* C, const void* D,
-                        const int* mv, const int* nv, const int* kv, float alpha, float beta, int* status, int ksplit, cudaStream_t st) {
+                        const int* mv, const int* nv, const int* kv, float alpha, float beta, int* status, int ksplit, cudaStream_t st,
+                        const void* const* XA = nullptr, const void* const* XB = nullptr, int xk = 0) {
     const int maxp = pairs_for<A_MN, B_MN, TO>(slot, sizeof(TO) == 2 ? 0 : 1);
     if (maxp < 1) return -1;
     const int m = mv[0], n = nv[0], k = kv[0];
@@ -610,7 +629,8 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
         if (mode != 1 || sizeof(TO) != 2 || grp.rope_T < 1 || !grp.rope_cos || !grp.rope_sin) return -1;
         for (int g = 0; g < count; g++) if (((grp.rope_mask >> g) & 1) && nv[g] % 64) return -1;
     }
-    CUtensorMap tmA[3], tmB[3], tmC[3], tmD;
+    CUtensorMap tmA[3], tmB[3], tmC[3], tmD, tmEA[3], tmEB[3];
+    bool have_x = false;
     int tiles_n = 0;
     if (mode == 0) {
         if (map_a<A_MN>(&tmA[0], A[0], m, k) || map_b<B_MN>(&tmB[0], B[0], n, k)) return 2;
@@ -621,12 +641,21 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
             if (map_b<B_MN>(&tmB[g], B[g], nv[g], k)) return 2;
             grp.n[g] = nv[g];
             tiles_n += (nv[g] + 255) / 256;
+            if (XA && xk > 0) {
+                if (map_a<A_MN>(&tmEA[g], XA[g], m, xk) || map_b<B_MN>(&tmEB[g], XB[g], nv[g], xk)) return 2;
+                have_x = true;
+            }
         }
+        if (have_x) grp.xkb = (xk + BK2 - 1) / BK2;
     } else if (mode == 2) {
+        if (count > 6) return -1;
         for (int g = 0; g < count; g++) {
-            if (map_a<A_MN>(&tmA[g], A[g], m, kv[g]) || map_b<B_MN>(&tmB[g], B[g], n, kv[g])) return 2;
+            CUtensorMap* ta = g < 3 ? &tmA[g] : &tmEA[g - 3];
+            CUtensorMap* tb_ = g < 3 ? &tmB[g] : &tmEB[g - 3];
+            if (map_a<A_MN>(ta, A[g], m, kv[g]) || map_b<B_MN>(tb_, B[g], n, kv[g])) return 2;
             grp.kb[g] = (kv[g] + BK2 - 1) / BK2;
         }
+        have_x = count > 3;
         tiles_n = (n + 255) / 256;
     } else if (mode == 3) {
         for (int g = 0; g < count; g++) {
@@ -646,7 +675,8 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     for (int g = 0; g < (per_problem_c ? count : (mode == 4 ? 3 : 1)); g++)
         c_ok = c_ok && ((uintptr_t)C[g] & 15) == 0 && ((long long)nv[per_problem_c ? g : 0] * osz) % 16 == 0;
     if (c_ok && (!has_d || ((uintptr_t)D & 15) == 0)) tma_out = has_d ? 2 : 1;
-    if (mode != 0 && (tma_out != 1 || ksplit != 1)) return -1;          // grouped launches need the plain TMA-store epilogue
+    // grouped launches need the TMA-store epilogue; only the K-segment form takes an addend
+    if (mode != 0 && (ksplit != 1 || !(tma_out == 1 || (tma_out == 2 && mode == 2)))) return -1;
     if (grp.rope_mask && tma_out != 1) return -1;
     if (tma_out) {
         size_t wsb0 = 0;
@@ -663,7 +693,11 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     } else {
         tmC[0] = tmA[0]; tmD = tmA[0];
     }
-    for (int g = 1; g < 3; g++) {           // unused slots carry valid (ignored) maps
+    for (int g = 0; g < 3; g++) {           // unused slots carry valid (ignored) maps
+        const bool used = mode == 1 ? (have_x && g < count) : (mode == 2 && g + 3 < count);
+        if (!used) { tmEA[g] = tmA[0]; tmEB[g] = tmB[0]; }
+    }
+    for (int g = 1; g < 3; g++) {
         if ((mode != 2 && mode != 3) || g >= count) tmA[g] = tmA[0];
         if (mode == 0 || g >= count) tmB[g] = tmB[0];
         if (mode != 4 && (!per_problem_c || g >= count || !tma_out)) tmC[g] = tmC[0];
@@ -692,7 +726,7 @@ static int gemm2_launch(int slot, int mode, int count, const void* const* A, con
     if (want_prof && (cudaMalloc(&prof, 64) != cudaSuccess || cudaMemset(prof, 0, 64) != cudaSuccess)) prof = nullptr;
 #endif
     if (cudaLaunchKernelEx(&cfg, k_gemm_tc2<A_MN, B_MN, TO>, tmA[0], tmB[0], tmC[0], tmD, tmA[1], tmA[2], tmB[1], tmB[2], tmC[1], tmC[2],
-                           grp, tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
+                           tmEA[0], tmEA[1], tmEA[2], tmEB[0], tmEB[1], tmEB[2], grp, tma_out, Cp, Dp, m, n, k, alpha, beta, status, ksplit, ws, prof) != cudaSuccess) return 3;
 #ifdef AXENG_PROF
     if (prof) {
         long long h[8];
@@ -732,15 +766,21 @@ int ax_gemm_tc2(int out_bf16, int tb, const void* A, const void* B, void* C, con
 // Grouped launch (see GemmGroup).  mode 1: A[0] shared, B[g] / C[g] / n[g] per problem, m[0], k[0].  mode 2: A[s] / B[s] /
 // k[s] per segment, C[0], m[0], n[0].  mode 3: A[g] / B[g] / C[g] / m[g] / n[g] per problem, k[0].  Returns -1 when this
 // kernel cannot serve the request (the caller then runs the problems one by one).  mode 4: A[0], B[0] = gate weights,
-// B[1] = up weights (both n[0] wide), C[0] = g, C[1] = u, C[2] = silu(g) * u; bf16 output only.
+// B[1] = up weights (both n[0] wide), C[0] = g, C[1] = u, C[2] = silu(g) * u; bf16 output only.  XA / XB / xk (mode 1):
+// every problem's own extra K-segment.  Mode 2 takes up to 6 segments and an addend D (C = alpha * sum + beta * D).
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
-                      const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st) {
+                      const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st,
+                      const void* const* XA, const void* const* XB, int xk, const void* D, float beta) {
     const int rope_mask = g_rope_req.rope_mask;
-    if (count < 2 || count > 3 || mode < 1 || mode > 4) { g_rope_req.rope_mask = 0; return -1; }
+    const int maxc = mode == 2 ? 6 : 3;
+    if (count < 2 || count > maxc || mode < 1 || mode > 4) { g_rope_req.rope_mask = 0; return -1; }
     if (mode == 4 && (!out_bf16 || count != 2 || !aligned16(C[2]))) { g_rope_req.rope_mask = 0; return -1; }
     if (rope_mask && (mode != 1 || !out_bf16 || tb != 0)) { g_rope_req.rope_mask = 0; return -1; }
+    if (XA && (mode != 1 || tb == 2 || xk < 8 || xk % 8)) { g_rope_req.rope_mask = 0; return -1; }
+    if (D && (mode != 2 || !aligned16(D))) { g_rope_req.rope_mask = 0; return -1; }
     for (int g = 0; g < count; g++) {
         bool bad = !aligned16(A[(mode == 2 || mode == 3) ? g : 0]) || !aligned16(B[g]);
+        if (XA) bad = bad || !XA[g] || !XB[g] || !aligned16(XA[g]) || !aligned16(XB[g]);
         const int mg = m[mode == 3 ? g : 0], ng = n[(mode == 1 || mode == 3) ? g : 0], kg = k[mode == 2 ? g : 0];
         bad = bad || mg < 256 || ng < 8 || kg < 8;
         if (tb == 0) bad = bad || kg % 8 || ng % 8;
@@ -749,8 +789,8 @@ int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* con
         if (bad) { g_rope_req.rope_mask = 0; return -1; }
     }
 #define G2(AM, BMj, SL)                                                                                                        \
-    (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, mode, count, A, B, C, nullptr, m, n, k, alpha, 0.f, status, 1, st)            \
-              : gemm2_launch<AM, BMj, float>(SL, mode, count, A, B, C, nullptr, m, n, k, alpha, 0.f, status, 1, st))
+    (out_bf16 ? gemm2_launch<AM, BMj, bf16>(SL, mode, count, A, B, C, D, m, n, k, alpha, D ? beta : 0.f, status, 1, st, XA, XB, xk)   \
+              : gemm2_launch<AM, BMj, float>(SL, mode, count, A, B, C, D, m, n, k, alpha, D ? beta : 0.f, status, 1, st, XA, XB, xk))
     if (tb == 0) return G2(0, 1, 0);
     if (tb == 1) return G2(0, 0, 1);
     return G2(1, 1, 2);

@@ -111,8 +111,23 @@ void ax_gemm_side(int on);
 // [rows, heads * 64] projections and leave the launch rotated (tables fp32 [T, 32], row = batch * T + token).  The call
 // either honours the request or returns -1; it never ignores it.
 void ax_gemm_group_rope(const float* cs, const float* sn, int T, int mask);
+// XA / XB / xk (mode 1, may be null): problem g adds XA[g] XB[g] of depth xk to its output.  Mode 2 takes up to six
+// segments and an addend D: C = alpha * sum + beta * D.
 int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* const* A, const void* const* B, void* const* C,
-                      const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st);
+                      const int* m, const int* n, const int* k, float alpha, int* status, cudaStream_t st,
+                      const void* const* XA = nullptr, const void* const* XB = nullptr, int xk = 0,
+                      const void* D = nullptr, float beta = 0.f);
+
+// fp32 scratch of the split-K GEMMs (main stream only), also used by the adapter-gradient kernel
+float* ax_splitk_ws(size_t* bytes);
+
+// lora.cu — adapter weight gradients out[g] = alpha * X[g]^T S[g] (X [N, F[g]], S [N, R] bf16; out fp32 [F, R], or
+// [R, F] with layout 1) for up to three products in one launch pair.  -1 when not served.
+// out[g] [N, R] bf16 = alpha * X[g] [N, F[g]] W[g] with W [F, R] (tb 0) or [R, F] (tb 1): the skinny products of an adapter.
+int ax_lora_proj(int count, int tb, const void* const* X, const void* const* W, void* const* out, const int* F, int N, int R,
+                 float alpha, cudaStream_t st);
+int ax_lora_grad(int count, const void* const* X, const void* const* S, float* const* out, const int* F, int N, int R,
+                 int layout, float alpha, float* ws, size_t ws_bytes, cudaStream_t st);
 
 // attn_tc.cu — tcgen05 flash attention (bf16, DH 64/128). -1 when not served.
 int ax_attn_tc_init(void);

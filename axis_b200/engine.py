@@ -27,8 +27,8 @@ import numpy as np
 # fused kinds of this engine (include/axeng.h)
 (GEMM_EX, ROPE_BTHD, ATTN_FWD, ATTN_BWD, RMSNORM_BWD_ACC, CE_FUSED, EMBED_BWD_DET,
  GNORM_FLAT, ADAMW_FLAT, EMBED_I32, REDUCE, ALLGATHER_F32, FORK, JOIN, STREAM,
- SILU_MUL_BWD_RC, GEMM_GROUP, TRANSPOSE_BF16, COLSUM_BATCH, EVENT) = range(32, 52)
-KIND_COUNT = 52
+ SILU_MUL_BWD_RC, GEMM_GROUP, TRANSPOSE_BF16, COLSUM_BATCH, EVENT, GEMM_XSEG, LORA_GRAD, LORA_PROJ) = range(32, 55)
+KIND_COUNT = 55
 KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "COPY", "GEMM_SB",
               "PERM_0213", "ROPE", "SOFTMAX_CAUSAL", "REPEAT_KV", "RMSNORM_BWD", "COLSUM",
               "REPEAT_KV_BWD", "SOFTMAX_BWD", "SILU_BWD", "EMBED", "EMBED_BWD", "CE", "TICK", "CAST",
@@ -36,7 +36,7 @@ KIND_NAMES = ["GEMM", "ADD", "MUL", "SILU_MUL", "RMSNORM", "ADAMW", "SCALE", "CO
               "COUNTVALID", "BROADCAST", "GEMM_EX", "ROPE_BTHD", "ATTN_FWD", "ATTN_BWD",
               "RMSNORM_BWD_ACC", "CE_FUSED", "EMBED_BWD_DET", "GNORM_FLAT", "ADAMW_FLAT",
               "EMBED_I32", "REDUCE", "ALLGATHER_F32", "FORK", "JOIN", "STREAM", "SILU_MUL_BWD_RC",
-              "GEMM_GROUP", "TRANSPOSE_BF16", "COLSUM_BATCH", "EVENT"]
+              "GEMM_GROUP", "TRANSPOSE_BF16", "COLSUM_BATCH", "EVENT", "GEMM_XSEG", "LORA_GRAD", "LORA_PROJ"]
 
 _I32_MAX = 2 ** 31 - 1
 CHUNK = 1024          # arena granularity of the flat optimizer / collective ops
@@ -113,6 +113,15 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                m,oa = m_g; n,ob = n_g
                oc=4 (SwiGLU pair, batch=2): a=A; b=gate weights, sa=up weights (n wide each);
                c=g, d=u, sc=h=silu(g)*u
+    GEMM_XSEG: no launch — extra operands of the NEXT GEMM_GROUP: a,b,d = A'_g; sa,sb,sc = B'_g (batch of them, depth k
+               each); before oc=1: output g gets + A'_g B'_g (an adapter's low-rank term inside the projection's launch);
+               before oc=2 (batch may then be 1): they are further K-segments of the sum (six at most in all), and
+               c > 0 = addend D with factor beta: C = alpha * sum + beta * D
+    LORA_GRAD: adapter weight gradients alpha * X_g^T S_g of batch <= 3 projections: X_g = a,sa,sb (0 = same as a) [m, F_g];
+               S_g = b,d,sc [m, R]; F_g = n,k,tb; R = gamma; out = fp32 buffer c at element offsets oa,ob,oc, laid out
+               [F_g, R], or [R, F_g] with beta = 1; dt 1/2 = bf16 inputs
+    LORA_PROJ: out_g [m, R] = alpha * X_g W_g for batch <= 3 adapters: X_g = a,sa,sb (0 = same as a) [m, F_g]; W_g = b,d,sc,
+               [F_g, R] with tb=0 (u = x A) or [R, F_g] with tb=1 (t = g B^T); out_g = buffers c,oa,ob; F_g = n,k,oc; R = gamma
     RMSNORM_BWD_ACC with oa=j>0: dw is deferred, the per-block partial sums stay in area j-1 of the scratch sb
                (areas of 296*n floats, allocated zeroed)
     COLSUM_BATCH: a=scratch areas, b=int32 table, c=fp32 arena; areas oa..oa+m-1 are summed into

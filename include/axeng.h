@@ -66,6 +66,10 @@ enum EngOpKind {
                                  stored [out,in] in bf16 go to the [in,out] compute / master layout on the device */
     ENG_COLSUM_BATCH = 50,    /* dw of several RMSNORM_BWD_ACC launches whose partial sums were left in scratch (oa > 0 there) */
     ENG_EVENT = 51,           /* cross-stream dependency by id: record on a stream / make a stream wait (main, collectives, side) */
+    ENG_GEMM_XSEG = 52,       /* extra operands of the NEXT GEMM_GROUP (no launch): a low-rank term per output (mode 1), further
+                                 K-segments and a residual addend (mode 2) */
+    ENG_LORA_GRAD = 53,       /* adapter weight gradients alpha * X^T S of up to three projections: X read once, fixed summation order */
+    ENG_LORA_PROJ = 54,       /* the skinny products of adapters, x A (forward) or g B^T (backward), of up to three projections */
     ENG_KIND_COUNT
 };
 

@@ -221,6 +221,31 @@ def run_embed_bwd(b, N, D, V, dt):
     return b.report(f"embed_bwd_det {N} tokens x {D} into {V} rows dt={dt}", ms, bytes_=N * D * es + 2 * min(N, V) * D * 4)
 
 
+def run_lora(b, which, N, Fs, R, chain=1):
+    """LORA_PROJ (skinny products x A / g B^T) or LORA_GRAD (adapter weight gradients) on 1-3 widths; chain > 1: that many
+    instances back to back on separate buffers, figure per instance."""
+    plan, nbytes = [], 0
+    pad = lambda v: list(v) + [0] * (3 - len(v))
+    for _ in range(chain):
+        xs = pad([b.buf(N * F, 1) for F in Fs])
+        f_ = pad(Fs)
+        if which == "lora_proj":
+            ws = pad([b.buf(F * R, 1, scale=0.05) for F in Fs])
+            outs = pad([b.eng.alloc(N * R, 2) for _ in Fs])
+            plan.append(op(E.LORA_PROJ, a=xs[0], sa=xs[1], sb=xs[2], b=ws[0], d=ws[1], sc=ws[2], c=outs[0], oa=outs[1], ob=outs[2],
+                           n=f_[0], k=f_[1], oc=f_[2], m=N, batch=len(Fs), tb=1, gamma=float(R), dt=1))
+        else:
+            ss = pad([b.buf(N * R, 1) for _ in Fs])
+            out = b.eng.alloc(sum(Fs) * R)
+            offs = pad(list(np.cumsum([0] + [F * R for F in Fs[:-1]])))
+            plan.append(op(E.LORA_GRAD, a=xs[0], sa=xs[1], sb=xs[2], b=ss[0], d=ss[1], sc=ss[2], c=out, oa=int(offs[0]),
+                           ob=int(offs[1]), oc=int(offs[2]), n=f_[0], k=f_[1], tb=f_[2], m=N, batch=len(Fs), gamma=float(R), dt=1))
+        nbytes = sum(N * F * 2 for F in Fs)
+    ms = b.time(plan) / chain
+    tag = f" (chain of {chain})" if chain > 1 else ""
+    return b.report(f"{which} N={N} F={list(Fs)} R={R}{tag}", ms, bytes_=nbytes)
+
+
 def run_adamw(b, n):
     n = n // 1024 * 1024
     p, g = b.buf(n, 0, scale=0.02), b.buf(n, 0, scale=1e-3)
@@ -521,6 +546,9 @@ def main():
         run_ce(b, a.rows, a.V, a.dt)
     elif w == "adamw":
         run_adamw(b, a.count)
+    elif w in ("lora_proj", "lora_grad"):
+        for Fs in ((a.dim,), (4096,), (a.dim, 512, 512), (4096, 4096)):
+            run_lora(b, w, a.rows, Fs, 16, a.chain)
     elif w == "embed_bwd":
         run_embed_bwd(b, a.rows, a.dim, a.V, a.dt)
     elif w == "all":

@@ -157,9 +157,38 @@ class InterpEngine:
             return self._gemm(o, False)
         if kind == E.GEMM_EX:
             return self._gemm(o, True)
+        if kind == E.GEMM_XSEG:
+            # no launch: extra operands of the next GEMM_GROUP
+            self.launches -= 1
+            self._xseg = dict(n=batch, a=(a, b, d), b=(sa, sb, sc), k=k, addend=c if c > 0 else 0, beta=beta)
+            return None
+        if kind == E.LORA_PROJ:
+            R = int(gamma)
+            xs_, ws_, os_, fs_ = (a, sa if sa > 0 else a, sb if sb > 0 else a), (b, d, sc), (c, oa, ob), (n, k, oc)
+            sdt = 1 if dt >= 1 else 0
+            for g_ in range(batch):
+                X = self._get(xs_[g_], m * fs_[g_], sdt).reshape(m, fs_[g_])
+                W = self._get(ws_[g_], fs_[g_] * R, sdt)
+                W = W.reshape(R, fs_[g_]).T if tb else W.reshape(fs_[g_], R)
+                self._put(os_[g_], np.float32(1.0 if alpha == 0.0 else alpha) * (X @ W), sdt)
+            return None
+        if kind == E.LORA_GRAD:
+            R, lay = int(gamma), beta != 0.0
+            xs_, ss_, fs_, offs_ = (a, sa if sa > 0 else a, sb if sb > 0 else a), (b, d, sc), (n, k, tb), (oa, ob, oc)
+            in_dt = 1 if dt >= 1 else 0
+            for g_ in range(batch):
+                X = self._get(xs_[g_], m * fs_[g_], in_dt).reshape(m, fs_[g_])
+                S = self._get(ss_[g_], m * R, in_dt).reshape(m, R)
+                r = np.float32(1.0 if alpha == 0.0 else alpha) * (X.T @ S)
+                self._put(c, r.T if lay else r, 0, offs_[g_])
+            return None
         if kind == E.GEMM_GROUP:
             # expanded into the plain GEMMs it stands for (same semantics as the library's fallback)
             self.launches -= 1
+            xs = getattr(self, "_xseg", None)
+            self._xseg = None
+            if xs is not None:
+                assert oc in (1, 2) and (oc == 2 or (xs["n"] == batch and not xs["addend"]))
             ia, ic, dims = (a, sa, sb), (c, d, sc), (n if oc == 1 else k, oa, ob)
             ib = (b, sa, sb) if oc == 1 else (b, d, sc)
             if oc == 4:
@@ -175,11 +204,21 @@ class InterpEngine:
                                batch=1, tb=tb, dt=dt, alpha=alpha)
                 elif oc == 1:
                     sub = E.op(E.GEMM_SB, a=a, b=ib[g_], c=ic[g_], m=m, n=dims[g_], k=k, batch=1, tb=tb, dt=dt, alpha=alpha)
+                elif g_ == 0 and xs is not None and xs["addend"]:
+                    sub = E.op(E.GEMM_EX, a=ia[0], b=ib[0], c=c, d=xs["addend"], m=m, n=n, k=dims[0], batch=1, tb=tb, dt=dt,
+                               alpha=alpha, beta=xs["beta"])
                 else:
                     sub = E.op(E.GEMM_SB, a=ia[g_], b=ib[g_], c=c, m=m, n=n, k=dims[g_], batch=1, tb=tb, dt=dt, alpha=alpha,
                                beta=1.0 if g_ else 0.0)
                 self.launches += 1
-                self._gemm(sub, False)
+                self._gemm(sub, sub[0] == E.GEMM_EX)
+                if oc == 1 and xs is not None:      # the output's own low-rank term
+                    self._gemm(E.op(E.GEMM_SB, a=xs["a"][g_], b=xs["b"][g_], c=ic[g_], m=m, n=dims[g_], k=xs["k"], batch=1,
+                                    tb=tb, dt=dt, alpha=alpha, beta=1.0), False)
+            if oc == 2 and xs is not None:          # further K-segments
+                for g_ in range(xs["n"]):
+                    self._gemm(E.op(E.GEMM_SB, a=xs["a"][g_], b=xs["b"][g_], c=c, m=m, n=n, k=xs["k"], batch=1, tb=tb, dt=dt,
+                                    alpha=alpha, beta=1.0), False)
             if oc == 1 and gamma > 0:       # rotary on the first two outputs ([m, heads*64], row = batch*T + token)
                 T_ = self.bufs[int(beta)].size // (32 * 4)
                 cos = self._f32(int(beta), T_ * 32).reshape(T_, 32)

@@ -275,3 +275,160 @@ def test_grouped_projection_with_rotary_in_the_epilogue(eng, fallback):
                      (eng.download_bf16(ov, (N, KV * 64)), v_ref)):
         assert np.abs(got - ref).max() <= 1.2e-2 * np.abs(ref).max()
     assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [0, 1])
+@pytest.mark.parametrize("tb", [0, 1])
+@pytest.mark.parametrize("count", [2, 3])
+def test_grouped_gemm_shared_input_with_a_low_rank_term_per_output(eng, dt, tb, count):
+    """GEMM_XSEG before GEMM_GROUP mode 1: C_g = alpha * (A B_g + A'_g B'_g) — an adapter's rank-16 product as a
+    K-segment of its projection's launch; the variant number tells that the grouped kernel served it in bf16."""
+    rng = np.random.default_rng(500 + 10 * tb + count + dt)
+    m, k, r, ns = 520, 320, 16, (520, 264, 136)[:count]
+    mk = lambda sh: bf(rng.standard_normal(sh).astype(np.float32)) if dt else rng.standard_normal(sh).astype(np.float32)
+    A = mk((m, k))
+    Bs = [mk((n, k) if tb == 1 else (k, n)) for n in ns]
+    XAs = [mk((m, r)) for _ in ns]
+    XBs = [mk((n, r) if tb == 1 else (r, n)) for n in ns]
+    ia = put(eng, A, dt)
+    ib = [put(eng, b, dt) for b in Bs] + [0]
+    xa = [put(eng, a, dt) for a in XAs] + [0]
+    xb = [put(eng, b, dt) for b in XBs] + [0]
+    ic = [eng.alloc(m * n, 2 if dt else 4) for n in ns] + [0]
+    nn = list(ns) + [0]
+    eng.launch_count(reset=True)
+    eng.run([op(E.GEMM_XSEG, a=xa[0], b=xa[1], d=xa[2], sa=xb[0], sb=xb[1], sc=xb[2], k=r, batch=count),
+             op(E.GEMM_GROUP, a=ia, b=ib[0], sa=ib[1], sb=ib[2], c=ic[0], d=ic[1], sc=ic[2], m=m, k=k,
+                n=nn[0], oa=nn[1], ob=nn[2], batch=count, oc=1, tb=tb, dt=dt, alpha=0.5)])
+    if dt:
+        assert eng.launch_count() == 1                       # one grouped launch, nothing run one by one
+    for g, n in enumerate(ns):
+        got = eng.download_bf16(ic[g], (m, n)) if dt else eng.download(ic[g], (m, n))
+        Bop = Bs[g].T if tb == 1 else Bs[g]
+        XBop = XBs[g].T if tb == 1 else XBs[g]
+        ref = 0.5 * (A.astype(np.float64) @ Bop.astype(np.float64) + XAs[g].astype(np.float64) @ XBop.astype(np.float64))
+        check(got, ref.astype(np.float32), dt == 1, k + r)
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [0, 1])
+@pytest.mark.parametrize("tb", [0, 1])
+@pytest.mark.parametrize("count,extra,addend", [(3, 3, False), (1, 1, True), (2, 2, True), (3, 1, False)])
+def test_grouped_gemm_up_to_six_segments_and_an_addend(eng, dt, tb, count, extra, addend):
+    """GEMM_XSEG before GEMM_GROUP mode 2: further K-segments (depth 16) behind the op's own, and a residual addend:
+    C = sum_s A_s B_s + D."""
+    rng = np.random.default_rng(600 + 10 * tb + 3 * count + extra + dt)
+    m, n, r, ks = 520, 392, 16, (320, 136, 200)[:count]
+    mk = lambda sh: bf(rng.standard_normal(sh).astype(np.float32)) if dt else rng.standard_normal(sh).astype(np.float32)
+    As = [mk((m, k)) for k in ks] + [mk((m, r)) for _ in range(extra)]
+    Bs = [mk((n, k) if tb == 1 else (k, n)) for k in ks] + [mk((n, r) if tb == 1 else (r, n)) for _ in range(extra)]
+    D = mk((m, n))
+    ia = [put(eng, a, dt) for a in As[:count]] + [0, 0]
+    ib = [put(eng, b, dt) for b in Bs[:count]] + [0, 0]
+    xa = [put(eng, a, dt) for a in As[count:]] + [0, 0]
+    xb = [put(eng, b, dt) for b in Bs[count:]] + [0, 0]
+    idd = put(eng, D, dt) if addend else 0
+    ic = eng.alloc(m * n, 2 if dt else 4)
+    kk = list(ks) + [0, 0]
+    eng.launch_count(reset=True)
+    eng.run([op(E.GEMM_XSEG, a=xa[0], b=xa[1], d=xa[2], sa=xb[0], sb=xb[1], sc=xb[2], k=r, batch=extra, c=idd, beta=1.0),
+             op(E.GEMM_GROUP, c=ic, a=ia[0], sa=ia[1], sb=ia[2], b=ib[0], d=ib[1], sc=ib[2], m=m, n=n,
+                k=kk[0], oa=kk[1], ob=kk[2], batch=count, oc=2, tb=tb, dt=dt)])
+    if dt:
+        assert eng.launch_count() == 1
+    ref = D.astype(np.float64) if addend else np.zeros((m, n), np.float64)
+    for a, b_ in zip(As, Bs):
+        ref = ref + a.astype(np.float64) @ (b_.T if tb == 1 else b_).astype(np.float64)
+    got = eng.download_bf16(ic, (m, n)) if dt else eng.download(ic, (m, n))
+    check(got, ref.astype(np.float32), dt == 1, sum(ks) + r * extra)
+    assert eng.device_status() == 0
+
+
+def test_extra_operands_are_refused_where_they_have_no_meaning(eng):
+    """A GEMM_XSEG whose count differs from the mode-1 group's, or before a mode-3 group, is an error, and the pending
+    operands do not leak into a later group."""
+    rng = np.random.default_rng(7)
+    m, k, n, r = 256, 64, 64, 16
+    A, B = bf(rng.standard_normal((m, k)).astype(np.float32)), bf(rng.standard_normal((k, n)).astype(np.float32))
+    ia, ib, ic, id_ = put(eng, A, 1), put(eng, B, 1), eng.alloc(m * n, 2), eng.alloc(m * n, 2)
+    xa, xb = put(eng, bf(rng.standard_normal((m, r)).astype(np.float32)), 1), put(eng, bf(rng.standard_normal((r, n)).astype(np.float32)), 1)
+    grp = op(E.GEMM_GROUP, a=ia, b=ib, sa=ib, c=ic, d=id_, m=m, k=k, n=n, oa=n, batch=2, oc=1, dt=1)
+    with pytest.raises(RuntimeError):
+        eng.run([op(E.GEMM_XSEG, a=xa, sa=xb, k=r, batch=1), grp])
+    eng.run([grp])                                   # the refused operands are gone
+    got = eng.download_bf16(ic, (m, n))
+    check(got, (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32), True, k)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("R", [8, 16, 32])
+def test_adapter_gradients_stream_kernel(eng, layout, R):
+    """LORA_GRAD: alpha * X_g^T S_g for three products (ragged widths and token count), written at offsets of one fp32
+    buffer as [F, R] or [R, F]; bit-identical on a second run (fixed summation order)."""
+    rng = np.random.default_rng(800 + layout + R)
+    N, Fs = 1000, (520, 264, 1536)
+    Xs = [bf(rng.standard_normal((N, F)).astype(np.float32)) for F in Fs]
+    Ss = [bf(rng.standard_normal((N, R)).astype(np.float32)) for _ in Fs]
+    ix = [put(eng, x, 1) for x in Xs]
+    is_ = [put(eng, s_, 1) for s_ in Ss]
+    offs = [64, 64 + Fs[0] * R + 8, 64 + Fs[0] * R + 8 + Fs[1] * R + 8]
+    total = offs[2] + Fs[2] * R + 64
+    out = eng.alloc(total)
+    eng.upload(out, np.full(total, 7.0, np.float32))
+    plan = [op(E.LORA_GRAD, a=ix[0], sa=ix[1], sb=ix[2], b=is_[0], d=is_[1], sc=is_[2], c=out, oa=offs[0], ob=offs[1],
+               oc=offs[2], n=Fs[0], k=Fs[1], tb=Fs[2], m=N, batch=3, gamma=float(R), beta=float(layout), alpha=0.5, dt=1)]
+    eng.run(plan)
+    assert eng.last_variant() == 0x60                         # the streaming kernel, not the GEMM path
+    got = eng.download(out, total)
+    eng.run(plan)
+    assert np.array_equal(got, eng.download(out, total))
+    touched = np.zeros(total, bool)
+    for g, F in enumerate(Fs):
+        ref = 0.5 * (Xs[g].astype(np.float64).T @ Ss[g].astype(np.float64))
+        ref = ref.T if layout else ref
+        seg = got[offs[g]:offs[g] + F * R].reshape(ref.shape)
+        assert np.abs(seg - ref).max() <= 2e-5 * np.abs(ref).max() + 1e-4
+        touched[offs[g]:offs[g] + F * R] = True
+    assert np.all(got[~touched] == 7.0)                       # nothing outside the three outputs is written
+    # the GEMM path (library fallback switch) gives the same numbers within fp32 summation order
+    eng.set_fallback(1)
+    eng.run(plan)
+    eng.set_fallback(0)
+    assert np.abs(eng.download(out, total) - got)[touched].max() <= 1e-3 * np.abs(got[touched]).max()
+    assert eng.device_status() == 0
+
+
+@pytest.mark.parametrize("tb", [0, 1])
+@pytest.mark.parametrize("R", [8, 16, 32])
+def test_adapter_skinny_products_stream_kernel(eng, tb, R):
+    """LORA_PROJ: out_g [N, R] = alpha * X_g W_g (W [F, R]) or X_g W_g^T (W [R, F]) for three adapters at once, ragged token
+    count and widths (one narrower than a 256-column piece, one of several pieces)."""
+    rng = np.random.default_rng(900 + tb + R)
+    N, Fs = 1000, (520, 136, 1536)
+    Xs = [bf(rng.standard_normal((N, F)).astype(np.float32)) for F in Fs]
+    Ws = [bf(rng.standard_normal((R, F) if tb else (F, R)).astype(np.float32) * 0.1) for F in Fs]
+    ix, iw = [put(eng, x, 1) for x in Xs], [put(eng, w, 1) for w in Ws]
+    io = [eng.alloc(N * R + 64, 2) for _ in Fs]
+    for o_ in io:
+        eng.upload_bf16(o_, np.full(N * R + 64, 3.0, np.float32))
+    plan = [op(E.LORA_PROJ, a=ix[0], sa=ix[1], sb=ix[2], b=iw[0], d=iw[1], sc=iw[2], c=io[0], oa=io[1], ob=io[2],
+               n=Fs[0], k=Fs[1], oc=Fs[2], m=N, batch=3, tb=tb, gamma=float(R), alpha=2.0, dt=1)]
+    eng.launch_count(reset=True)
+    eng.run(plan)
+    assert eng.last_variant() == 0x62 and eng.launch_count() == 1
+    for g, F in enumerate(Fs):
+        got = eng.download_bf16(io[g], (N * R + 64,))
+        ref = 2.0 * (Xs[g].astype(np.float64) @ (Ws[g].T if tb else Ws[g]).astype(np.float64))
+        check(got[:N * R].reshape(N, R), ref.astype(np.float32), True, F)
+        assert np.all(got[N * R:] == 3.0)
+    # one shared input (the u_g = x A_g of projections of one input), against the GEMM path
+    plan2 = [op(E.LORA_PROJ, a=ix[2], b=iw[2], d=iw[2], c=io[0], oa=io[1], n=Fs[2], k=Fs[2], m=N, batch=2, tb=tb,
+                gamma=float(R), dt=1)]
+    eng.run(plan2)
+    a0, a1 = eng.download_bf16(io[0], (N, R)), eng.download_bf16(io[1], (N, R))
+    assert np.array_equal(a0, a1)
+    eng.set_fallback(1)
+    eng.run(plan2)
+    eng.set_fallback(0)
+    check(eng.download_bf16(io[0], (N, R)), a0, True, Fs[2])
+    assert eng.device_status() == 0

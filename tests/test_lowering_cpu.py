@@ -8,6 +8,7 @@ import os
 import numpy as np
 import pytest
 
+from axis_b200 import engine as E
 from axis_b200.compile import CompiledTransformer, compile_model, greedy_owner
 from axis_b200.model import Transformer
 from oracle import step_numpy as O
@@ -406,3 +407,21 @@ def test_head_dim_64_plan_with_rotary_inside_the_projection_and_the_attention_ba
     g = ct.grads()
     for nm in g_ref:
         assert rel(g[nm], g_ref[nm]) <= lim_g, nm
+
+
+def test_adapter_plan_is_a_few_fat_launches_per_layer():
+    """With adapters on all seven projections a layer lowers to 8 tensor-core GEMM launches (the four projection groups
+    each way, adapter terms riding as K-segments), 8 streaming launches for the skinny products and 8 for the adapter
+    gradients — not to four extra GEMMs per projection as in axis/compile.py:270-305."""
+    cfg = dict(vocab_size=64, dim=64, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=96, tie_embeddings=True)
+    w = O.init_weights(cfg, seed=3)
+    w.update(O.init_lora(cfg, 8, ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"], seed=4))
+    ct = CompiledTransformer(InterpEngine(), cfg, w, 2, 16, dtype="bf16", lora_r=8, lora_alpha=16.0,
+                             lora_targets=("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"))
+    kinds = [o[0] for o in ct.plan_step]
+    L = cfg["n_layers"]
+    gemms = sum(kinds.count(k) for k in (E.GEMM, E.GEMM_SB, E.GEMM_EX, E.GEMM_GROUP))
+    assert gemms == 8 * L + 2                       # + logits and their input gradient
+    assert kinds.count(E.LORA_PROJ) == 8 * L and kinds.count(E.LORA_GRAD) == 8 * L
+    assert kinds.count(E.GEMM_XSEG) == 8 * L
+    assert kinds.count(E.ROPE_BTHD) == L            # head_dim 16 here: the rotary epilogue serves head_dim 64
