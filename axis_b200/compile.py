@@ -342,8 +342,8 @@ class CompiledTransformer:
                        gamma=float(lora_r), alpha=sc_l, dt=DT)]
 
         def lora_grads(i, prefs, x, gs_):
-            """dA_p = x^T t_p and dB_p = u_p^T g_p of the adapted projections among prefs (x shared): two ops, each a
-            stream over its wide operands with a fixed summation order"""
+            """dA_p = x^T t_p and dB_p = u_p^T g_p of the adapted projections among prefs (x shared): streams over the
+            wide operands with a fixed summation order"""
             pp = [(p_, g_) for p_, g_ in zip(prefs, gs_) if adapted(p_)]
             if not pp:
                 return []
@@ -354,10 +354,11 @@ class CompiledTransformer:
             offb = pad([self._off[f"blocks.{i}.{p_}.lora_b"] for p_, _ in pp])
             fin = lin_geom[pp[0][0]][0]
             fo = pad([lin_geom[p_][1] for p_, _ in pp])
+            # batch < 0: only noted here; one launch at the end of the layer's backward runs the layer's whole set
             return [op(LORA_GRAD, a=x, b=ts[0], d=ts[1], sc=ts[2], c=self.a_grad, oa=offa[0], ob=offa[1], oc=offa[2],
-                       n=fin, k=fin, tb=fin, m=N, batch=len(pp), gamma=float(lora_r), dt=DT),
+                       n=fin, k=fin, tb=fin, m=N, batch=-len(pp), gamma=float(lora_r), dt=DT),
                     op(LORA_GRAD, a=gg[0], sa=gg[1], sb=gg[2], b=us_[0], d=us_[1], sc=us_[2], c=self.a_grad,
-                       oa=offb[0], ob=offb[1], oc=offb[2], n=fo[0], k=fo[1], tb=fo[2], m=N, batch=len(pp),
+                       oa=offb[0], ob=offb[1], oc=offb[2], n=fo[0], k=fo[1], tb=fo[2], m=N, batch=-len(pp),
                        gamma=float(lora_r), beta=1.0, dt=DT)]
 
         def lin_f(x, i, pref, y, res=-1):
@@ -599,6 +600,10 @@ class CompiledTransformer:
                    beta=float(b_cos), gamma=float(b_sin)),
             ]
             plan += lin_b_group((dq, dk, dv), ys[i], i, ("attn.q_proj", "attn.k_proj", "attn.v_proj"), dy)
+            if lora:
+                # every operand of the layer's adapter gradients is still in place (the incoming gradient dcur is
+                # overwritten by the next op): all of them as one launch
+                plan += [op(LORA_GRAD, batch=0)]
             plan += before_write(dcur)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
             if (L - 1 - i) % bucket_layers == bucket_layers - 1 or i == 0:

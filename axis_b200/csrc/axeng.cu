@@ -384,41 +384,70 @@ static int do_gemm_xseg(const EngOp* op) {
     return 0;
 }
 
-// Adapter weight gradients out_g = alpha * X_g^T S_g of up to three projections (batch = count):
+// Adapter weight gradients out_g = alpha * X_g^T S_g of up to three projections (|batch| = count):
 //   X_g = a, sa, sb (sa / sb <= 0: the same X as problem 0)   S_g = b, d, sc   F_g (columns of X_g) = n, k, tb
 //   out_g = buffer c (fp32) at element offsets oa, ob, oc   m = tokens   gamma = rank R   beta = 1: out_g is [R, F_g]
 //   (the transposed layout), else [F_g, R]   dt: 1 / 2 = bf16 inputs, 0 = fp32 inputs (GEMM path)
-static int do_lora_grad(const EngOp* op) {
-    const int count = op->batch, R = (int)op->gamma, layout = op->beta != 0.f ? 1 : 0, N = op->m;
-    if (count < 1 || count > 3 || R < 1 || N < 1) { set_err("lora_grad: bad count/rank/tokens"); return 112; }
-    const int ix[3] = {op->a, op->sa > 0 ? op->sa : op->a, op->sb > 0 ? op->sb : op->a}, is[3] = {op->b, op->d, op->sc};
-    const int F[3] = {op->n, op->k, op->tb}, off[3] = {op->oa, op->ob, op->oc};
-    const long long ei = op->dt >= 1 ? 2 : 4;
-    const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
-    const void* X[3]; const void* S[3]; float* out[3];
+// batch < 0: the products are only noted (host state of the enqueueing thread, sixteen at most); batch == 0 runs all
+// noted products as one launch — the adapters of a whole layer, whose operands are all still in place at the end of
+// the layer's backward.  Tokens, rank and scale of a deferred set are those of its first op.
+struct LoraGradItem { int x, s, c, off, F, layout; };
+static struct { int n, N, R, dt; float alpha; LoraGradItem it[16]; } g_lgrad = {};
+
+static int lora_grad_run(int count, const LoraGradItem* it, int N, int R, int dt, float alpha) {
+    const void* X[16]; const void* S[16]; float* out[16]; int F[16], lay[16];
     for (int g = 0; g < count; g++) {
-        if (F[g] < 1 || off[g] < 0) { set_err("lora_grad: bad width/offset"); return 112; }
-        NEED(ix[g], (long long)N * F[g] * ei); NEED(is[g], (long long)N * R * ei);
-        NEED(op->c, ((long long)off[g] + (long long)F[g] * R) * 4);
-        X[g] = BUFP(ix[g]); S[g] = BUFP(is[g]); out[g] = (float*)BUFP(op->c) + off[g];
+        X[g] = BUFP(it[g].x); S[g] = BUFP(it[g].s); out[g] = (float*)BUFP(it[g].c) + it[g].off;
+        F[g] = it[g].F; lay[g] = it[g].layout;
     }
-    if (op->dt >= 1 && !(G.fallback & 1)) {
+    if (dt >= 1 && !(G.fallback & 1)) {
         size_t wsb = 0;
         float* ws = ax_splitk_ws(&wsb);
-        const int rc = ax_lora_grad(count, X, S, out, F, N, R, layout, alpha, ws, wsb, G.cur);
+        const int rc = ax_lora_grad(count, X, S, out, F, lay, N, R, alpha, ws, wsb, G.cur);
         if (rc == 0) { G.launches += 2; ax_variant = 0x60; return 0; }
         if (rc > 0) { set_err("lora_grad failed rc=%d: %s", rc, cudaGetErrorString(cudaGetLastError())); return rc; }
     }
     for (int g = 0; g < count; g++) {          // as transposed-A GEMMs, one per product
         EngOp q = {};
-        q.kind = ENG_GEMM_SB; q.batch = 1; q.tb = 2; q.dt = op->dt >= 1 ? 2 : 0; q.k = N; q.alpha = alpha; q.d = -1;
-        q.c = op->c; q.oc = off[g];
-        if (layout) { q.a = is[g]; q.b = ix[g]; q.m = R; q.n = F[g]; }
-        else { q.a = ix[g]; q.b = is[g]; q.m = F[g]; q.n = R; }
+        q.kind = ENG_GEMM_SB; q.batch = 1; q.tb = 2; q.dt = dt >= 1 ? 2 : 0; q.k = N; q.alpha = alpha; q.d = -1;
+        q.c = it[g].c; q.oc = it[g].off;
+        if (it[g].layout) { q.a = it[g].s; q.b = it[g].x; q.m = R; q.n = it[g].F; }
+        else { q.a = it[g].x; q.b = it[g].s; q.m = it[g].F; q.n = R; }
         const int rc = do_gemm(&q, false);
         if (rc) return rc;
     }
     ax_variant = 0x61;
+    return 0;
+}
+
+static int do_lora_grad(const EngOp* op) {
+    if (op->batch == 0) {                      // run what was noted
+        const auto p = g_lgrad;
+        g_lgrad.n = 0;
+        return p.n ? lora_grad_run(p.n, p.it, p.N, p.R, p.dt, p.alpha) : 0;
+    }
+    const bool defer = op->batch < 0;
+    const int count = defer ? -op->batch : op->batch, R = (int)op->gamma, layout = op->beta != 0.f ? 1 : 0, N = op->m;
+    if (count > 3 || R < 1 || N < 1) { set_err("lora_grad: bad count/rank/tokens"); return 112; }
+    const int ix[3] = {op->a, op->sa > 0 ? op->sa : op->a, op->sb > 0 ? op->sb : op->a}, is[3] = {op->b, op->d, op->sc};
+    const int F[3] = {op->n, op->k, op->tb}, off[3] = {op->oa, op->ob, op->oc};
+    const long long ei = op->dt >= 1 ? 2 : 4;
+    const float alpha = op->alpha == 0.f ? 1.f : op->alpha;
+    LoraGradItem it[3];
+    for (int g = 0; g < count; g++) {
+        if (F[g] < 1 || off[g] < 0) { set_err("lora_grad: bad width/offset"); return 112; }
+        NEED(ix[g], (long long)N * F[g] * ei); NEED(is[g], (long long)N * R * ei);
+        NEED(op->c, ((long long)off[g] + (long long)F[g] * R) * 4);
+        it[g] = {ix[g], is[g], op->c, off[g], F[g], layout};
+    }
+    if (!defer) return lora_grad_run(count, it, N, R, op->dt, alpha);
+    if (g_lgrad.n == 0) { g_lgrad.N = N; g_lgrad.R = R; g_lgrad.dt = op->dt; g_lgrad.alpha = alpha; }
+    if (g_lgrad.n + count > 16 || g_lgrad.N != N || g_lgrad.R != R || g_lgrad.dt != op->dt || g_lgrad.alpha != alpha) {
+        g_lgrad.n = 0;
+        set_err("lora_grad: a deferred set holds at most 16 products of one token count, rank, type and scale");
+        return 112;
+    }
+    for (int g = 0; g < count; g++) g_lgrad.it[g_lgrad.n++] = it[g];
     return 0;
 }
 

@@ -122,12 +122,12 @@ int ax_gemm_tc2_group(int out_bf16, int tb, int mode, int count, const void* con
 float* ax_splitk_ws(size_t* bytes);
 
 // lora.cu — adapter weight gradients out[g] = alpha * X[g]^T S[g] (X [N, F[g]], S [N, R] bf16; out fp32 [F, R], or
-// [R, F] with layout 1) for up to three products in one launch pair.  -1 when not served.
+// [R, F] where layout[g] is 1) for up to sixteen products in one launch pair.  -1 when not served.
 // out[g] [N, R] bf16 = alpha * X[g] [N, F[g]] W[g] with W [F, R] (tb 0) or [R, F] (tb 1): the skinny products of an adapter.
 int ax_lora_proj(int count, int tb, const void* const* X, const void* const* W, void* const* out, const int* F, int N, int R,
                  float alpha, cudaStream_t st);
-int ax_lora_grad(int count, const void* const* X, const void* const* S, float* const* out, const int* F, int N, int R,
-                 int layout, float alpha, float* ws, size_t ws_bytes, cudaStream_t st);
+int ax_lora_grad(int count, const void* const* X, const void* const* S, float* const* out, const int* F, const int* layout,
+                 int N, int R, float alpha, float* ws, size_t ws_bytes, cudaStream_t st);
 
 // attn_tc.cu — tcgen05 flash attention (bf16, DH 64/128). -1 when not served.
 int ax_attn_tc_init(void);

@@ -4,7 +4,8 @@
 // The reference computes these as GEMMs like any other (axis/compile.py:270-305: dA = x^T (g B^T), dB = (x A)^T g);
 // with R = 16 such a product is a stream over X — 16 flops per byte — and runs at HBM speed only if X is read once,
 // by many CTAs, with next to no work per byte.  A tcgen05 tile would be 1/16 full and a split-K launch per product
-// costs more in fill, drain and reduction than the product itself.  So: one launch covers up to three products; a
+// costs more in fill, drain and reduction than the product itself.  So: one launch covers up to sixteen products (all
+// adapters of a layer); a
 // CTA takes 256 columns of one X and a slice of the tokens, stages 64-token pieces with cp.async, multiplies with
 // mma.sync (the fragments are transposed on the way out of shared memory by ldmatrix.trans) and leaves an fp32
 // partial [F, R] per token slice; a second small kernel sums the slices in a fixed order (bit-reproducible), scales
@@ -27,11 +28,13 @@ struct LoraGradProb {
     float* out;
     int F;                   // columns of X == rows of out
     int chunks;              // ceil(F / LG_COLS)
+    int layout;              // 0: out is [F, R], 1: [R, F]
     long long ws_off;        // offset of this product's partials in the workspace (floats)
 };
+#define LG_MAX_PROBS 16
 struct LoraGradArgs {
-    LoraGradProb p[3];
-    int count, N, nsplit, tok_per, layout;
+    LoraGradProb p[LG_MAX_PROBS];
+    int count, N, nsplit, tok_per;
     float alpha;
 };
 
@@ -149,24 +152,25 @@ __global__ void k_lora_grad_reduce(const LoraGradArgs a, const float* __restrict
         float s = 0.f;
         for (int sp = 0; sp < a.nsplit; sp++) s += ws[P.ws_off + sp * n + i];
         const int f = (int)(i / R), r = (int)(i % R);
-        P.out[a.layout ? (long long)r * P.F + f : i] = a.alpha * s;
+        P.out[P.layout ? (long long)r * P.F + f : i] = a.alpha * s;
     }
 }
 
 static bool g_lora_attr = false;
 
-// X[g] [N, F[g]] bf16, S[g] [N, R] bf16 -> out[g] fp32 ([F, R], or [R, F] with layout 1).  ws: fp32 workspace of ws_bytes.
-// Returns -1 when the request is outside what the kernel serves (the caller then uses GEMMs).
-int ax_lora_grad(int count, const void* const* X, const void* const* S, float* const* out, const int* F, int N, int R,
-                 int layout, float alpha, float* ws, size_t ws_bytes, cudaStream_t st) {
-    if (count < 1 || count > 3 || N < 1 || !(R == 8 || R == 16 || R == 32) || !ws) return -1;
+// X[g] [N, F[g]] bf16, S[g] [N, R] bf16 -> out[g] fp32 ([F, R], or [R, F] where layout[g] is 1).  ws: fp32 workspace of
+// ws_bytes.  Returns -1 when the request is outside what the kernel serves (the caller then uses GEMMs).
+int ax_lora_grad(int count, const void* const* X, const void* const* S, float* const* out, const int* F, const int* layout,
+                 int N, int R, float alpha, float* ws, size_t ws_bytes, cudaStream_t st) {
+    if (count < 1 || count > LG_MAX_PROBS || N < 1 || !(R == 8 || R == 16 || R == 32) || !ws) return -1;
     LoraGradArgs a = {};
-    a.count = count; a.N = N; a.layout = layout; a.alpha = alpha;
+    a.count = count; a.N = N; a.alpha = alpha;
     int chunks = 0, fmax = 0;
     long long fsum = 0;
     for (int g = 0; g < count; g++) {
         if (F[g] < 8 || F[g] % 8 || !aligned16(X[g]) || !aligned16(S[g]) || !out[g]) return -1;
         a.p[g].X = (const bf16*)X[g]; a.p[g].S = (const bf16*)S[g]; a.p[g].out = out[g]; a.p[g].F = F[g];
+        a.p[g].layout = layout[g] ? 1 : 0;
         a.p[g].chunks = (F[g] + LG_COLS - 1) / LG_COLS;
         chunks += a.p[g].chunks; fsum += F[g]; fmax = F[g] > fmax ? F[g] : fmax;
     }

@@ -119,7 +119,8 @@ def op(kind: int, a: int = -1, b: int = -1, c: int = -1, d: int = -1,
                c > 0 = addend D with factor beta: C = alpha * sum + beta * D
     LORA_GRAD: adapter weight gradients alpha * X_g^T S_g of batch <= 3 projections: X_g = a,sa,sb (0 = same as a) [m, F_g];
                S_g = b,d,sc [m, R]; F_g = n,k,tb; R = gamma; out = fp32 buffer c at element offsets oa,ob,oc, laid out
-               [F_g, R], or [R, F_g] with beta = 1; dt 1/2 = bf16 inputs
+               [F_g, R], or [R, F_g] with beta = 1; dt 1/2 = bf16 inputs; batch < 0: the |batch| products are only noted (at most
+               16), batch = 0: everything noted runs as one launch pair (a whole layer's adapters)
     LORA_PROJ: out_g [m, R] = alpha * X_g W_g for batch <= 3 adapters: X_g = a,sa,sb (0 = same as a) [m, F_g]; W_g = b,d,sc,
                [F_g, R] with tb=0 (u = x A) or [R, F_g] with tb=1 (t = g B^T); out_g = buffers c,oa,ob; F_g = n,k,oc; R = gamma
     RMSNORM_BWD_ACC with oa=j>0: dw is deferred, the per-block partial sums stay in area j-1 of the scratch sb

@@ -148,6 +148,17 @@ class InterpEngine:
                 r = r + np.float32(beta) * self._get(src, m * n, out_dt, oc + z * sc).reshape(m, n)
             self._put(c, r, out_dt, oc + z * sc)
 
+    def _lora_grad(self, o):
+        (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc, alpha, beta, gamma) = o
+        R, lay = int(gamma), beta != 0.0
+        xs_, ss_, fs_, offs_ = (a, sa if sa > 0 else a, sb if sb > 0 else a), (b, d, sc), (n, k, tb), (oa, ob, oc)
+        in_dt = 1 if dt >= 1 else 0
+        for g_ in range(abs(batch)):
+            X = self._get(xs_[g_], m * fs_[g_], in_dt).reshape(m, fs_[g_])
+            S = self._get(ss_[g_], m * R, in_dt).reshape(m, R)
+            r = np.float32(1.0 if alpha == 0.0 else alpha) * (X.T @ S)
+            self._put(c, r.T if lay else r, 0, offs_[g_])
+
     def _exec(self, o):
         (kind, a, b, c, d, m, n, k, batch, tb, sa, sb, sc, dt, oa, ob, oc, alpha, beta, gamma) = o
         self.trace.append(kind)
@@ -173,15 +184,20 @@ class InterpEngine:
                 self._put(os_[g_], np.float32(1.0 if alpha == 0.0 else alpha) * (X @ W), sdt)
             return None
         if kind == E.LORA_GRAD:
-            R, lay = int(gamma), beta != 0.0
-            xs_, ss_, fs_, offs_ = (a, sa if sa > 0 else a, sb if sb > 0 else a), (b, d, sc), (n, k, tb), (oa, ob, oc)
-            in_dt = 1 if dt >= 1 else 0
-            for g_ in range(batch):
-                X = self._get(xs_[g_], m * fs_[g_], in_dt).reshape(m, fs_[g_])
-                S = self._get(ss_[g_], m * R, in_dt).reshape(m, R)
-                r = np.float32(1.0 if alpha == 0.0 else alpha) * (X.T @ S)
-                self._put(c, r.T if lay else r, 0, offs_[g_])
-            return None
+            # batch < 0: noted only; batch == 0: everything noted runs now (as one launch pair in the library)
+            pend = getattr(self, "_lgrad", [])
+            if batch == 0:
+                self._lgrad = []
+                self.launches += 1 if pend else -1
+                for o2 in pend:
+                    self._lora_grad(o2)
+                return None
+            if batch < 0:
+                self.launches -= 1
+                self._lgrad = pend + [o]
+                return None
+            self.launches += 1
+            return self._lora_grad(o)
         if kind == E.GEMM_GROUP:
             # expanded into the plain GEMMs it stands for (same semantics as the library's fallback)
             self.launches -= 1

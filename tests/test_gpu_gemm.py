@@ -432,3 +432,31 @@ def test_adapter_skinny_products_stream_kernel(eng, tb, R):
     eng.set_fallback(0)
     check(eng.download_bf16(io[0], (N, R)), a0, True, Fs[2])
     assert eng.device_status() == 0
+
+
+def test_adapter_gradients_noted_and_run_as_one_launch(eng):
+    """LORA_GRAD with batch < 0 only notes its products; batch = 0 runs all of them (both layouts mixed) as one launch pair."""
+    rng = np.random.default_rng(77)
+    N, R, Fs = 777, 16, (264, 520, 136, 1032)
+    Xs = [bf(rng.standard_normal((N, F)).astype(np.float32)) for F in Fs]
+    Ss = [bf(rng.standard_normal((N, R)).astype(np.float32)) for _ in Fs]
+    ix, is_ = [put(eng, x, 1) for x in Xs], [put(eng, s_, 1) for s_ in Ss]
+    offs = list(np.cumsum([0] + [F * R for F in Fs]))
+    out = eng.alloc(int(offs[-1]))
+    eng.upload(out, np.zeros(int(offs[-1]), np.float32))
+    eng.launch_count(reset=True)
+    eng.run([op(E.LORA_GRAD, a=ix[0], sa=ix[1], b=is_[0], d=is_[1], c=out, oa=int(offs[0]), ob=int(offs[1]), n=Fs[0], k=Fs[1],
+                m=N, batch=-2, gamma=float(R), dt=1),
+             op(E.LORA_GRAD, a=ix[2], sa=ix[3], b=is_[2], d=is_[3], c=out, oa=int(offs[2]), ob=int(offs[3]), n=Fs[2], k=Fs[3],
+                m=N, batch=-2, gamma=float(R), beta=1.0, dt=1)])
+    assert eng.launch_count() == 0 and np.all(eng.download(out, int(offs[-1])) == 0)      # nothing has run yet
+    eng.run([op(E.LORA_GRAD, batch=0)])
+    assert eng.launch_count() == 2 and eng.last_variant() == 0x60
+    got = eng.download(out, int(offs[-1]))
+    for g, F in enumerate(Fs):
+        ref = Xs[g].astype(np.float64).T @ Ss[g].astype(np.float64)
+        ref = ref.T if g >= 2 else ref
+        seg = got[offs[g]:offs[g + 1]].reshape(ref.shape)
+        assert np.abs(seg - ref).max() <= 2e-5 * np.abs(ref).max() + 1e-4
+    eng.run([op(E.LORA_GRAD, batch=0)])              # an empty set is a no-op
+    assert eng.launch_count() == 2 and eng.device_status() == 0

@@ -411,7 +411,7 @@ def test_head_dim_64_plan_with_rotary_inside_the_projection_and_the_attention_ba
 
 def test_adapter_plan_is_a_few_fat_launches_per_layer():
     """With adapters on all seven projections a layer lowers to 8 tensor-core GEMM launches (the four projection groups
-    each way, adapter terms riding as K-segments), 8 streaming launches for the skinny products and 8 for the adapter
+    each way, adapter terms riding as K-segments), 8 streaming launches for the skinny products and one for all adapter
     gradients — not to four extra GEMMs per projection as in axis/compile.py:270-305."""
     cfg = dict(vocab_size=64, dim=64, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=96, tie_embeddings=True)
     w = O.init_weights(cfg, seed=3)
@@ -422,6 +422,8 @@ def test_adapter_plan_is_a_few_fat_launches_per_layer():
     L = cfg["n_layers"]
     gemms = sum(kinds.count(k) for k in (E.GEMM, E.GEMM_SB, E.GEMM_EX, E.GEMM_GROUP))
     assert gemms == 8 * L + 2                       # + logits and their input gradient
-    assert kinds.count(E.LORA_PROJ) == 8 * L and kinds.count(E.LORA_GRAD) == 8 * L
+    assert kinds.count(E.LORA_PROJ) == 8 * L
+    assert sum(1 for o in ct.plan_step if o[0] == E.LORA_GRAD and o[8] == 0) == L        # one run per layer ...
+    assert sum(-o[8] for o in ct.plan_step if o[0] == E.LORA_GRAD and o[8] < 0) == 14 * L   # ... of its 14 noted products
     assert kinds.count(E.GEMM_XSEG) == 8 * L
     assert kinds.count(E.ROPE_BTHD) == L            # head_dim 16 here: the rotary epilogue serves head_dim 64
