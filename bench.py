@@ -422,6 +422,7 @@ def main():
         line["attn_bwd"] = attn_bwd_isolated()
         if not args.no_cpu_baseline:
             line["c1_measured"] = {"cpu": cpu_c1_measured(), "gpu_fp32": gpu_c1()}
+        line["other_configs"] = {"c5": other_config("c5")}
     barrier()
     if RANK == 0:
         emit(line)
@@ -486,6 +487,24 @@ def attn_bwd_isolated(reps=20):
     return {"shape": "Q/dO [4,24,2048,64] K/V [4,8,2048,64] bf16 causal GQA 3:1", "ms": ms, "tflops": tf, "flops": flops,
             "frac_burst": tf / tf_burst, "frac_sustained": tf / tf_sus, "peak_source": src, "reps": reps,
             "l2": "flushed between repetitions", "launches_per_call": 4, "device_status": st}
+
+
+def other_config(key, steps=5, warmup=3):
+    """A second configuration measured by this script itself in a child process (`bench.py --config <key>`), reduced
+    to the figures that matter: the long-sequence adapter fine-tune (BASELINE configs[4]) next to the headline line."""
+    import subprocess
+    cmd = [sys.executable, os.path.abspath(__file__), "--config", key, "--steps", str(steps), "--warmup", str(warmup),
+           "--no-cpu-baseline"]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        d = json.loads(r.stdout.strip().splitlines()[-1])
+    except (subprocess.SubprocessError, ValueError, IndexError) as e:
+        return {"error": f"{type(e).__name__}: {e}"[:200], "command": " ".join(cmd[1:])}
+    gemm = sum(v["calls"] for k_, v in d.get("kernels", {}).items() if k_.startswith("GEMM") and k_ != "GEMM_XSEG")
+    return {"workload": d["config"]["workload"], "metric": d["metric"], "value": d["value"], "unit": d["unit"],
+            "ms_per_step": d["ms_per_step"], "steps": d["steps"], "warmup": d["warmup"], "gemm_launches_per_step": gemm,
+            "gpu_launches": d["gpu_launches"], "loss_first": d["loss_first"], "loss_last": d["loss_last"],
+            "clocks": d["clocks"], "device_status": d["device_status"], "command": "python bench.py " + " ".join(cmd[2:])}
 
 
 def gpu_c1(steps=30):
