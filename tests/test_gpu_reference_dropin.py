@@ -83,5 +83,5 @@ def test_reference_python_capture_and_replay_on_this_library(ref):
     assert np.allclose(replayed, eager, rtol=2e-6, atol=0)
     wb = b.get_weights()
     for n in wa:
-        assert np.abs(wa[n] - wb[n]).max() <= 1e-6, n
+        assert np.abs(wa[n] - wb[n]).max() <= 5e-6, n       # atomic summation order differs from run to run
     assert eager[2] < eager[0]
