@@ -42,7 +42,7 @@ def _write_npz_atomic(path: str, payload: Dict[str, np.ndarray]) -> None:
 
 
 def _pack(state: Dict[str, np.ndarray], pnames: List[str], owned: Iterable[str], step: int, meta: Optional[dict],
-          rank: int, world: int) -> Dict[str, np.ndarray]:
+          rank: int, world: int, scheduler_step: Optional[int] = None) -> Dict[str, np.ndarray]:
     owned = list(owned)
     index = {nm: i for i, nm in enumerate(pnames)}
     payload: Dict[str, np.ndarray] = {}
@@ -54,14 +54,39 @@ def _pack(state: Dict[str, np.ndarray], pnames: List[str], owned: Iterable[str],
               "optimizer": {"t": int(round(float(np.asarray(state["_t"]).reshape(-1)[0]))),
                             "lr": float(np.asarray(state["_lr"]).reshape(-1)[0])},
               "pnames": list(pnames), "owned": owned, "rank": int(rank), "world": int(world)}
+    if scheduler_step is not None:      # the reference's key (axis/checkpoint.py:34-35)
+        header["scheduler_step"] = int(scheduler_step)
     payload["__header__"] = np.frombuffer(json.dumps(header).encode("utf-8"), dtype=np.uint8)
     return payload
 
 
-def save(path: str, ct, step: int = 0, meta: Optional[dict] = None) -> None:
-    """Write the state this rank holds (everything, or its ZeRO-1 shard) to `path`."""
+def save(path: str, ct, step: int = 0, meta: Optional[dict] = None, scheduler_step: Optional[int] = None) -> None:
+    """Write the state this rank holds (everything, or its ZeRO-1 shard) to `path`.  scheduler_step: the position of
+    the caller's learning-rate schedule, stored under the reference's header key."""
     _write_npz_atomic(path, _pack(ct.state_dict(), list(ct.pnames), list(ct.owned), step, meta,
-                                  getattr(ct, "rank", 0), getattr(ct, "world", 1)))
+                                  getattr(ct, "rank", 0), getattr(ct, "world", 1), scheduler_step))
+
+
+def _moment_owners(names: List[str], shapes: Dict[str, tuple], moments: Dict[int, tuple]) -> Dict[str, int]:
+    """Which parameter each `opt/m/<i>` of a reference-written file belongs to (such a file names no parameters for its
+    moments: they follow the optimizer's parameter list, axis/checkpoint.py:27-33).  With a moment per model entry the
+    lists coincide.  With fewer — an optimizer over the trainable subset, e.g. adapters on a frozen base — the
+    moments are matched, in order, to the adapter parameters if their count fits, and every pairing must agree in
+    shape; anything else is refused rather than guessed."""
+    idx = sorted(moments)
+    if idx != list(range(len(idx))):
+        raise ValueError("optimizer moments are not numbered 0..n-1")
+    if len(idx) == len(names):
+        cand = names
+    else:
+        cand = [nm for nm in names if nm.endswith((".lora_a", ".lora_b"))]
+        if len(cand) != len(idx):
+            raise ValueError(f"{len(idx)} optimizer moments for {len(names)} parameters ({len(cand)} of them adapters): "
+                             "the file does not say which parameters the optimizer covered")
+    for i, nm in zip(idx, cand):
+        if tuple(moments[i]) != tuple(shapes[nm]):
+            raise ValueError(f"opt/m/{i} has shape {tuple(moments[i])}, parameter {nm} has {tuple(shapes[nm])}")
+    return {nm: i for i, nm in zip(idx, cand)}
 
 
 def read(path: str):
@@ -70,18 +95,20 @@ def read(path: str):
         header = json.loads(bytes(z["__header__"]).decode("utf-8"))
         names = [k[len("model/"):] for k in z.files if k.startswith("model/")]
         pnames = header.get("pnames")
-        if pnames is None:
-            # a file written by the reference: its moment lists follow the model's parameter order,
-            # which is the order of its model/ entries
-            pnames = names
-        index = {nm: i for i, nm in enumerate(pnames)}
+        if pnames is not None:
+            index = {nm: i for i, nm in enumerate(pnames)}
+        else:
+            # a file written by the reference
+            moments = {int(k.rsplit("/", 1)[1]): z[k].shape for k in z.files if k.startswith("opt/m/")}
+            index = _moment_owners(names, {nm: z[f"model/{nm}"].shape for nm in names}, moments) if moments else {}
         state: Dict[str, np.ndarray] = {}
         for nm in names:
             state[f"w/{nm}"] = z[f"model/{nm}"]
-            mk, vk = f"opt/m/{index[nm]}", f"opt/v/{index[nm]}"
-            if mk in z.files:
-                state[f"m/{nm}"] = z[mk]
-                state[f"v/{nm}"] = z[vk]
+            if nm in index:
+                mk, vk = f"opt/m/{index[nm]}", f"opt/v/{index[nm]}"
+                if mk in z.files:
+                    state[f"m/{nm}"] = z[mk]
+                    state[f"v/{nm}"] = z[vk]
         opt = header.get("optimizer", {"t": 0, "lr": 0.0})
         state["_t"] = np.array([opt["t"]], dtype=np.float32)
         state["_lr"] = np.array([opt["lr"]], dtype=np.float32)
@@ -100,8 +127,11 @@ def load(path: str, ct) -> dict:
         if f"m/{nm}" not in state:      # weights-only file: fresh optimizer state
             state[f"m/{nm}"] = np.zeros(ct.shapes[nm], np.float32)
             state[f"v/{nm}"] = np.zeros(ct.shapes[nm], np.float32)
+        for pre in ("m/", "v/"):
+            if tuple(state[pre + nm].shape) != tuple(ct.shapes[nm]):
+                raise ValueError(f"{nm}: checkpoint moment {pre[0]} has shape {state[pre + nm].shape}, model has {ct.shapes[nm]}")
     ct.load_state_dict(state)
-    return header
+    return header               # "scheduler_step", when the writer had a schedule, is in the header for the caller's schedule
 
 
 def merge_shards(paths: Iterable[str], out_path: str) -> dict:
@@ -118,7 +148,7 @@ def merge_shards(paths: Iterable[str], out_path: str) -> dict:
         if first is None:
             first = header
         else:
-            for k in ("step", "pnames"):
+            for k in ("step", "pnames", "scheduler_step"):
                 if header.get(k) != first.get(k):
                     raise ValueError(f"shard {p} disagrees with {paths[0]} on {k}")
             if header["optimizer"] != first["optimizer"]:
@@ -135,5 +165,6 @@ def merge_shards(paths: Iterable[str], out_path: str) -> dict:
         raise ValueError(f"shards lack {len(lacking)} parameters, e.g. {lacking[0]}")
     merged["_t"] = np.array([first["optimizer"]["t"]], np.float32)
     merged["_lr"] = np.array([first["optimizer"]["lr"]], np.float32)
-    _write_npz_atomic(out_path, _pack(merged, pnames, pnames, first["step"], first.get("meta"), 0, 1))
+    _write_npz_atomic(out_path, _pack(merged, pnames, pnames, first["step"], first.get("meta"), 0, 1,
+                                      first.get("scheduler_step")))
     return first
