@@ -165,14 +165,28 @@ class CompiledTransformer:
         self._cown, _ = greedy_owner(self.pnames, self.shapes, cw, cw > 1)
 
         # ── arena layout: by reduction owner, then by bucket (order of completion in backward) ──
+        # Layers complete in reverse order; `bucket_layers` of them form a bucket, except that the layers finished
+        # last (the first of the model) form buckets of half, a quarter ... one layer: the reduction of the final
+        # bucket has nothing left to hide behind, and under ZeRO-1 the first forward ops of the next step wait for
+        # exactly these weights, so both should be small.
+        sizes, rem = [], L
+        while rem > bucket_layers:
+            sizes.append(bucket_layers); rem -= bucket_layers
+        while rem > 1:
+            sizes.append(rem - rem // 2); rem //= 2
+        sizes.append(1)
+        pos_bucket, bucket_end = [], set()      # backward position (L-1-layer) -> bucket; positions that end a bucket
+        for b_, sz in enumerate(sizes):
+            pos_bucket += [1 + b_] * sz
+            bucket_end.add(len(pos_bucket) - 1)
+
         def bucket_of(nm: str) -> int:
             if nm in ("norm.weight", "lm_head.weight"):
                 return 0
             if nm == "embed.weight":         # its scatter-add ends the backward: a bucket of its own, reduced last
-                return 2 + (L - 1) // bucket_layers
-            layer = int(nm.split(".")[1])
-            return 1 + (L - 1 - layer) // bucket_layers
-        nb = 3 + (L - 1) // bucket_layers
+                return 1 + len(sizes)
+            return pos_bucket[L - 1 - int(nm.split(".")[1])]
+        nb = 2 + len(sizes)
         self._nbuckets = nb
         off = 0
         self._off: Dict[str, int] = {}
@@ -606,10 +620,10 @@ class CompiledTransformer:
                 plan += [op(LORA_GRAD, batch=0)]
             plan += before_write(dcur)
             plan += norm_b(xs[i], p + "attn_norm.weight", dy, dr1, dcur)
-            if (L - 1 - i) % bucket_layers == bucket_layers - 1 or i == 0:
+            if (L - 1 - i) in bucket_end:
                 plan += flush_dw()
-                marks[1 + (L - 1 - i) // bucket_layers] = len(plan)
-                mark_ev[1 + (L - 1 - i) // bucket_layers] = ev[0]
+                marks[pos_bucket[L - 1 - i]] = len(plan)
+                mark_ev[pos_bucket[L - 1 - i]] = ev[0]
         if not lora:
             if not tied:
                 plan += [op(SCALE, a=G["embed.weight"], c=G["embed.weight"], n=V * D, alpha=0.0)]

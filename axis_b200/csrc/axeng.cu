@@ -1042,7 +1042,10 @@ static int run_ops(const EngOp* ops, int n_ops) {
             G.prof_ms[ops[i].kind] += ms; G.prof_calls[ops[i].kind]++;
             cudaEventDestroy(e0); cudaEventDestroy(e1);
         }
-        if (rc) { G.last_op_rc = rc; G.cur = G.stream; return 1000 + i; }
+        if (rc) {                      // a failed plan leaves nothing noted for a later one
+            g_xseg = {}; g_lgrad.n = 0;
+            G.last_op_rc = rc; G.cur = G.stream; return 1000 + i;
+        }
     }
     G.cur = G.stream;
     return 0;
