@@ -275,13 +275,26 @@ __global__ void k_attn_bwd_prep128(const bf16* __restrict__ o, const bf16* __res
 
 #define BWD128_THREADS 288     // 8 softmax warps (two per TMEM lane quadrant) + 1 control warp
 #define QS 64                  // queries per sub-tile
+#define QST 3                  // Q/dO ring stages
 struct Bwd128Smem {
-    // K, V: 128 keys x 128 (two blocks of 16 KB); Q/dO sub-tiles: 64 x 128 (two blocks of 8 KB), two stages;
-    // dS^T: 128 keys x 64 queries bf16; dQ staging: 64 queries x 128 fp32 (four blocks of 8 KB)
-    static constexpr int K = 0, V = 32768, Q0 = 65536, DO0 = Q0 + 2 * 16384, DS = DO0 + 2 * 16384, DQ = DS + 16384,
-                         STAT = DQ + 32768, BARS = STAT + 1024, TOTAL = BARS + 128 + 1024;
+    // K, V: 128 keys x 128 (two blocks of 16 KB); Q/dO sub-tiles: 64 x 128 (two blocks of 8 KB), three stages;
+    // dS^T: 128 keys x 64 queries bf16, two buffers; dQ staging: 64 queries x 128 fp32 (four blocks of 8 KB);
+    // row statistics of a sub-tile (64 lse, 64 D) beside its Q/dO stage
+    static constexpr int K = 0, V = 32768, Q0 = 65536, DO0 = Q0 + QST * 16384, DS = DO0 + QST * 16384, DQ = DS + 2 * 16384,
+                         STAT = DQ + 32768, BARS = STAT + QST * 512, TOTAL = BARS + 256 + 1024;
 };
+static_assert(Bwd128Smem::TOTAL <= 227 * 1024, "head_dim-128 backward shared memory exceeds the per-CTA limit");
 
+// One CTA per (128 keys, head) walks the query sub-tiles (64 queries) of the causal range.  Per sub-tile:
+//   S^T = K Q^T, dP^T = V dO^T   16 MMAs into TMEM (lanes = keys)
+//   softmax warps                 read their 32 + 32 values in one TMEM round trip and release the two accumulators at
+//                                 once, so S^T / dP^T of the next sub-tile are computed under this one's arithmetic;
+//                                 P^T and dS^T go to TMEM columns of their own (packed bf16) and dS^T to shared memory
+//   dV += P^T dO, dK += dS^T Q    A operands from TMEM;  dQ^T = K^T dS^T with dS^T from shared memory (two buffers)
+// The control warp issues S^T / dP^T of sub-tile i first and then dV, dK, dQ^T of sub-tile i-1, so the tensor pipe
+// always has the independent half of the work queued.  TMEM (512 columns): S^T 64, dP^T 64, dV 128, dK 128, dQ^T 64,
+// P^T 32, dS^T 32.  dQ^T is single: the softmax warps move it out (transposing staging + TMA reduce-add) right after
+// they have handed over P^T / dS^T of the following sub-tile.
 __global__ void __launch_bounds__(BWD128_THREADS, 1)
 k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -291,11 +304,12 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sb = smem_u32(smem);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Bwd128Smem::BARS);
-    // kv_full, q_full[2], q_empty[2], sdp_full, pds_full, dq_full[2]
-    const uint32_t b_kv = smem_u32(bars), b_qf = b_kv + 8, b_qe = b_qf + 16, b_sdp = b_qe + 16, b_pds = b_sdp + 8, b_dq = b_pds + 8;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    // kv_full, q_full[3], q_empty[3], sdp_full, sdp_free, pds_full, dq_full, dq_empty
+    const uint32_t b_kv = smem_u32(bars), b_qf = b_kv + 8, b_qe = b_qf + 8 * QST, b_sdp = b_qe + 8 * QST, b_sfree = b_sdp + 8,
+                   b_pds = b_sfree + 8, b_dq = b_pds + 8, b_dqe = b_dq + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* s_stat = reinterpret_cast<float*>(smem + Bwd128Smem::STAT);   // [2][lse*log2(e) 64 | D 64]
+    float* s_stat = reinterpret_cast<float*>(smem + Bwd128Smem::STAT);   // [stage][lse 64 | D 64]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // 1-D grid ordered by decreasing work: key tile 0 of all (kv head, batch) pairs first
@@ -308,8 +322,8 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(b_kv, 1);
-        for (int s = 0; s < 2; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 1); mbar_init(b_dq + 8 * s, 1); }
-        mbar_init(b_sdp, 1); mbar_init(b_pds, 256);
+        for (int s = 0; s < QST; s++) { mbar_init(b_qf + 8 * s, 1); mbar_init(b_qe + 8 * s, 1); }
+        mbar_init(b_sdp, 1); mbar_init(b_sfree, 256); mbar_init(b_pds, 256); mbar_init(b_dq, 1); mbar_init(b_dqe, 256);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -318,8 +332,9 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // columns: S^T/P^T 0..63, dP^T/dS^T 64..127, dV 128..255, dK 256..383, dQ^T[0] 384..447, dQ^T[1] 448..511
-    const uint32_t t_S = tmem, t_dP = tmem + 64, t_dV = tmem + 128, t_dK = tmem + 256, t_dQ = tmem + 384;
+    // columns: S^T 0..63, dP^T 64..127, dV 128..255, dK 256..383, dQ^T 384..447, P^T 448..479, dS^T 480..511 (packed bf16)
+    const uint32_t t_S = tmem, t_dP = tmem + 64, t_dV = tmem + 128, t_dK = tmem + 256, t_dQ = tmem + 384, t_P = tmem + 448,
+                   t_dS = tmem + 480;
 
     if (warp == 8) {
         {   // the whole warp runs the loop converged; lane 0 issues the TMA loads, one elected lane the MMAs
@@ -341,8 +356,13 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             auto load_q = [&](int it) {
                 if (lane != 0) return;
-                const int s = it & 1, hh = it / per_head, u = 2 * j + it % per_head, h = g * rep + hh;
-                mbar_expect_tx(b_qf + 8 * s, 32768);
+                const int s = it % QST, hh = it / per_head, u = 2 * j + it % per_head, h = g * rep + hh;
+                mbar_expect_tx(b_qf + 8 * s, 32768 + 512);
+                // the sub-tile's row statistics ride on the same barrier (a softmax warp that loaded them from global
+                // memory itself would expose that latency at its next scoreboard wait)
+                const long long sidx = ((long long)b * H + h) * T + u * QS;
+                bulk_load_1d(sb + Bwd128Smem::STAT + s * 512, lse + sidx, 256, b_qf + 8 * s);
+                bulk_load_1d(sb + Bwd128Smem::STAT + s * 512 + 256, Dv + sidx, 256, b_qf + 8 * s);
                 tma_load_4d(sb + Bwd128Smem::Q0 + s * 16384, &tmQ, b_qf + 8 * s, 0, h, u * QS, b);
                 tma_load_4d(sb + Bwd128Smem::Q0 + s * 16384 + 8192, &tmQ, b_qf + 8 * s, 64, h, u * QS, b);
                 tma_load_4d(sb + Bwd128Smem::DO0 + s * 16384, &tmdO, b_qf + 8 * s, 0, h, u * QS, b);
@@ -351,41 +371,49 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             load_q(0);
             __syncwarp();
             if (!mbar_wait(b_kv, 0)) ok = false;
-            for (int it = 0; it < n_it && ok; it++) {
-                const int s = it & 1;
-                const uint32_t so = (uint32_t)s * 1024;                  // stage offset (16 KB) in 16-byte units
-                if (it + 1 < n_it) {        // prefetch the next Q/dO sub-tile once its stage is free
-                    if (it >= 1 && !mbar_wait(b_qe + 8 * (s ^ 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
+            // iteration it: S^T / dP^T of sub-tile it, then dV, dK and dQ^T of sub-tile it - 1 (one more round at the end)
+            for (int it = 0; it <= n_it && ok; it++) {
+                if (it + 1 < n_it) {        // prefetch sub-tile it+1: its stage was last read by dV / dK of sub-tile it-2
+                    if (it >= 2 && !mbar_wait(b_qe + 8 * ((it - 2) % QST), ((it - 2) / QST) & 1)) { ok = false; break; }
                     load_q(it + 1);
                     __syncwarp();
                 }
-                if (!mbar_wait(b_qf + 8 * s, (it >> 1) & 1)) { ok = false; break; }
-                // S^T/dP^T(it) overwrite the columns whose P^T/dS^T the dV/dK MMAs of it-1 read as A operands: MMAs on
-                // different accumulators are not ordered against each other, so wait for their completion
-                if (it >= 1 && !mbar_wait(b_qe + 8 * (s ^ 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
-                tc_fence_after();
-                // S^T (128 keys x 64 queries) = K Q^T and dP^T = V dO^T over the 128-wide head: 8 k-steps each
+                if (it < n_it) {
+                    const uint32_t so = (uint32_t)(it % QST) * 1024;     // stage offset (16 KB) in 16-byte units
+                    if (!mbar_wait(b_qf + 8 * (it % QST), (it / QST) & 1) || *abort_flag) { ok = false; break; }
+                    // every softmax thread holds S^T / dP^T of sub-tile it-1 in registers
+                    if (it >= 1 && !mbar_wait(b_sfree, (it - 1) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    // S^T (128 keys x 64 queries) = K Q^T and dP^T = V dO^T over the 128-wide head: 8 k-steps each
 #pragma unroll
-                for (int kk = 0; kk < DH2 / 16; kk++)
-                    mma128_ss_e(t_S, desc_of(loK_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loQ_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
+                    for (int kk = 0; kk < DH2 / 16; kk++)
+                        mma128_ss_e(t_S, desc_of(loK_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loQ_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
 #pragma unroll
-                for (int kk = 0; kk < DH2 / 16; kk++)
-                    mma128_ss_e(t_dP, desc_of(loV_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loO_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
-                commit128_e(b_sdp);
-                if (!mbar_wait(b_pds, it & 1)) { ok = false; break; }
-                tc_fence_after();
-                // P^T / dS^T in TMEM: queries 0..31 packed in columns 0..15, queries 32..63 in columns 32..47
+                    for (int kk = 0; kk < DH2 / 16; kk++)
+                        mma128_ss_e(t_dP, desc_of(loV_k + (kk >> 2) * 1024 + (kk & 3) * 2), desc_of(loO_k + so + (kk >> 2) * 512 + (kk & 3) * 2), id_s, kk != 0);
+                    commit128_e(b_sdp);
+                }
+                if (it >= 1) {
+                    const int p = it - 1;                                  // the sub-tile whose P^T / dS^T are due
+                    const uint32_t so = (uint32_t)(p % QST) * 1024;
+                    if (!mbar_wait(b_pds, p & 1) || *abort_flag) { ok = false; break; }
+                    tc_fence_after();
+                    // P^T / dS^T: 64 queries packed in 32 columns, 16 queries (8 columns) per k-step
 #pragma unroll
-                for (int kk = 0; kk < QS / 16; kk++)       // dV += P^T dO   (k = queries; B = dO sub-tile, head-dim blocks 8 KB apart)
-                    mma128_ts_e(t_dV, t_S + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loO_n + so + kk * 128), id_acc, (it | kk) != 0);
+                    for (int kk = 0; kk < QS / 16; kk++)       // dV += P^T dO   (k = queries; B = dO sub-tile, head-dim blocks 8 KB apart)
+                        mma128_ts_e(t_dV, t_P + kk * 8, desc_of(loO_n + so + kk * 128), id_acc, (p | kk) != 0);
 #pragma unroll
-                for (int kk = 0; kk < QS / 16; kk++)       // dK += dS^T Q
-                    mma128_ts_e(t_dK, t_dP + (kk >> 1) * 32 + (kk & 1) * 8, desc_of(loQ_n + so + kk * 128), id_acc, (it | kk) != 0);
-                commit128_e(b_qe + 8 * s);                   // Q/dO stage and the P^T/dS^T columns are free once these have run
+                    for (int kk = 0; kk < QS / 16; kk++)       // dK += dS^T Q
+                        mma128_ts_e(t_dK, t_dS + kk * 8, desc_of(loQ_n + so + kk * 128), id_acc, (p | kk) != 0);
+                    commit128_e(b_qe + 8 * (p % QST));          // the Q/dO stage and the P^T / dS^T columns are free once these have run
+                    // the single dQ^T accumulator: sub-tile p-1 has been moved out
+                    if (p >= 1 && !mbar_wait(b_dqe, (p - 1) & 1)) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < AT / 16; kk++)       // dQ^T = K^T dS^T   (k = keys), double-buffered
-                    mma128_ss_e(t_dQ + (it & 1) * 64, desc_of(loK_m + kk * 128), desc_of(loDS + kk * 128), id_dq, kk != 0);
-                commit128_e(b_dq + 8 * (it & 1));
+                    for (int kk = 0; kk < AT / 16; kk++)       // dQ^T = K^T dS^T   (k = keys), dS^T from its shared-memory buffer
+                        mma128_ss_e(t_dQ, desc_of(loK_m + kk * 128), desc_of(loDS + (p & 1) * 1024 + kk * 128), id_dq, kk != 0);
+                    commit128_e(b_dq);
+                }
             }
             __syncwarp();
             if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, STAT_BWD128 | 1); }
@@ -396,23 +424,18 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float c = scale * LOG2E;
         bool ok = true;
-        // row statistics of a sub-tile: threads 0..63 fetch lse, threads 64..127 fetch D
-        auto stat_of = [&](int it) -> float {
-            const int hh = it / per_head, u = 2 * j + it % per_head, h = g * rep + hh;
-            const long long idx = ((long long)b * H + h) * T + u * QS + (threadIdx.x & 63);
-            return threadIdx.x < 64 ? lse[idx] * LOG2E : Dv[idx];
-        };
-        if (threadIdx.x < 128) s_stat[threadIdx.x] = stat_of(0);
         // drain of dQ^T(t): TMEM (lanes = head dim, columns = queries) -> transposed, swizzled fp32 staging
         // (rows = queries, four 32-float blocks) -> TMA reduce-add into the fp32 dq buffer
         auto drain = [&](int t) -> bool {
-            if (!mbar_wait(b_dq + 8 * (t & 1), (t >> 1) & 1) || *abort_flag) return false;
+            if (!mbar_wait(b_dq, t & 1) || *abort_flag) return false;
             tc_fence_after();
             if (threadIdx.x == 0) bulk_wait_read0();         // the previous reduce has finished reading the staging
             named_bar_sync(1, 256);
             uint32_t v[32];
-            tmem_ld32(t_dQ + (t & 1) * 64 + lane_base + hf * 32, v);
+            tmem_ld32(t_dQ + lane_base + hf * 32, v);
             tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(b_dqe);                              // the accumulator may be overwritten by the next dQ^T
             // element (query q, head-dim r): block r/32, row q (128 B), 16-byte chunk ((r%32)/4) ^ (q & 7)
             uint8_t* col = smem + Bwd128Smem::DQ + (r >> 5) * 8192 + (r & 3) * 4;
             const int ch = (r & 31) >> 2;
@@ -422,37 +445,37 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 *reinterpret_cast<float*>(col + qq * 128 + ((ch ^ (qq & 7)) << 4)) = __uint_as_float(v[q]) * scale;
             }
             fence_async_smem();
-            tc_fence_before();
             named_bar_sync(1, 256);
             if (threadIdx.x == 0) {
                 const int hh = t / per_head, u = 2 * j + t % per_head, h = g * rep + hh;
 #pragma unroll
+#ifndef AXENG_EXP_NOREDUCE
                 for (int blk = 0; blk < 4; blk++)
                     tma_reduce_add_4d(&tmdQ, sb + Bwd128Smem::DQ + blk * 8192, blk * 32, h, u * QS, b);
+#endif
                 bulk_commit();
             }
             return true;
         };
-        named_bar_sync(1, 256);
+        const float c_l = -LOG2E;
         for (int it = 0; it < n_it && ok; it++) {
             const int u = 2 * j + it % per_head;              // query sub-tile
-            const int cur = it & 1;
-            float nxt = 0.f;
-            if (it + 1 < n_it && threadIdx.x < 128) nxt = stat_of(it + 1);
             if (!mbar_wait(b_sdp, it & 1) || *abort_flag) { ok = false; break; }
-            // the dS^T tile in shared memory is rewritten below: dQ^T of the previous sub-tile must have read it
-            if (it >= 1 && !mbar_wait(b_dq + 8 * ((it - 1) & 1), ((it - 1) >> 1) & 1)) { ok = false; break; }
+            // the stage's barrier completed before S^T was issued; observing it makes the bulk-copied statistics visible
+            if (!mbar_wait(b_qf + 8 * (it % QST), (it / QST) & 1)) { ok = false; break; }
             tc_fence_after();
             const bool diag = u < 2 * j + 2;                  // sub-tiles that straddle this key tile's diagonal
             const int qoff = u * QS - j * AT;                 // query index of column 0 relative to key row 0
-            const float* L = s_stat + cur * 128;
+            const float* L = s_stat + (it % QST) * 128;
             const float* Dr = L + 64;
-            uint8_t* ds_row = smem + Bwd128Smem::DS + r * 128;
+            uint8_t* ds_row = smem + Bwd128Smem::DS + (it & 1) * 16384 + r * 128;
             {
                 uint32_t sv[32], dp[32], wp[16], wd[16];
                 tmem_ld32(t_S + lane_base + hf * 32, sv);
                 tmem_ld32(t_dP + lane_base + hf * 32, dp);
                 tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(b_sfree);                            // the two accumulators are free for the next sub-tile
                 if (diag) {                                      // query < key: masked (score -> -inf, so P = dS = 0)
 #pragma unroll
                     for (int q = 0; q < 32; q++)
@@ -463,18 +486,22 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     const int cs = hf * 32 + q;                  // query column within the sub-tile
                     const float4 l4 = *reinterpret_cast<const float4*>(L + cs);       // broadcast 16-byte loads
                     const float4 d4 = *reinterpret_cast<const float4*>(Dr + cs);
-                    float p0 = fast_exp2(__uint_as_float(sv[q]) * c - l4.x);
-                    float p1 = fast_exp2(__uint_as_float(sv[q + 1]) * c - l4.y);
-                    float p2 = fast_exp2(__uint_as_float(sv[q + 2]) * c - l4.z);
-                    float p3 = fast_exp2(__uint_as_float(sv[q + 3]) * c - l4.w);
+                    float p0 = fast_exp2(fmaf(__uint_as_float(sv[q]), c, l4.x * c_l));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(sv[q + 1]), c, l4.y * c_l));
+                    float p2 = fast_exp2(fmaf(__uint_as_float(sv[q + 2]), c, l4.z * c_l));
+                    float p3 = fast_exp2(fmaf(__uint_as_float(sv[q + 3]), c, l4.w * c_l));
                     wp[q >> 1] = pack_bf16(p0, p1);
                     wp[(q >> 1) + 1] = pack_bf16(p2, p3);
                     wd[q >> 1] = pack_bf16(p0 * (__uint_as_float(dp[q]) - d4.x), p1 * (__uint_as_float(dp[q + 1]) - d4.y));
                     wd[(q >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[q + 2]) - d4.z), p3 * (__uint_as_float(dp[q + 3]) - d4.w));
                 }
-                // packed columns hf*32 .. hf*32+15: inside the columns this thread has read
-                tmem_st16(t_S + lane_base + hf * 32, wp);
-                tmem_st16(t_dP + lane_base + hf * 32, wd);
+                // P^T / dS^T columns were last read by dV / dK of the previous sub-tile (issued a whole pass of arithmetic
+                // ago); the shared-memory dS^T buffer of this parity by dQ^T of sub-tile it-2, whose completion these
+                // threads observed when they moved it out
+                if (it >= 1 && !mbar_wait(b_qe + 8 * ((it - 1) % QST), ((it - 1) / QST) & 1)) { ok = false; break; }
+                tc_fence_after();
+                tmem_st16(t_P + lane_base + hf * 16, wp);
+                tmem_st16(t_dS + lane_base + hf * 16, wd);
                 // dS^T also to shared memory (B operand of dQ^T): row = key, 16-byte chunk index XOR (row & 7)
 #pragma unroll
                 for (int k4 = 0; k4 < 4; k4++) {
@@ -487,11 +514,8 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(b_pds);
-            if (it + 1 < n_it && threadIdx.x < 128) s_stat[(cur ^ 1) * 128 + threadIdx.x] = nxt;
-            // dQ^T of the previous sub-tile: its MMA finished long ago, so this does not stall on the tensor pipe;
-            // the barriers inside (or the one below) also publish the statistics just written
-            if (it == 0) named_bar_sync(1, 256);
-            else if (!drain(it - 1)) { ok = false; break; }
+            // dQ^T of the previous sub-tile: its MMA was issued right after that sub-tile's P^T / dS^T were handed over
+            if (it >= 1 && !drain(it - 1)) { ok = false; break; }
         }
         if (ok && !drain(n_it - 1)) ok = false;
         if (threadIdx.x == 0) bulk_wait0();
