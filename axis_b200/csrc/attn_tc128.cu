@@ -449,10 +449,8 @@ k_attn_bwd_tc128(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (threadIdx.x == 0) {
                 const int hh = t / per_head, u = 2 * j + t % per_head, h = g * rep + hh;
 #pragma unroll
-#ifndef AXENG_EXP_NOREDUCE
                 for (int blk = 0; blk < 4; blk++)
                     tma_reduce_add_4d(&tmdQ, sb + Bwd128Smem::DQ + blk * 8192, blk * 32, h, u * QS, b);
-#endif
                 bulk_commit();
             }
             return true;
