@@ -103,9 +103,9 @@ def test_bf16_step_within_tolerance_of_fp32():
 
 def test_bf16_tensor_core_shapes_and_curve():
     """A shape large enough for every GEMM to take the tcgen05 path (N = 512 tokens,
-    dims multiples of 128): gradients vs the fp32 oracle, then 30 steps of loss drift at lr 1e-3
-    (the reference's own curve gate, engine/modal_harden_test.py:178-227, allows 3e-2 for bf16 over
-    30 steps at this learning rate; a single step is held to the 1e-3 bar above)."""
+    dims multiples of 128): gradients vs the fp32 oracle, then 30 optimizer steps at lr 1e-3 with the loss of every
+    step held to 1e-3 of the fp32 oracle's (measured drift about 1e-4; the reference's own curve gate,
+    engine/modal_harden_test.py:178-227, allows 3e-2 for bf16 over 30 steps at this learning rate)."""
     cfg = dict(vocab_size=512, dim=256, n_layers=2, n_heads=4, n_kv_heads=2, mlp_hidden=384, tie_embeddings=True)
     w0 = O.init_weights(cfg, seed=1)
     rng = np.random.default_rng(1)
@@ -126,7 +126,7 @@ def test_bf16_tensor_core_shapes_and_curve():
         b, _, _ = O.train_step(model, opt, x, y, max_grad_norm=1.0)
         drift = max(drift, abs(a - b) / abs(b))
     print(f"bf16 30-step loss drift vs the fp32 oracle: {drift:.2e}")
-    assert drift <= 3e-3, drift
+    assert drift <= 1e-3, drift
     assert ct.eng.device_status() == 0
 
 
