@@ -287,7 +287,7 @@ class CompiledTransformer:
         self.b_lr = eng.new_tensor(np.array([lr], dtype=np.float32))
         self.b_t = eng.new_tensor(np.zeros(1, dtype=np.float32))
         self.b_gnorm = A(1)          # global gradient norm of the last step
-        self.b_sumsq = eng.alloc_zero(4 * max(cw, 1))     # per-owner sum of squares
+        self.b_sumsq = eng.alloc_zero(4 * 64)             # per-owner (or, on one GPU, per-bucket) sums of squares
         self.b_sumsq_local = eng.alloc_zero(4)
         npart = max(1, (max(s[1] for s in self._seg) + 8191) // 8192)
         self.b_partials = A(npart)
@@ -699,7 +699,39 @@ class CompiledTransformer:
                 out += [op(EVENT, tb=1, sa=1, oa=EV_W + b)]
             return out + [op(STREAM, tb=0)]
         self._gather_ops = gather_ops
-        self.plan_step = gather_ops() + self._plan_fb_sync + opt_ops(max_grad_norm)
+
+        # One GPU: the squared norm of a bucket's gradients is taken as soon as the bucket is complete and AdamW sums
+        # the per-bucket figures in bucket order.  With the weight gradients on the side stream the norms run there too
+        # (behind the bucket's dW GEMMs, which that stream runs in order, and behind an event for what the main chain
+        # contributes: norm weight gradients, the embedding scatter), so the pass over the gradient arena that the clip
+        # needs runs under the backward instead of between it and AdamW.  The inline plan takes the same per-bucket
+        # sums on the main chain, so both plans add the same numbers in the same order.
+        def plan_with_bucket_norms():
+            merged, last, e = [], 0, ev[0]
+            for b in range(nb):
+                cut = marks.get(b, last)
+                merged += plan[last:cut]
+                last = cut
+                st, ln = self._groups[0][b]
+                gn = op(GNORM_FLAT, a=self.a_grad, c=self.b_partials, d=self.b_sumsq, ob=b, m=ln // CHUNK,
+                        oa=st // CHUNK, tb=(self.b_t if b == 0 else 0))
+                if side_dw:
+                    e += 2
+                    merged += [op(EVENT, tb=1, sa=0, oa=e - 1), op(EVENT, tb=2, sa=2, oa=e - 1), op(STREAM, tb=2), gn,
+                               op(EVENT, tb=1, sa=2, oa=e), op(STREAM, tb=0)]
+                else:
+                    merged += [gn]
+            merged += plan[last:] + ([op(EVENT, tb=2, sa=0, oa=e)] if side_dw else [])
+            s0, sl = my_seg
+            return merged + [op(ADAMW_FLAT, a=self.a_master, b=self.a_grad, c=self.a_m, d=self.a_v,
+                                m=sl // CHUNK, k=s0 // CHUNK, sa=(self.a_mirror if hf else 0), sb=self.b_lr,
+                                tb=self.b_t, sc=self.b_wdflag, oa=self.b_sumsq, ob=nb, oc=self.b_gnorm,
+                                alpha=float(max_grad_norm or 0.0), beta=self.wd, gamma=adam_eps)]
+        self.bucket_norms = bool(cw == 1 and not zero and nb <= 64 and all(self._groups[0][b][1] > 0 for b in range(nb)))
+        if self.bucket_norms:
+            self.plan_step = plan_with_bucket_norms()
+        else:
+            self.plan_step = gather_ops() + self._plan_fb_sync + opt_ops(max_grad_norm)
         self._plan_noclip = None
         self._captured = False
         self._pending_loss = None            # read-back ticket of the last replay_step_async

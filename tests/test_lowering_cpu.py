@@ -246,6 +246,7 @@ def _side_stream_hazards(plan):
               E.ATTN_BWD: ["tb", "sc", "oa", "oc"], E.ROPE_BTHD: ["c", "sb"], E.CE_FUSED: ["c", "d", "sa", "sb"],
               E.EMBED_I32: ["c"], E.EMBED_BWD_DET: ["c"], E.SILU_MUL: ["c"], E.SCALE: ["c"]}
     bad, stream = [], 0
+    n_norms = [0]
     side = []                                   # (index, reads, writes, e_out or None)
     for i, o in enumerate(plan):
         k = o[0]
@@ -261,6 +262,17 @@ def _side_stream_hazards(plan):
                         s_[4].add(o[F["sa"]])
             continue
         if stream == 2:
+            if k == E.GNORM_FLAT:
+                # a bucket's squared norm, in order behind the bucket's dW GEMMs on this stream: it must also wait for
+                # the main chain (norm weight gradients, embedding scatter) and be awaited before AdamW
+                prev = plan[i - 1], plan[i - 2], plan[i - 3]
+                if not (prev[0][0] == E.STREAM and prev[1][0] == E.EVENT and prev[1][F["tb"]] == 2 and prev[1][F["sa"]] == 2
+                        and prev[2][0] == E.EVENT and prev[2][F["tb"]] == 1 and prev[2][F["sa"]] == 0
+                        and prev[1][F["oa"]] == prev[2][F["oa"]]):
+                    bad.append((i, "side-stream norm does not wait for the main chain"))
+                side.append([i, set(), {o[F["c"]], o[F["d"]]}, None, set()])
+                n_norms[0] += 1
+                continue
             if k not in (E.GEMM_SB, E.GEMM_GROUP):
                 bad.append((i, "non-GEMM op on the side stream"))
             prev = plan[i - 1], plan[i - 2], plan[i - 3]
@@ -289,7 +301,7 @@ def _side_stream_hazards(plan):
                 bad.append((i, f"{E.KIND_NAMES[k]} over the gradient arena before the side GEMM at {s_[0]} is awaited"))
     if any(0 not in s_[4] for s_ in side):
         bad.append((len(plan), "the main chain ends before the side stream"))
-    return bad, len(side)
+    return bad, len(side) - n_norms[0]
 
 
 @pytest.mark.parametrize("world", [1, 2])
@@ -427,3 +439,28 @@ def test_adapter_plan_is_a_few_fat_launches_per_layer():
     assert sum(-o[8] for o in ct.plan_step if o[0] == E.LORA_GRAD and o[8] < 0) == 14 * L   # ... of its 14 noted products
     assert kinds.count(E.GEMM_XSEG) == 8 * L
     assert kinds.count(E.ROPE_BTHD) == L            # head_dim 16 here: the rotary epilogue serves head_dim 64
+
+
+def test_bucket_norms_on_the_side_stream_match_the_single_pass():
+    """One GPU: the clip's gradient norm is assembled from per-bucket sums taken as the buckets complete — on the side
+    stream when the weight gradients run there, on the main chain otherwise; both plans give the same bits, the norm is
+    the norm of all gradients, and the step counter ticks once per step."""
+    cfg = dict(vocab_size=61, dim=32, n_layers=5, n_heads=4, n_kv_heads=2, mlp_hidden=48, tie_embeddings=True)
+    w0 = O.init_weights(cfg, seed=2)
+    rng = np.random.default_rng(2)
+    a = CompiledTransformer(InterpEngine(), cfg, w0, 2, 8, dtype="fp32", max_grad_norm=0.5)
+    b = CompiledTransformer(InterpEngine(), cfg, w0, 2, 8, dtype="fp32", max_grad_norm=0.5, overlap_dw=False)
+    assert a.bucket_norms and b.bucket_norms and a.overlap_dw and not b.overlap_dw
+    assert sum(1 for o in a.plan_step if o[0] == E.GNORM_FLAT) == a._nbuckets
+    assert any(o[0] == E.STREAM and o[9] == 2 for o in a.plan_step) and not any(o[0] == E.EVENT for o in b.plan_step)
+    for _ in range(3):
+        x, y = O.make_batch(rng, cfg["vocab_size"], 2, 8, 0.1)
+        la, lb = a.step(x, y), b.step(x, y)
+        assert la == lb and a.grad_norm() == b.grad_norm()       # the same sums in the same order
+        # the model's own reference: one pass over all gradients
+        g = a.grads()
+        total = np.sqrt(sum(float((v.astype(np.float64) ** 2).sum()) for v in g.values()))
+        assert abs(a.grad_norm() - total) <= 1e-5 * total
+    wa, wb = a.get_weights(), b.get_weights()
+    assert all(np.array_equal(wa[n], wb[n]) for n in wa)
+    assert a.state_dict()["_t"][0] == b.state_dict()["_t"][0] == 3.0
