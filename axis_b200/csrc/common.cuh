@@ -95,3 +95,23 @@ static inline int ew_grid(long long work_items, int threads) {
     return (int)b;
 }
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Programmatic dependent launch.  A kernel of the main chain lets its successor be scheduled early and then waits
+// itself until its predecessor in the stream has completed (nothing before this point may read what that kernel
+// wrote); without the launch attribute both instructions are no-ops.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+extern int ax_gemm_pdl(void);
+// launch with the attribute that allows the overlap (off on the side stream and with AXENG_NO_PDL=1, like the GEMMs)
+template <typename... KA, typename... A>
+static inline cudaError_t ax_launch_chain(void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = ax_gemm_pdl() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KA>(args)...);
+}

@@ -364,6 +364,7 @@ template <typename T>
 __global__ void k_silu_bwd(const T* __restrict__ g, const T* __restrict__ u, const T* __restrict__ grad,
                            T* __restrict__ dg, T* __restrict__ du, long long n, int vec) {
     constexpr int N = Vec<T>::N;
+    pdl_enter();
     const long long stride = (long long)gridDim.x * blockDim.x;
     long long start = 0;
     if (vec) {
@@ -393,7 +394,7 @@ __global__ void k_silu_bwd(const T* __restrict__ g, const T* __restrict__ u, con
 int ax_silu_bwd(int dt, const void* g, const void* u, const void* grad, void* dg, void* du, long long n, cudaStream_t st) {
     if (n <= 0) return 0;
     const int vec = aligned16(g) && aligned16(u) && aligned16(grad) && aligned16(dg) && aligned16(du);
-    if (dt == 1) k_silu_bwd<bf16><<<ew_grid(n / 8 + 1, T256), T256, 0, st>>>((const bf16*)g, (const bf16*)u, (const bf16*)grad, (bf16*)dg, (bf16*)du, n, vec);
+    if (dt == 1) ax_launch_chain(k_silu_bwd<bf16>, dim3(ew_grid(n / 8 + 1, T256)), dim3(T256), 0, st, (const bf16*)g, (const bf16*)u, (const bf16*)grad, (bf16*)dg, (bf16*)du, n, vec);
     else k_silu_bwd<float><<<ew_grid(n / 4 + 1, T256), T256, 0, st>>>((const float*)g, (const float*)u, (const float*)grad, (float*)dg, (float*)du, n, vec);
     return 0;
 }

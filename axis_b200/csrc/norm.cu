@@ -50,6 +50,7 @@ template <typename T, int VPL>
 __global__ void __launch_bounds__(256)
 k_rmsnorm_warp(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ o, int rows, float eps) {
     constexpr int N = Vec<T>::N, DIM = 32 * VPL * N;
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nw = gridDim.x * (blockDim.x >> 5);
     for (int r = gw; r < rows; r += nw) {
@@ -202,6 +203,7 @@ k_rmsnorm_bwd_packed(const bf16* __restrict__ x, const bf16* __restrict__ w, con
                      bf16* dx, float* __restrict__ partial, int rows, float eps) {
     constexpr int DIM = 32 * VPL * 8;
     extern __shared__ float sdw_all[];                     // [RBP_WARPS][DIM]
+    pdl_enter();
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int gw = blockIdx.x * RBP_WARPS + wib, nw = gridDim.x * RBP_WARPS;
     float* sdw = sdw_all + wib * DIM;
@@ -353,7 +355,7 @@ int ax_rmsnorm(int dt, const void* x, const void* w, void* o, int rows, int dim,
     if (vec && dim % (32 * per) == 0 && dim / (32 * per) <= 8) {
         const int vpl = dim / (32 * per);
         const int g = (rows + 7) / 8 < AX_SMS * 8 ? (rows + 7) / 8 : AX_SMS * 8;
-#define NW(TT, V) case V: k_rmsnorm_warp<TT, V><<<g, 256, 0, st>>>((const TT*)x, (const TT*)w, (TT*)o, rows, eps); return 0;
+#define NW(TT, V) case V: ax_launch_chain(k_rmsnorm_warp<TT, V>, dim3(g), dim3(256), 0, st, (const TT*)x, (const TT*)w, (TT*)o, rows, eps); return 0;
         if (dt == 1) { switch (vpl) { NW(bf16, 1) NW(bf16, 2) NW(bf16, 3) NW(bf16, 4) NW(bf16, 5) NW(bf16, 6) NW(bf16, 7) NW(bf16, 8) } }
         else { switch (vpl) { NW(float, 1) NW(float, 2) NW(float, 3) NW(float, 4) NW(float, 5) NW(float, 6) NW(float, 7) NW(float, 8) } }
 #undef NW
@@ -538,7 +540,7 @@ int ax_rmsnorm_bwd_acc(int dt, const void* x, const void* w, const void* g, cons
         if (dt == 1) {
             int nbp = (rows + RBP_WARPS - 1) / RBP_WARPS;
             if (nbp > RB_BLOCKS) nbp = RB_BLOCKS;            // 296 blocks: two per SM resident at once, one wave
-#define BP(V) case V: k_rmsnorm_bwd_packed<V><<<nbp, RBP_WARPS * 32, (size_t)RBP_WARPS * dim * 4, st>>>((const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
+#define BP(V) case V: ax_launch_chain(k_rmsnorm_bwd_packed<V>, dim3(nbp), dim3(RBP_WARPS * 32), (size_t)RBP_WARPS * dim * 4, st, (const bf16*)x, (const bf16*)w, (const bf16*)g, (const bf16*)res, (bf16*)dx, part, rows, eps); break;
             switch (vpl) { BP(1) BP(2) BP(3) BP(4) BP(5) BP(6) }
 #undef BP
             if (dw && !defer) k_colsum_partials<<<(dim + 31) / 32, dim3(32, 8), 0, st>>>(scratch, dw, nbp, dim);
