@@ -174,8 +174,10 @@ int ax_lora_grad(int count, const void* const* X, const void* const* S, float* c
         a.p[g].chunks = (F[g] + LG_COLS - 1) / LG_COLS;
         chunks += a.p[g].chunks; fsum += F[g]; fmax = F[g] > fmax ? F[g] : fmax;
     }
-    // token slices: enough CTAs for about three per SM, at least one 64-token stage each, partials inside the workspace
-    int nsplit = (3 * AX_SMS + chunks - 1) / chunks;
+    // token slices: as many CTAs as are resident at once (three per SM) and no more — a second, partial wave would cost
+    // as much as the first; at least one 64-token stage each, partials inside the workspace
+    int nsplit = (3 * AX_SMS) / chunks;
+    if (nsplit < 1) nsplit = 1;
     const int max_split = (N + LG_TOK - 1) / LG_TOK;
     if (nsplit > max_split) nsplit = max_split;
     if (nsplit > 64) nsplit = 64;
